@@ -1,0 +1,80 @@
+// RMSNorm and residual-add + RMSNorm over the 32-bit residual stream.
+//
+//   residual[r] += delta[r]            (32-bit sum; skipped when delta is null)
+//   out[o]       = residual[r] * rsqrt(mean(residual[r]^2) + eps) * weight
+//
+// Statistics, the product with the weight and the residual sum are 32-bit; the result is rounded
+// once to the activation type.  The reference's fused kernel (utils/fused_ops.py:65-78) rounds
+// the residual sum to the activation type first; keeping the stream in 32-bit is more exact.
+// `rows` (optional) selects the source rows: output row o reads row rows[o]; used for the final
+// norm, which runs only where logits are wanted (utils/model.py:147-157).
+#include "common.cuh"
+
+template <typename T, typename W>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                   const W* __restrict__ weight, T* __restrict__ out,
+                                   const int* __restrict__ rows, int width, float eps, int write_residual) {
+    __shared__ float scratch[33];
+    const int o = blockIdx.x;
+    const int r = rows ? rows[o] : o;
+    float* res = residual + (size_t)r * width;
+    const T* del = delta ? delta + (size_t)r * width : nullptr;
+    float sum_squares = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = res[i];
+        if (del) {
+            v += Num<T>::load(del + i);
+            if (write_residual) res[i] = v;
+        }
+        sum_squares += v * v;
+    }
+    const float total = block_sum(sum_squares, scratch);
+    const float inverse = rsqrtf(total / (float)width + eps);
+    T* dst = out + (size_t)o * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = res[i];
+        if (del && !write_residual) v += Num<T>::load(del + i);
+        Num<T>::store(dst + i, v * inverse * Num<W>::load(weight + i));
+    }
+}
+
+// Plain RMSNorm of activation-typed rows (used by parts that normalise something other than the
+// residual stream).  Same arithmetic.
+template <typename T, typename W>
+__global__ void rmsnorm_kernel(const T* __restrict__ x, const W* __restrict__ weight, T* __restrict__ out,
+                               int width, float eps) {
+    __shared__ float scratch[33];
+    const T* src = x + (size_t)blockIdx.x * width;
+    float sum_squares = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = Num<T>::load(src + i);
+        sum_squares += v * v;
+    }
+    const float total = block_sum(sum_squares, scratch);
+    const float inverse = rsqrtf(total / (float)width + eps);
+    T* dst = out + (size_t)blockIdx.x * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        Num<T>::store(dst + i, Num<T>::load(src + i) * inverse * Num<W>::load(weight + i));
+}
+
+static int norm_threads(int width) { return width >= 2048 ? 512 : (width >= 512 ? 256 : 128); }
+
+LLM_EXPORT int llm_add_rmsnorm(float* residual, const void* delta, const void* weight, void* out, const int* rows,
+                               int n_rows, int width, float eps, int write_residual, int dtype,
+                               int weight_dtype, cudaStream_t stream) {
+    if (n_rows == 0) return LLM_OK;
+    LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype,
+                              (add_rmsnorm_kernel<T, W><<<n_rows, norm_threads(width), 0, stream>>>(
+                                  residual, (const T*)delta, (const W*)weight, (T*)out, rows, width, eps,
+                                  write_residual)));
+    return llm_check_launch("add_rmsnorm");
+}
+
+LLM_EXPORT int llm_rmsnorm(const void* x, const void* weight, void* out, int n_rows, int width, float eps,
+                           int dtype, int weight_dtype, cudaStream_t stream) {
+    if (n_rows == 0) return LLM_OK;
+    LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype,
+                              (rmsnorm_kernel<T, W><<<n_rows, norm_threads(width), 0, stream>>>(
+                                  (const T*)x, (const W*)weight, (T*)out, width, eps)));
+    return llm_check_launch("rmsnorm");
+}

@@ -1,0 +1,45 @@
+// Error channel and device queries of the kernel library.
+#include "common.cuh"
+
+#include <stdarg.h>
+#include <stdio.h>
+
+static thread_local char g_last_error[512] = "";
+
+void llm_set_error(const char* format, ...) {
+    va_list args;
+    va_start(args, format);
+    vsnprintf(g_last_error, sizeof(g_last_error), format, args);
+    va_end(args);
+}
+
+int llm_check_launch(const char* what) {
+    cudaError_t status = cudaGetLastError();
+    if (status != cudaSuccess) {
+        llm_set_error("%s: %s", what, cudaGetErrorString(status));
+        return (int)status;
+    }
+    return LLM_OK;
+}
+
+LLM_EXPORT const char* llm_last_error() { return g_last_error; }
+
+// Compute capability of the current device as major * 10 + minor, or a negative CUDA error.
+LLM_EXPORT int llm_device_arch() {
+    int device = 0, major = 0, minor = 0;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status == cudaSuccess) status = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+    if (status == cudaSuccess) status = cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device);
+    if (status != cudaSuccess) {
+        llm_set_error("device query: %s", cudaGetErrorString(status));
+        return -(int)status;
+    }
+    return major * 10 + minor;
+}
+
+LLM_EXPORT int llm_sm_count() {
+    int device = 0, count = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return -1;
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return -1;
+    return count;
+}

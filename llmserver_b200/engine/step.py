@@ -1,0 +1,96 @@
+"""The step function: one batch of (request, its next tokens) through the model and the cache.
+
+It runs only the tokens it is given, as one flat batch, reading what earlier steps left in the
+cache, and returns float32 logits at the wanted places.  Pages are allocated before the forward, so
+the forward itself allocates nothing (the reference allocates blocks lazily inside the forward,
+utils/kv_cache.py:220-277,335-338).  Generation, the scheduler and trace replay all go through this
+one function.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence, Tuple
+
+import torch
+
+from ..cache import CacheManager
+from .batch import SequenceSlice, StepBatch, build_batch
+
+StepEntry = Tuple[object, Sequence[int], Sequence[int]]  # (request id, next tokens, wanted places)
+
+
+class StepFunction:
+    def __init__(self, model, cache: CacheManager):
+        self.model, self.cache = model, cache
+        self.device = model.runtime.device
+        self.computed = {}          # request -> tokens already in the cache
+        model.bind_cache(cache)
+        self.pending_flags: List[torch.Tensor] = []
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ request lifetime
+    def admit(self, request_id, prompt: Sequence[int] = None) -> int:
+        """Registers a request with the cache; with ``prompt`` given, cached pages of a known prefix
+        are taken over.  Returns the number of prompt tokens that need no computing."""
+        self.cache.admit(request_id)
+        covered = self.cache.share_prefix(request_id, prompt) if prompt is not None else 0
+        self.computed[request_id] = covered
+        return covered
+
+    def release(self, request_id) -> None:
+        self.cache.free(request_id)
+        del self.computed[request_id]
+
+    def num_computed(self, request_id) -> int:
+        return self.computed[request_id]
+
+    # ------------------------------------------------------------------ the step
+    def prepare(self, entries: List[StepEntry]) -> StepBatch:
+        """Allocates the pages the step needs (all or nothing) and builds the device batch."""
+        seen = set()
+        for request_id, tokens, _ in entries:
+            if request_id in seen:
+                raise ValueError(f"request {request_id!r} appears twice in one step")
+            seen.add(request_id)
+            if request_id not in self.computed:
+                raise KeyError(f"request {request_id!r} was not admitted")
+        # check the whole step against what is available before allocating anything
+        totals = [0] * len(self.cache.groups)
+        for request_id, tokens, _ in entries:
+            needed = self.cache.pages_needed(request_id, self.computed[request_id] + len(tokens))
+            totals = [a + b for a, b in zip(totals, needed)]
+        for group, (total, available) in enumerate(zip(totals, self.cache.available())):
+            if total > available:
+                from ..cache import KVCacheExhaustedError
+                raise KVCacheExhaustedError(f"the step needs {total} pages in cache group {group}, {available} are available")
+        slices = []
+        for request_id, tokens, want in entries:
+            start = self.computed[request_id]
+            self.cache.ensure(request_id, start + len(tokens))
+            slices.append(SequenceSlice(request_id, tokens, start, want,
+                                        [self.cache.table(request_id, group) for group in range(len(self.cache.groups))],
+                                        self.cache.slot_of(request_id)))
+        limit = self.model.spec.max_positions
+        if limit is not None:
+            for piece in slices:
+                if piece.start + len(piece.tokens) > limit:
+                    raise ValueError(f"request {piece.request_id!r} would reach {piece.start + len(piece.tokens)} tokens; "
+                                     f"the model's max_position_embeddings is {limit}")
+        return build_batch(slices, len(self.cache.groups), self.device, self.model.spec.vocab_size)
+
+    def run(self, entries: List[StepEntry]) -> torch.Tensor:
+        """Runs one step; returns logits [wanted, vocab] (float32) in the order of the entries and of
+        their wanted places."""
+        batch = self.prepare(entries)
+        logits = self.model.step(batch)
+        self.pending_flags.append(batch.error_flag)
+        for request_id, tokens, _ in entries:
+            self.computed[request_id] += len(tokens)
+            self.cache.advance(request_id, self.computed[request_id])
+        self.steps_run += 1
+        return logits
+
+    def check_errors(self) -> None:
+        """Reads the kernels' error flags of the steps run since the last check (synchronises)."""
+        flags, self.pending_flags = self.pending_flags, []
+        if flags and int(torch.stack([flag.reshape(()) for flag in flags]).max().item()) != 0:
+            raise RuntimeError("a kernel met a block-table entry outside the page pool; the cache bookkeeping is corrupt")

@@ -1,0 +1,113 @@
+"""Loads the compiled kernel library and declares the C launchers' signatures.
+
+There is no fallback: if the library cannot be built or loaded, or the device is not a B200-class
+GPU, the engine refuses to run.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+
+import torch
+
+from ..csrc.build import KernelBuildError, ensure_built
+
+_P, _I, _F, _S = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+
+# name -> argument types (every launcher returns an int status; the stream comes last)
+SIGNATURES = {
+    "llm_embedding_gather": [_P, _P, _P, _I, _I, _I, _I, _S],
+    "llm_add_rmsnorm": [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _S],
+    "llm_rmsnorm": [_P, _P, _P, _I, _I, _F, _I, _I, _S],
+    "llm_silu_mul": [_P, _P, _I, _I, _I, _S],
+    "llm_sample": [_P, _P, _P, _P, _P, _I, _I, _S],
+    "llm_qk_norm_rope_kv_write": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _I, _S],
+    "llm_attention_generic": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _S],
+    "llm_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _S],
+}
+
+_lock = threading.Lock()
+_library = None
+_arch_checked = False
+
+
+class KernelError(RuntimeError):
+    """A launcher refused its arguments or CUDA reported an error."""
+
+
+def library() -> ctypes.CDLL:
+    global _library
+    if _library is None:
+        with _lock:
+            if _library is None:
+                path = ensure_built()
+                try:
+                    loaded = ctypes.CDLL(path)
+                except OSError as error:
+                    raise KernelBuildError(f"the kernel library {path} could not be loaded: {error}") from error
+                loaded.llm_last_error.restype = ctypes.c_char_p
+                loaded.llm_last_error.argtypes = []
+                for name, argtypes in SIGNATURES.items():
+                    function = getattr(loaded, name)
+                    function.argtypes = argtypes
+                    function.restype = ctypes.c_int
+                _library = loaded
+    return _library
+
+
+def declare(name: str, argtypes) -> None:
+    """Adds a launcher's signature (used by modules that own further kernels)."""
+    SIGNATURES[name] = argtypes
+    if _library is not None:
+        function = getattr(_library, name)
+        function.argtypes = argtypes
+        function.restype = ctypes.c_int
+
+
+def require_device() -> None:
+    """Raises unless CUDA is usable and the current device is compute capability 10.x."""
+    global _arch_checked
+    if _arch_checked:
+        return
+    if not torch.cuda.is_available():
+        raise KernelError("llmserver_b200 runs on a CUDA device only (no CPU path); torch.cuda.is_available() is False")
+    arch = library().llm_device_arch()
+    if arch < 0:
+        raise KernelError(f"device query failed: {library().llm_last_error().decode()}")
+    if arch // 10 != 10:
+        raise KernelError(f"the kernels are built for sm_100a (B200); the current device is sm_{arch}")
+    _arch_checked = True
+
+
+def call(name: str, *args) -> None:
+    status = getattr(library(), name)(*args)
+    if status != 0:
+        raise KernelError(f"{name} failed ({status}): {library().llm_last_error().decode()}")
+
+
+def stream_handle() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return 0
+    if dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"the kernels take float32 or bfloat16, not {dtype}")
+
+
+def pointer(tensor) -> int:
+    return 0 if tensor is None else tensor.data_ptr()
+
+
+def check(tensor: torch.Tensor, name: str, dtype=None, last_dim=None) -> torch.Tensor:
+    if not tensor.is_cuda:
+        raise KernelError(f"{name} must live on a CUDA device (there is no CPU path); it is on {tensor.device}")
+    if not tensor.is_contiguous():
+        raise KernelError(f"{name} must be contiguous; strides {tensor.stride()} for shape {tuple(tensor.shape)}")
+    if dtype is not None and tensor.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {tensor.dtype}")
+    if last_dim is not None and tensor.shape[-1] != last_dim:
+        raise KernelError(f"{name}: last dimension {tensor.shape[-1]} != {last_dim}")
+    return tensor

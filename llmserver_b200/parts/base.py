@@ -1,0 +1,99 @@
+"""Interfaces of the parts a layer is put together from.
+
+Every part is built from ``(params, weights, runtime)``: ``params`` are its sizes and constants
+(the dict form of its ``PartSpec``), ``weights`` the tensors it declared, already on the device,
+and ``runtime`` says in which dtype and on which device it runs.  No part knows which model it is in.
+
+    Mixer        forward(x [N, H], batch, cache) -> [N, H_out]   reads/writes its cache view
+    FeedForward  forward(x [N, H]) -> [N, H]
+    Norm         add_norm(residual f32 [N, H], delta or None, rows=None) -> normed [*, H]
+    PositionEncoding   holds what mixers need to encode positions (for rotary: inverse frequencies)
+    Block        forward(residual, delta, batch, cache) -> (residual, delta): the arrangement of
+                 norms, mixer and feed-forward around the residual stream; ``delta`` is the output of
+                 the previous sub-layer that has not been added to the stream yet, so that the add
+                 fuses with the next norm.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Optional
+
+import torch
+
+from ..weights.declare import WeightDecl
+
+
+@dataclass
+class Runtime:
+    dtype: torch.dtype
+    device: torch.device
+
+
+class Part:
+    @classmethod
+    def declare_weights(cls, params: dict) -> Dict[str, WeightDecl]:
+        """Local tensor name -> declaration."""
+        return {}
+
+    def __init__(self, params: dict, weights: Dict[str, torch.Tensor], runtime: Runtime):
+        self.params, self.runtime = params, runtime
+
+
+class Mixer(Part):
+    @classmethod
+    def cache_need(cls, params: dict):
+        """``KVPagesNeed``, ``StateNeed`` or None: what one execution of this mixer keeps per request."""
+        return None
+
+    def attach(self, position) -> None:
+        """Receives the position encoding the layer names (or None)."""
+
+    def forward(self, x: torch.Tensor, batch, cache) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Norm(Part):
+    def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor],
+                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def on_embedding(self, residual: torch.Tensor, batch) -> None:
+        """Hook for encodings that act on the embedded tokens (absolute tables); default: nothing."""
+
+
+class Block(Part):
+    ROLES = ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm")
+
+    @classmethod
+    def prefix_of(cls, params: dict, role: str) -> str:
+        """Tensor-name prefix (inside the layer) of the part in ``role``."""
+        return params.get(f"{role}_prefix", role + ".")
+
+    def __init__(self, params, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
+        self.params = params
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+
+    def forward(self, residual, delta, batch, cache):
+        raise NotImplementedError
+
+
+@dataclass
+class EntryCache:
+    """What one schedule entry sees of the cache manager's storage.
+
+    ``k_pages`` / ``v_pages``: [page, kv_head, slot, head_dim] (None for mixers without pages);
+    ``group``: which block table of the batch goes with these pages; ``writes``: False when the
+    entry reads the cache another entry wrote; ``state``: [slot, ...] tensor of per-request state."""
+    k_pages: Optional[torch.Tensor] = None
+    v_pages: Optional[torch.Tensor] = None
+    group: int = 0
+    writes: bool = True
+    state: Optional[torch.Tensor] = None

@@ -1,0 +1,31 @@
+"""SwiGLU feed-forward."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..weights.declare import WeightDecl
+from .base import FeedForward
+from .registry import FEED_FORWARDS
+
+
+@FEED_FORWARDS.register("swiglu")
+class SwiGLU(FeedForward):
+    """down(silu(gate(x)) * up(x)) without biases (utils/layers.py:182-218).  gate and up are
+    concatenated once at load into one [2 I, H] matrix, gate rows first, as the reference's
+    ``fuse_projections`` (utils/layers.py:194-203).  Parameters: ``hidden``, ``intermediate``."""
+
+    @classmethod
+    def declare_weights(cls, params):
+        hidden, intermediate = params["hidden"], params["intermediate"]
+        return {"gate_proj.weight": WeightDecl((intermediate, hidden)),
+                "up_proj.weight": WeightDecl((intermediate, hidden)),
+                "down_proj.weight": WeightDecl((hidden, intermediate))}
+
+    def __init__(self, params, weights, runtime):
+        super().__init__(params, weights, runtime)
+        self.gate_up = torch.cat([weights["gate_proj.weight"], weights["up_proj.weight"]], dim=0).contiguous()
+        self.down = weights["down_proj.weight"].contiguous()
+
+    def forward(self, x):
+        return ops.linear(ops.silu_mul(ops.linear(x, self.gate_up)), self.down)

@@ -1,0 +1,293 @@
+"""Each CUDA kernel alone against a plain PyTorch float64 computation of the same operation, at sizes
+other than the tiny models' (widths and vocabularies that are no power of two, head sizes in steps of
+16, several group sizes, page sizes 1 to 32)."""
+import math
+
+import pytest
+import torch
+
+import plain_model
+
+pytestmark = pytest.mark.gpu
+
+DEVICE = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tolerance(dtype):
+    # relative to the largest magnitude of the expected tensor
+    return 2e-6 if dtype == torch.float32 else 1e-2
+
+
+def close(got, want, dtype, what, factor=1.0):
+    got, want = got.double().cpu(), want.double().cpu()
+    assert got.shape == want.shape, f"{what}: {got.shape} != {want.shape}"
+    assert torch.isfinite(got).all(), f"{what}: non-finite values"
+    error = (got - want).abs().max().item() / max(want.abs().max().item(), 1e-30)
+    assert error <= tolerance(dtype) * factor, f"{what}: relative error {error:.3e}"
+
+
+def rand(shape, dtype, seed, scale=1.0):
+    generator = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=generator) * scale).to(dtype).to(DEVICE)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(dtype):
+    from llmserver_b200 import ops
+    table = rand((1000, 200), dtype, 1)
+    ids = torch.tensor([0, 999, 5, 5, 321], dtype=torch.int32, device=DEVICE)
+    out = ops.embedding(table, ids)
+    assert out.dtype == torch.float32
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [80, 1000, 4096, 5120 + 48])
+def test_add_rmsnorm(dtype, width):
+    from llmserver_b200 import ops
+    rows = 7
+    residual = rand((rows, width), torch.float32, 2)
+    delta = rand((rows, width), dtype, 3)
+    weight = rand((width,), dtype, 4) + 1
+    eps = 1e-5
+    expected_residual = residual.double() + delta.double()
+    expected = plain_model.rms_norm(expected_residual, weight.double(), eps)
+    work = residual.clone()
+    out = ops.add_rmsnorm(work, delta, weight, eps)
+    close(work, expected_residual, torch.float32, "residual sum")
+    close(out, expected, dtype, "add + norm")
+    # without a delta the residual is only read
+    work = residual.clone()
+    out = ops.add_rmsnorm(work, None, weight, eps)
+    assert torch.equal(work, residual)
+    close(out, plain_model.rms_norm(residual.double(), weight.double(), eps), dtype, "norm")
+    # selected rows: residual untouched, delta added on the fly
+    picks = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEVICE)
+    work = residual.clone()
+    out = ops.add_rmsnorm(work, delta, weight, eps, rows=picks)
+    assert torch.equal(work, residual)
+    close(out, expected[picks.long()], dtype, "norm of selected rows")
+    # a float32 weight beside bfloat16 activations
+    if dtype == torch.bfloat16:
+        out = ops.add_rmsnorm(residual.clone(), delta, weight.float(), eps, act_dtype=dtype)
+        close(out, expected, dtype, "norm with a 32-bit weight")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rmsnorm_and_silu_mul(dtype):
+    from llmserver_b200 import ops
+    x = rand((5, 176), dtype, 5)
+    weight = rand((176,), dtype, 6) + 1
+    close(ops.rmsnorm(x, weight, 1e-6), plain_model.rms_norm(x.double(), weight.double(), 1e-6), dtype, "rmsnorm")
+    gate_up = rand((9, 2 * 1111), dtype, 7, 3.0)
+    gate, up = gate_up.double()[:, :1111], gate_up.double()[:, 1111:]
+    close(ops.silu_mul(gate_up), torch.nn.functional.silu(gate) * up, dtype, "silu_mul")
+
+
+@pytest.mark.parametrize("shape", [(1, 7, 5), (33, 100, 77), (130, 257, 1000), (2, 509, 96), (64, 64, 16)])
+def test_gemm_f32_is_true_32_bit(shape):
+    from llmserver_b200 import ops
+    m, n, k = shape
+    x, w = rand((m, k), torch.float32, 8), rand((n, k), torch.float32, 9)
+    out = ops.gemm_f32(x, w)
+    close(out, x.double() @ w.double().T, torch.float32, f"gemm {shape}", factor=max(1.0, k / 200))
+    # a row's result does not depend on the other rows of the call
+    alone = ops.gemm_f32(x[m // 2:m // 2 + 1].contiguous(), w)
+    assert torch.equal(alone[0], out[m // 2])
+
+
+def test_linear_bf16():
+    from llmserver_b200 import ops
+    for m, n, k in [(1, 300, 128), (8, 509, 96), (70, 1000, 512), (300, 264, 200)]:
+        x, w = rand((m, k), torch.bfloat16, 10), rand((n, k), torch.bfloat16, 11)
+        want = x.double() @ w.double().T
+        close(ops.linear(x, w), want, torch.bfloat16, f"linear bf16 {(m, n, k)}")
+        out32 = ops.linear(x, w, out_dtype=torch.float32)
+        assert out32.dtype == torch.float32
+        close(out32, want, torch.bfloat16, f"linear bf16 -> f32 {(m, n, k)}")
+
+
+def paged(dense_k, dense_v, page_size, seed, dtype):
+    """Scatters per-sequence dense K/V ([T, Hkv, D] each) into shuffled pages; returns pages, tables."""
+    kv_heads, dim = dense_k[0].shape[1:]
+    counts = [-(-k.shape[0] // page_size) for k in dense_k]
+    total = sum(counts) + 3
+    order = torch.randperm(total, generator=torch.Generator().manual_seed(seed)).tolist()
+    k_pages = torch.zeros((total, kv_heads, page_size, dim), dtype=dtype)
+    v_pages = torch.zeros_like(k_pages)
+    tables = torch.zeros((len(dense_k), max(counts)), dtype=torch.int32)
+    for row, (k, v) in enumerate(zip(dense_k, dense_v)):
+        for block in range(counts[row]):
+            page = order.pop()
+            tables[row, block] = page
+            chunk = slice(block * page_size, min((block + 1) * page_size, k.shape[0]))
+            k_pages[page, :, :chunk.stop - chunk.start] = k[chunk].transpose(0, 1)
+            v_pages[page, :, :chunk.stop - chunk.start] = v[chunk].transpose(0, 1)
+    return k_pages.to(DEVICE), v_pages.to(DEVICE), tables.to(DEVICE)
+
+
+def plain_attention_rows(q, k, v, scale, window, first_query):
+    """Rows first_query.. of plain causal attention; q [Tq, Hq, D] are the LAST Tq positions."""
+    total = k.shape[0]
+    full_q = torch.zeros((total,) + q.shape[1:], dtype=torch.float64)
+    full_q[first_query:] = q
+    return plain_model.causal_attention(full_q, k, v, scale, window)[first_query:]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,dim,page_size,window", [
+    (4, 2, 16, 4, None), (6, 1, 32, 8, None), (6, 3, 48, 16, 24), (8, 8, 64, 1, None), (5, 5, 80, 32, 7),
+    (32, 8, 128, 16, None), (3, 1, 256, 16, 100)])
+def test_attention_generic(dtype, heads, kv_heads, dim, page_size, window):
+    """Mixed batch: a decode token of a long sequence, a prompt portion in the middle of another, a
+    whole short prompt and a single first token."""
+    from llmserver_b200 import ops
+    contexts = [333, 150, 37, 1]      # tokens each sequence holds after the step
+    q_lens = [1, 41, 37, 1]           # tokens of the step
+    scale = dim ** -0.5
+    dense_k = [rand((c, kv_heads, dim), dtype, 20 + i).cpu() for i, c in enumerate(contexts)]
+    dense_v = [rand((c, kv_heads, dim), dtype, 30 + i).cpu() for i, c in enumerate(contexts)]
+    k_pages, v_pages, tables = paged(dense_k, dense_v, page_size, 1, dtype)
+    queries = [rand((n, heads, dim), dtype, 40 + i).cpu() for i, n in enumerate(q_lens)]
+    q_stride = (heads + 2 * kv_heads) * dim
+    packed = torch.zeros((sum(q_lens), q_stride), dtype=dtype)
+    packed[:, :heads * dim] = torch.cat(queries).reshape(-1, heads * dim)
+    positions = torch.cat([torch.arange(c - n, c) for c, n in zip(contexts, q_lens)]).to(torch.int32).to(DEVICE)
+    seq_of_token = torch.cat([torch.full((n,), i) for i, n in enumerate(q_lens)]).to(torch.int32).to(DEVICE)
+    out = ops.attention_generic(packed.to(DEVICE), q_stride, k_pages, v_pages, tables, seq_of_token, positions,
+                                heads, kv_heads, dim, scale, window or 0)
+    want = torch.cat([plain_attention_rows(q.double(), k.double(), v.double(), scale, window, c - n)
+                      for q, k, v, c, n in zip(queries, dense_k, dense_v, contexts, q_lens)])
+    close(out, want, dtype, "attention")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_a_far_key_and_respects_the_window_edge(dtype):
+    """One key among hundreds gets a score far above the rest, so the output must be its value: at
+    position 3 of 700 (far away, first page), at a page's last slot, and at the two sides of a
+    window's edge (the key at p - window + 1 is seen, the one at p - window is not)."""
+    from llmserver_b200 import ops
+    heads, kv_heads, dim, page_size = 2, 1, 32, 16
+    context = 700
+    direction = torch.zeros(dim)
+    direction[5] = 1.0
+
+    def run(hot_key, window):
+        k = torch.randn((context, kv_heads, dim), generator=torch.Generator().manual_seed(1)) * 0.1
+        v = torch.randn((context, kv_heads, dim), generator=torch.Generator().manual_seed(2))
+        k[hot_key, 0] = direction * 40.0
+        q = (direction * 40.0).repeat(1, heads, 1)
+        k_pages, v_pages, tables = paged([k.to(dtype)], [v.to(dtype)], page_size, 3, dtype)
+        q_stride = (heads + 2 * kv_heads) * dim
+        packed = torch.zeros((1, q_stride), dtype=dtype)
+        packed[:, :heads * dim] = q.reshape(1, -1).to(dtype)
+        positions = torch.tensor([context - 1], dtype=torch.int32, device=DEVICE)
+        seq = torch.zeros(1, dtype=torch.int32, device=DEVICE)
+        out = ops.attention_generic(packed.to(DEVICE), q_stride, k_pages, v_pages, tables, seq, positions, heads,
+                                    kv_heads, dim, 1.0, window)
+        return out.float().cpu().view(heads, dim), v.to(dtype).float()
+
+    for hot in (3, 15, 16, 687, 699):
+        out, v = run(hot, 0)
+        assert torch.allclose(out[0], v[hot, 0], atol=2e-2), f"key {hot} was not found"
+    window = 100
+    out, v = run(context - window, window)          # first key inside the window
+    assert torch.allclose(out[1], v[context - window, 0], atol=2e-2)
+    out, v = run(context - window - 1, window)      # last key outside the window
+    assert not torch.allclose(out[1], v[context - window - 1, 0], atol=0.2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,dim,page_size,qk_norm", [(4, 2, 16, 4, True), (6, 1, 48, 16, True),
+                                                                  (8, 8, 128, 16, False), (5, 5, 80, 3, True)])
+def test_qk_norm_rope_kv_write(dtype, heads, kv_heads, dim, page_size, qk_norm):
+    from llmserver_b200 import ops
+    starts, counts = [130, 0, 77], [1, 19, 6]
+    theta, eps = 50000.0, 1e-5
+    total = sum(counts)
+    width = (heads + 2 * kv_heads) * dim
+    qkv = rand((total, width), dtype, 50)
+    q_weight = rand((dim,), dtype, 51) + 1 if qk_norm else None
+    k_weight = rand((dim,), dtype, 52) + 1 if qk_norm else None
+    positions = torch.cat([torch.arange(s, s + c) for s, c in zip(starts, counts)])
+    seq_of_token = torch.cat([torch.full((c,), i) for i, c in enumerate(counts)])
+    pages_per_seq = [-(-(s + c) // page_size) for s, c in zip(starts, counts)]
+    n_pages = sum(pages_per_seq) + 2
+    order = torch.randperm(n_pages, generator=torch.Generator().manual_seed(4)).tolist()
+    tables = torch.zeros((3, max(pages_per_seq)), dtype=torch.int32)
+    for row, count in enumerate(pages_per_seq):
+        for block in range(count):
+            tables[row, block] = order.pop()
+    k_pages = torch.zeros((n_pages, kv_heads, page_size, dim), dtype=dtype, device=DEVICE)
+    v_pages = torch.zeros_like(k_pages)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEVICE)
+    inv_freq = (1.0 / (theta ** (torch.arange(0, dim, 2).float() / dim))).to(DEVICE)
+    work = qkv.clone()
+    ops.qk_norm_rope_kv_write(work, q_weight, k_weight, inv_freq, positions.to(torch.int32).to(DEVICE),
+                              seq_of_token.to(torch.int32).to(DEVICE), tables.to(DEVICE), k_pages, v_pages, heads,
+                              kv_heads, dim, eps, True, flag)
+    assert flag.item() == 0
+    source = qkv.double().cpu()
+    q = source[:, :heads * dim].view(total, heads, dim)
+    k = source[:, heads * dim:(heads + kv_heads) * dim].view(total, kv_heads, dim)
+    v = source[:, (heads + kv_heads) * dim:].view(total, kv_heads, dim)
+    if qk_norm:
+        q = plain_model.rms_norm(q, q_weight.double().cpu(), eps)
+        k = plain_model.rms_norm(k, k_weight.double().cpu(), eps)
+    cosine, sine = plain_model.rope_tables(positions, dim, theta, torch.float64)
+    q, k = plain_model.apply_rope(q, cosine, sine), plain_model.apply_rope(k, cosine, sine)
+    close(work[:, :heads * dim], q.reshape(total, -1), dtype, "rotated q")
+    got_k = torch.stack([k_pages[tables[s, p // page_size].item(), :, p % page_size]
+                         for s, p in zip(seq_of_token.tolist(), positions.tolist())])
+    got_v = torch.stack([v_pages[tables[s, p // page_size].item(), :, p % page_size]
+                         for s, p in zip(seq_of_token.tolist(), positions.tolist())])
+    close(got_k, k, dtype, "cached k")
+    assert torch.equal(got_v.cpu(), qkv[:, (heads + kv_heads) * dim:].view(total, kv_heads, dim).cpu()), "cached v is a copy"
+    written = (k_pages.float().abs().sum(dim=(1, 3)) > 0).sum().item()
+    assert written == total, "slots other than the tokens' own were written"
+    # an entry that reads another entry's cache rotates q and leaves the pages alone
+    before = k_pages.clone()
+    again = qkv.clone()
+    ops.qk_norm_rope_kv_write(again, q_weight, k_weight, inv_freq, positions.to(torch.int32).to(DEVICE),
+                              seq_of_token.to(torch.int32).to(DEVICE), tables.to(DEVICE), k_pages, v_pages, heads,
+                              kv_heads, dim, eps, False, flag)
+    assert torch.equal(before, k_pages) and torch.equal(again[:, :heads * dim], work[:, :heads * dim])
+
+
+def test_sampling_greedy_and_temperature():
+    from llmserver_b200 import ops
+    vocab = 5003
+    logits = rand((6, vocab), torch.float32, 60, 2.0)
+    logits[2, 77] = logits[2, 4000] = logits[2].max() + 1.0   # a tie: the lower index wins
+    tokens = ops.sample(logits).cpu()
+    assert tokens.tolist() == torch.argmax(logits.cpu(), dim=-1).tolist()
+    assert tokens[2].item() == 77
+    temperatures = torch.tensor([0.8, 0.0, 1.5, 0.8, 0.3, 1.0], dtype=torch.float32, device=DEVICE)
+    seeds = torch.tensor([1, 2, 3, 1, 2 ** 40 + 5, 7], dtype=torch.int64, device=DEVICE)
+    steps = torch.tensor([0, 0, 5, 1, 9, 1000], dtype=torch.int32, device=DEVICE)
+    drawn = ops.sample(logits, temperatures, seeds, steps).cpu().tolist()
+    again = ops.sample(logits[[3, 0]].contiguous(), temperatures[[3, 0]].contiguous(), seeds[[3, 0]].contiguous(),
+                       steps[[3, 0]].contiguous()).cpu().tolist()
+    assert again == [drawn[3], drawn[0]], "a row's draw depends on its place in the batch"
+    host = logits.cpu()
+    for row, token in enumerate(drawn):
+        if temperatures[row].item() == 0.0:
+            assert token == int(torch.argmax(host[row]))
+            continue
+        scores = plain_model.gumbel_scores(host[row], temperatures[row].item(), int(seeds[row]), int(steps[row]))
+        assert scores[token] >= scores.max() - 1e-4, f"row {row}: token {token} is not the Gumbel-max choice"
+    assert drawn[0] != drawn[3] or True  # different steps usually differ; not required
+
+
+def test_sampling_follows_the_distribution():
+    from llmserver_b200 import ops
+    probabilities = torch.tensor([0.5, 0.25, 0.125, 0.125])
+    draws = 4000
+    logits = probabilities.log().repeat(draws, 1).to(DEVICE).contiguous()
+    temperatures = torch.ones(draws, device=DEVICE)
+    seeds = torch.full((draws,), 12345, dtype=torch.int64, device=DEVICE)
+    steps = torch.arange(draws, dtype=torch.int32, device=DEVICE)
+    tokens = ops.sample(logits, temperatures, seeds, steps).cpu()
+    observed = torch.bincount(tokens.long(), minlength=4).double() / draws
+    assert (observed - probabilities.double()).abs().max() < 4 * math.sqrt(0.25 / draws)
