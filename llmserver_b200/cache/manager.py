@@ -267,6 +267,23 @@ class CacheManager:
         self.requests[request_id] = covered
         return covered
 
+    def probe_prefix(self, prompt: Sequence[int]):
+        """What ``share_prefix`` would do, without doing it: (tokens covered, how many of the pages
+        taken are idle now and would stop counting as available)."""
+        if not self.prefix_sharing or not self.groups:
+            return 0, 0
+        pool = self.groups[0].pool
+        parent, covered, idle = "root", 0, 0
+        for block in range((len(prompt) - 1) // self.page_size):
+            digest = self.block_digest(parent, prompt[block * self.page_size:(block + 1) * self.page_size])
+            page = pool.lookup(digest)
+            if page is None:
+                break
+            idle += page in pool.idle
+            covered += self.page_size
+            parent = digest
+        return covered, idle
+
     def register_prefix(self, request_id, prompt: Sequence[int], old_computed: int, new_computed: int) -> None:
         """Hashes the prompt blocks completed by the step that moved the request from ``old_computed``
         to ``new_computed`` tokens (utils/engine.py:382-401)."""

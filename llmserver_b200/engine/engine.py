@@ -1,0 +1,243 @@
+"""The engine: request intake, scheduling, the mixed step, sampling, stopping and freeing.
+
+Python entry point in the manner of the reference's ``Engine`` (utils/engine.py:46-475): the same
+constructor names where they apply (``max_new_tokens``, ``max_batch_size``, ``max_num_batched_tokens``,
+``prefill_chunk_size``, ``kv_cache_num_blocks``, ``kv_cache_block_size``, ``ignore_eos``,
+``cuda_graphs``), ``add_request`` / ``step`` / ``cancel_request``, requests that carry
+``generated_token_ids``.  It is a token-id engine: prompts come as ids, nothing is tokenised.
+
+What differs by design: one step is ONE forward over decode tokens and prompt portions together
+(the reference runs them as separate forwards, utils/engine.py:437-443); sampling is a kernel that
+does greedy and seeded temperature sampling (the reference: argmax only, utils/engine.py:295-297).
+
+When pages run out (decided in ``schedule_step``, as utils/engine.py:418-435): the plan is checked
+against the pages available in every cache group; if it does not fit, the running request with the
+fewest preemptions and the least waiting is preempted (its pages freed, itself put at the back of
+the waiting queue, to be recomputed) and planning is repeated; a lone running request that does not
+fit raises ``KVCacheExhaustedError``.
+"""
+from __future__ import annotations
+
+import itertools
+from dataclasses import dataclass
+from typing import Dict, Iterable, List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..cache import CacheManager, KVCacheExhaustedError
+from .request import Request, RequestFinishReason, RequestStatus
+from .scheduler import PageBudget, Scheduler, SchedulerOutput
+from .step import StepFunction
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 0.0
+    seed: Optional[int] = None
+    max_new_tokens: Optional[int] = None
+    ignore_eos: Optional[bool] = None
+
+
+class Engine:
+    def __init__(self, model, max_new_tokens: int = 128, max_batch_size: int = 8, max_num_batched_tokens: int = 8192,
+                 prefill_chunk_size: Optional[int] = None, kv_cache_num_blocks: Optional[int] = None,
+                 kv_cache_block_size: int = 16, ignore_eos: bool = False, cuda_graphs: Optional[bool] = None,
+                 prefix_caching: bool = True, eos_token_ids: Optional[Iterable[int]] = None, dtype="bfloat16",
+                 device="cuda:0", max_context: Optional[int] = None):
+        """``model``: a model folder (config.json + model.safetensors) or a loaded ``DecoderModel``.
+
+        ``kv_cache_num_blocks`` defaults to the reference benchmark's sizing rule
+        (benchmark_cuda.py:107-111): max_batch_size * ceil(max_context / block_size) + 8 pages."""
+        if isinstance(model, str):
+            from ..models import load_model
+            model = load_model(model, dtype, device)
+        if max_new_tokens <= 0:
+            raise ValueError(f"max_new_tokens is <= 0: {max_new_tokens}")
+        self.model = model
+        self.device, self.dtype = model.runtime.device, model.runtime.dtype
+        self.max_new_tokens = max_new_tokens
+        self.ignore_eos = ignore_eos
+        self.block_size = kv_cache_block_size
+        self.scheduler = Scheduler(max_batch_size, max_num_batched_tokens, prefill_chunk_size)
+        if max_context is None:
+            max_context = model.spec.max_positions or 4096
+        if kv_cache_num_blocks is None:
+            kv_cache_num_blocks = max_batch_size * -(-max_context // kv_cache_block_size) + 8
+        self.num_blocks = kv_cache_num_blocks
+        self.cache = CacheManager(model.cache_needs(), kv_cache_block_size, kv_cache_num_blocks,
+                                  num_slots=max_batch_size, prefix_sharing=prefix_caching,
+                                  model_identity=model.spec.architecture)
+        self.cache.materialize(self.device, self.dtype)
+        self.step_function = StepFunction(model, self.cache)
+        self.budget = PageBudget(self.cache)
+        self.eos_token_ids = set(model.spec.eos_token_ids if eos_token_ids is None else eos_token_ids)
+        self.active_requests: Dict[str, Request] = {}
+        self.finished_requests: Dict[str, Request] = {}
+        self._ids = itertools.count()
+        self.cuda_graphs = bool(cuda_graphs) if cuda_graphs is not None else False
+        self.stats = {"steps": 0, "preemptions": 0, "tokens": 0, "prefill_tokens": 0, "decode_tokens": 0}
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt=None, prompt_token_ids: Optional[Sequence[int]] = None,
+                    max_new_tokens: Optional[int] = None, temperature: float = 0.0, seed: Optional[int] = None,
+                    ignore_eos: Optional[bool] = None) -> Request:
+        """Queues a request.  ``prompt`` exists for signature parity with the reference
+        (utils/engine.py:210) and must be None or a sequence of ids: text needs a tokenizer, which
+        this engine does not have."""
+        if prompt_token_ids is None:
+            if prompt is None or isinstance(prompt, str):
+                raise ValueError("pass prompt_token_ids: this engine takes token ids, not text")
+            prompt_token_ids = prompt
+        prompt_token_ids = [int(token) for token in prompt_token_ids]
+        if not prompt_token_ids:
+            raise ValueError("prompt_token_ids must not be empty")
+        vocab = self.model.spec.vocab_size
+        for token in prompt_token_ids:
+            if not 0 <= token < vocab:
+                raise ValueError(f"token id {token} is outside the vocabulary of {vocab}")
+        limit = self.model.spec.max_positions
+        budget = max_new_tokens or self.max_new_tokens
+        if limit is not None and len(prompt_token_ids) + budget > limit + 1:
+            raise ValueError(f"prompt of {len(prompt_token_ids)} tokens plus {budget} new tokens exceeds max_position_embeddings {limit}")
+        index = next(self._ids)
+        request = Request(f"req-{index}", prompt_token_ids, budget, temperature,
+                          seed if seed is not None else index, self.ignore_eos if ignore_eos is None else ignore_eos)
+        self.active_requests[request.request_id] = request
+        self.scheduler.waiting.append(request)
+        return request
+
+    def cancel_request(self, request_id: str) -> bool:
+        request = self.active_requests.get(request_id)
+        if request is None or request.status in (RequestStatus.FINISHED, RequestStatus.CANCELLED):
+            return False
+        if request in self.scheduler.waiting:
+            self.scheduler.waiting.remove(request)
+        if request in self.scheduler.running:
+            self.scheduler.running.remove(request)
+        request.cancel()
+        self._release(request)
+        self._archive(request)
+        return True
+
+    def _release(self, request: Request) -> None:
+        if self.cache.is_admitted(request.request_id):
+            self.step_function.release(request.request_id)
+
+    def _archive(self, request: Request) -> None:
+        self.active_requests.pop(request.request_id, None)
+        self.finished_requests[request.request_id] = request
+        while len(self.finished_requests) > 1000:   # utils/engine.py:47 max_completed_requests
+            self.finished_requests.pop(next(iter(self.finished_requests)))
+
+    # ------------------------------------------------------------------ scheduling
+    def _probe_waiting_prefixes(self) -> None:
+        """Sets ``num_computed_tokens`` of waiting requests to what a shared prefix would cover, so the
+        plan counts only the tokens that need computing (the reference looks prefixes up when the
+        request is added, utils/engine.py:197-208,226; here it happens as late as possible)."""
+        if not self.cache.prefix_sharing:
+            return
+        for request in itertools.islice(self.scheduler.waiting, self.scheduler.max_batch_size):
+            request.num_computed_tokens, request.prefix_idle_pages = self.cache.probe_prefix(request.prefill_token_ids)
+
+    def preempt_request(self, request: Request) -> None:
+        self._release(request)
+        self.scheduler.running.remove(request)
+        request.preempt_for_compute()
+        self.scheduler.waiting.append(request)
+        self.stats["preemptions"] += 1
+
+    def schedule_step(self) -> SchedulerOutput:
+        while True:
+            self._probe_waiting_prefixes()
+            out = self.scheduler.plan(self.budget)
+            if all(need <= have for need, have in zip(out.pages_needed, self.cache.available())):
+                for request in self.scheduler.commit(out):
+                    covered = self.step_function.admit(request.request_id, request.prefill_token_ids)
+                    request.num_computed_tokens = covered
+                return out
+            if len(self.scheduler.running) <= 1:
+                raise KVCacheExhaustedError(f"Required pages {out.pages_needed} exceed the pages available {self.cache.available()}")
+            candidates = [request for request in reversed(self.scheduler.running)
+                          if any(self.cache.table(request.request_id, group) for group in range(len(self.cache.groups)))]
+            if not candidates:
+                raise KVCacheExhaustedError(f"Required pages {out.pages_needed} exceed the pages available {self.cache.available()}")
+            victim = sorted(candidates, key=lambda request: (request.preemption_count, request.waiting_steps))[0]
+            self.preempt_request(victim)
+
+    # ------------------------------------------------------------------ the step
+    def step(self) -> bool:
+        """Plans and runs one mixed step; returns whether work is left."""
+        if not (self.scheduler.waiting or self.scheduler.running):
+            return False
+        out = self.schedule_step()
+        entries, sampled = [], []     # sampled: requests that get a token from this step, in row order
+        for request in out.decode_requests:
+            entries.append((request.request_id, [request.generated_token_ids[-1]], [0]))
+            sampled.append(request)
+        finishing = []
+        for request, count in zip(out.prefill_requests, out.prefill_token_counts):
+            start = request.num_computed_tokens
+            tokens = request.prefill_token_ids[start:start + count]
+            done = start + count == len(request.prefill_token_ids)
+            wants = done and not request.needs_decode_resume   # utils/engine.py:380
+            entries.append((request.request_id, tokens, [count - 1] if wants else []))
+            if wants:
+                sampled.append(request)
+            finishing.append(done)
+        logits = self.step_function.run(entries)
+        tokens = self._sample(logits, sampled) if sampled else []
+        self.stats["steps"] += 1
+        self.stats["decode_tokens"] += len(out.decode_requests)
+        self.stats["prefill_tokens"] += sum(out.prefill_token_counts)
+        for request in out.decode_requests:
+            request.complete_decode()
+        for request, count, done in zip(out.prefill_requests, out.prefill_token_counts, finishing):
+            old = request.num_computed_tokens
+            request.advance_prefill(count)
+            self.cache.register_prefix(request.request_id, request.prompt_token_ids, old, request.num_computed_tokens)
+            if done:
+                request.complete_prefill()
+        for request, token in zip(sampled, tokens):
+            self._accept(request, token)
+        self.scheduler.running[:] = [request for request in self.scheduler.running
+                                     if request.status not in (RequestStatus.FINISHED, RequestStatus.CANCELLED)]
+        return bool(self.scheduler.waiting or self.scheduler.running)
+
+    def _sample(self, logits: torch.Tensor, requests: List[Request]) -> List[int]:
+        """One kernel for the whole step and the step's only device-to-host read
+        (utils/engine.py:295-297 reads the argmax the same way)."""
+        if any(request.temperature > 0 for request in requests):
+            host = torch.tensor([[request.temperature for request in requests]], dtype=torch.float32)
+            temperatures = host.to(self.device, non_blocking=True).view(-1)
+            seeds = torch.tensor([request.seed for request in requests], dtype=torch.int64).to(self.device, non_blocking=True)
+            steps = torch.tensor([len(request.generated_token_ids) for request in requests], dtype=torch.int32).to(self.device, non_blocking=True)
+            tokens = ops.sample(logits, temperatures, seeds, steps)
+        else:
+            tokens = ops.sample(logits)
+        result = tokens.tolist()
+        self.step_function.check_errors()
+        return result
+
+    def _accept(self, request: Request, token: int) -> None:
+        request.append_generated_token(token)
+        self.stats["tokens"] += 1
+        if token in self.eos_token_ids and not request.ignore_eos:
+            request.finish(RequestFinishReason.EOS)
+        elif len(request.generated_token_ids) >= request.max_new_tokens:
+            request.finish(RequestFinishReason.LENGTH)
+        else:
+            return
+        self._release(request)
+        self._archive(request)
+
+    # ------------------------------------------------------------------ convenience
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: Optional[int] = None, temperature: float = 0.0,
+                 seed: Optional[int] = None, ignore_eos: Optional[bool] = None) -> List[List[int]]:
+        """Runs the given prompts (lists of token ids) to completion; returns the generated ids."""
+        requests = [self.add_request(prompt_token_ids=prompt, max_new_tokens=max_new_tokens, temperature=temperature,
+                                     seed=None if seed is None else seed + index, ignore_eos=ignore_eos)
+                    for index, prompt in enumerate(prompts)]
+        while self.step():
+            pass
+        return [request.generated_token_ids for request in requests]
