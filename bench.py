@@ -1,0 +1,309 @@
+#!/usr/bin/env python3
+"""Headline benchmark: decode tokens per second of the Qwen3-8B shape on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B]
+
+One "step" is one decode step of the whole batch.  The default run builds the 8B shape (36 layers,
+width 4096, 32/8 heads of 128, intermediate 12288, vocabulary 151936) with seeded random bfloat16
+weights, puts ``--batch`` requests (default 8) at a context whose mean over the timed steps is 3072
+(2048-token prompts decoded to 4096), and times K decode steps with CUDA events after W warm-up steps.
+It prints ONE JSON line: ``value`` is decoded tokens per second on the device, ``e2e`` the same through
+``llmserver_b200.Engine`` with host token ids in and sampled ids out, ``prefill`` a 2048-token prompt
+in one step, ``roofline`` the decode step's bytes over its time against the measured copy bandwidth,
+``points`` decode at batch 1 and 64.  Inputs larger than L2: every step streams all weights (16 GB).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936, hidden_size=4096,
+                intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,
+                head_dim=128, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                max_position_embeddings=40960, hidden_act="silu", attention_bias=False, use_sliding_window=False)
+CONTEXT = 4096          # prompts of 2048 tokens decoded to 4096
+PROMPT = 2048
+MEAN_DECODE_CONTEXT = (CONTEXT + PROMPT) // 2
+PAGE_SIZE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as handle:
+                raw = json.load(handle)
+            peaks = {key: float(raw[key]) for key in FALLBACK_PEAKS if key in raw}
+            if "hbm_gbs" in peaks and "bf16_tflops" in peaks:
+                peaks.setdefault("bf16_tflops_sustained", peaks["bf16_tflops"])
+                return peaks, "measured"
+        except (OSError, ValueError, KeyError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons through NVML while the timed region runs (reads only)."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index: int = 0, period: float = 0.1):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.period, self.index = period, index
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:  # NVML missing: report nothing rather than fail the benchmark
+            self.nvml = None
+
+    def _loop(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM))
+                mask = self.nvml.nvmlDeviceGetCurrentClocksEventReasons(self.handle) if hasattr(
+                    self.nvml, "nvmlDeviceGetCurrentClocksEventReasons") else self.nvml.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nvml is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        ordered = sorted(self.samples)
+        return {"sm_mhz": ordered[len(ordered) // 2] if ordered else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons)}
+
+
+def decode_bytes(config, layers: int, batch: int, context: int) -> float:
+    """Bytes one decode step has to read: every weight it uses once, and the cache of the live requests."""
+    hidden, inter, dim = config.hidden_size, config.intermediate_size, config.head_dim
+    heads, kv_heads = config.num_attention_heads, config.num_key_value_heads
+    per_layer = ((heads + 2 * kv_heads) * dim * hidden + hidden * heads * dim + 3 * hidden * inter + 2 * hidden + 2 * dim) * 2
+    head = config.vocab_size * hidden * 2
+    cache = 2 * kv_heads * dim * 2 * layers * batch * context
+    return layers * per_layer + head + hidden * 2 + cache
+
+
+def prefill_flops(config, layers: int, tokens: int) -> float:
+    hidden, inter, dim = config.hidden_size, config.intermediate_size, config.head_dim
+    heads, kv_heads = config.num_attention_heads, config.num_key_value_heads
+    linear = 2 * tokens * ((heads + 2 * kv_heads) * dim * hidden + hidden * heads * dim + 3 * hidden * inter)
+    attention = 2 * 2 * heads * dim * tokens * (tokens + 1) / 2      # QK^T and PV over the causal half
+    return layers * (linear + attention) + 2 * config.vocab_size * hidden   # logits of the last token only
+
+
+class Harness:
+    """Model, cache and step function sized for the largest batch, reused by every measurement."""
+
+    def __init__(self, layers: int, max_batch: int, seed: int = 0):
+        import torch
+        from llmserver_b200.cache import CacheManager
+        from llmserver_b200.config import Qwen3Config
+        from llmserver_b200.engine.step import StepFunction
+        from llmserver_b200.models import random_model
+
+        self.torch = torch
+        raw = dict(QWEN3_8B, num_hidden_layers=layers)
+        self.config = Qwen3Config.from_dict(raw)
+        self.layers = layers
+        self.model = random_model(self.config, seed, "bfloat16", "cuda:0")
+        pages = max_batch * (CONTEXT // PAGE_SIZE) + 8     # the reference benchmark's sizing rule
+        self.cache = CacheManager(self.model.cache_needs(), PAGE_SIZE, pages, num_slots=max_batch, prefix_sharing=False)
+        self.cache.materialize(self.model.runtime.device, self.model.runtime.dtype)
+        for group in self.cache.groups:     # contents do not change the timing; avoid an all-zero cache anyway
+            group.storage.normal_(0.0, 0.5)
+        self.step_function = StepFunction(self.model, self.cache)
+        self.generator = torch.Generator().manual_seed(seed)
+
+    def tokens(self, count: int):
+        return self.torch.randint(0, self.config.vocab_size, (count,), generator=self.generator).tolist()
+
+    def place(self, batch: int, context: int):
+        """Puts ``batch`` requests at ``context`` cached tokens each (pages allocated, contents as they are)."""
+        for request_id in list(self.step_function.computed):
+            self.step_function.release(request_id)
+        ids = [f"b{index}" for index in range(batch)]
+        for request_id in ids:
+            self.step_function.admit(request_id)
+            self.cache.ensure(request_id, context)
+            self.step_function.computed[request_id] = context
+        return ids
+
+    def time_decode(self, batch: int, steps: int, warmup: int):
+        torch = self.torch
+        from llmserver_b200 import ops
+        start_context = max(1, MEAN_DECODE_CONTEXT - steps // 2 - warmup)
+        ids = self.place(batch, start_context)
+        tokens = self.tokens(batch)
+        events = []
+        launches_before = None
+        for step in range(warmup + steps):
+            if step == warmup:
+                torch.cuda.synchronize()
+                launches_before = ops.launch_count()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            logits = self.step_function.run([(request_id, [token], [0]) for request_id, token in zip(ids, tokens)])
+            sampled = ops.sample(logits)
+            end.record()
+            if step >= warmup:
+                events.append((begin, end))
+            tokens = sampled.tolist()      # the next step's inputs are this step's outputs
+        torch.cuda.synchronize()
+        launches = ops.launch_count() - launches_before
+        self.step_function.check_errors()
+        times = [begin.elapsed_time(end) for begin, end in events]
+        total_ms = sum(times)
+        mean_context = start_context + warmup + (steps + 1) / 2
+        return {"ms_per_step": total_ms / steps, "tokens_per_s": batch * steps / (total_ms / 1e3),
+                "launches": launches, "mean_context": mean_context}
+
+    def time_prefill(self, tokens: int, repeats: int = 3):
+        torch = self.torch
+        best = None
+        for _ in range(repeats + 1):     # the first run warms up
+            for request_id in list(self.step_function.computed):
+                self.step_function.release(request_id)
+            self.step_function.admit("p")
+            prompt = self.tokens(tokens)
+            torch.cuda.synchronize()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            self.step_function.run([("p", prompt, [tokens - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            elapsed = begin.elapsed_time(end)
+            best = elapsed if best is None else min(best, elapsed)
+        self.step_function.release("p")
+        return best
+
+    def time_e2e(self, batch: int, steps: int, warmup: int):
+        """The same decode through the public entry point: host token ids in, sampled ids out; every
+        step copies its batch from pinned host memory and reads the sampled tokens back."""
+        torch = self.torch
+        from llmserver_b200.engine.engine import Engine
+        from llmserver_b200.engine.request import RequestStatus
+
+        for request_id in list(self.step_function.computed):
+            self.step_function.release(request_id)
+        prompt_len = max(1, MEAN_DECODE_CONTEXT - steps // 2 - warmup)
+        # the engine shares the model and the cache that are already on the device
+        engine = Engine(self.model, max_new_tokens=warmup + steps + 2, max_batch_size=batch,
+                        max_num_batched_tokens=max(8192, batch), ignore_eos=True, cache=self.cache,
+                        step_function=self.step_function)
+        requests = [engine.add_request(prompt_token_ids=self.tokens(prompt_len)) for _ in range(batch)]
+        while any(request.status != RequestStatus.DECODING for request in requests):
+            engine.step()
+        for _ in range(warmup):
+            engine.step()
+        torch.cuda.synchronize()
+        started = time.perf_counter()
+        for _ in range(steps):
+            engine.step()
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - started
+        h2d = engine.step_function.last_batch_bytes
+        for request in requests:
+            engine.cancel_request(request.request_id)
+        return {"value": batch * steps / elapsed, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": batch * 4, "ms_per_step": elapsed * 1e3 / steps}
+
+
+def reference_arm():
+    line = {"impl": "reference",
+            "unavailable": "AshvinSehgal/LLMServer has no setup.py or pyproject.toml, so pip cannot install it into baseline/_ref; "
+                           "its job files also exclude compute capability >= 10 and it needs Hugging Face weights from the network"}
+    print(json.dumps(line))
+    return 0
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"],
+                        help="fewer layers than the 8B shape's 36 (layer sizes stay); the record names both numbers")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (the engine has no multi-GPU path)")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    import torch
+
+    os.environ["PATH"] = os.path.dirname(sys.executable) + os.pathsep + os.environ.get("PATH", "")
+    peaks, peak_source = read_peaks()
+    harness = Harness(args.layers, max(args.batch, 1 if args.skip_points else 64))
+    config = harness.config
+    harness.time_decode(args.batch, 4, 3)      # untimed: lets the library choose its kernels
+    with ClockSampler() as clocks:
+        main_run = harness.time_decode(args.batch, args.steps, args.warmup)
+    points = {}
+    if not args.skip_points:
+        for batch in (1, 64):
+            if batch == args.batch:
+                points[f"decode_b{batch}"] = round(main_run["tokens_per_s"], 1)
+                continue
+            points[f"decode_b{batch}"] = round(harness.time_decode(batch, min(args.steps, 32), 3)["tokens_per_s"], 1)
+    prefill_ms = harness.time_prefill(PROMPT)
+    flops = prefill_flops(config, args.layers, PROMPT)
+    e2e = harness.time_e2e(args.batch, args.steps, args.warmup)
+    bytes_per_step = decode_bytes(config, args.layers, args.batch, main_run["mean_context"])
+    achieved = bytes_per_step / (main_run["ms_per_step"] / 1e3) / 1e9
+    line = {
+        "metric": "decode tok/s (Qwen3-8B shape, batch 8, context 4096)", "value": round(main_run["tokens_per_s"], 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic: seeded random weights N(0,0.02), uniform random token ids",
+        "config": {"model": "Qwen3-8B shape", "layers": args.layers, "layers_full": QWEN3_8B["num_hidden_layers"],
+                   "hidden": config.hidden_size, "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,
+                   "head_dim": config.head_dim, "intermediate": config.intermediate_size, "vocab": config.vocab_size,
+                   "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT,
+                   "decode_context_mean": round(main_run["mean_context"]), "page_size": PAGE_SIZE, "parallelism": "none (1 GPU)",
+                   "l2": "inputs larger than L2: each step streams all weights", "peaks": peak_source},
+        "clocks": clocks.summary(),
+        "e2e": {key: (round(value, 1) if isinstance(value, float) else value) for key, value in e2e.items()},
+        "gpu_launches": main_run["launches"],
+        "prefill": {"value": round(PROMPT / (prefill_ms / 1e3), 1), "tokens": PROMPT, "ms": round(prefill_ms, 3),
+                    "frac": round(flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

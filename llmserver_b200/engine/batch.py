@@ -52,6 +52,7 @@ class StepBatch:
     max_q_len: int = 0
     max_context: int = 0
     decode_only: bool = False
+    host_bytes: int = 0
     scratch: dict = field(default_factory=dict)   # per-step data kernels' wrappers derive once
 
 
@@ -132,5 +133,5 @@ def build_batch(slices: List[SequenceSlice], n_groups: int, device, vocab_size: 
                       for width, offset in zip(widths, table_offsets)],
         error_flag=buffer[flag_offset:flag_offset + 1],
         q_lens=q_lens, context_lens=context_len, max_q_len=max(q_lens), max_context=max(context_len),
-        decode_only=all(length == 1 for length in q_lens),
+        decode_only=all(length == 1 for length in q_lens), host_bytes=total * 4,
     )

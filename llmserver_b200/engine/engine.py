@@ -44,7 +44,8 @@ class Engine:
                  prefill_chunk_size: Optional[int] = None, kv_cache_num_blocks: Optional[int] = None,
                  kv_cache_block_size: int = 16, ignore_eos: bool = False, cuda_graphs: Optional[bool] = None,
                  prefix_caching: bool = True, eos_token_ids: Optional[Iterable[int]] = None, dtype="bfloat16",
-                 device="cuda:0", max_context: Optional[int] = None):
+                 device="cuda:0", max_context: Optional[int] = None, cache: Optional[CacheManager] = None,
+                 step_function: Optional[StepFunction] = None):
         """``model``: a model folder (config.json + model.safetensors) or a loaded ``DecoderModel``.
 
         ``kv_cache_num_blocks`` defaults to the reference benchmark's sizing rule
@@ -64,12 +65,16 @@ class Engine:
             max_context = model.spec.max_positions or 4096
         if kv_cache_num_blocks is None:
             kv_cache_num_blocks = max_batch_size * -(-max_context // kv_cache_block_size) + 8
-        self.num_blocks = kv_cache_num_blocks
-        self.cache = CacheManager(model.cache_needs(), kv_cache_block_size, kv_cache_num_blocks,
-                                  num_slots=max_batch_size, prefix_sharing=prefix_caching,
-                                  model_identity=model.spec.architecture)
-        self.cache.materialize(self.device, self.dtype)
-        self.step_function = StepFunction(model, self.cache)
+        if cache is None:
+            cache = CacheManager(model.cache_needs(), kv_cache_block_size, kv_cache_num_blocks,
+                                 num_slots=max_batch_size, prefix_sharing=prefix_caching,
+                                 model_identity=model.spec.architecture)
+            cache.materialize(self.device, self.dtype)
+        # a cache (and step function) that already live on the device may be handed in and shared
+        self.cache = cache
+        self.block_size = cache.page_size
+        self.num_blocks = cache.groups[0].pool.num_pages if cache.groups else 0
+        self.step_function = step_function or StepFunction(model, self.cache)
         self.budget = PageBudget(self.cache)
         self.eos_token_ids = set(model.spec.eos_token_ids if eos_token_ids is None else eos_token_ids)
         self.active_requests: Dict[str, Request] = {}

@@ -26,6 +26,7 @@ class StepFunction:
         model.bind_cache(cache)
         self.pending_flags: List[torch.Tensor] = []
         self.steps_run = 0
+        self.last_batch_bytes = 0   # size of the last step's host-to-device copy
 
     # ------------------------------------------------------------------ request lifetime
     def admit(self, request_id, prompt: Sequence[int] = None) -> int:
@@ -75,7 +76,9 @@ class StepFunction:
                 if piece.start + len(piece.tokens) > limit:
                     raise ValueError(f"request {piece.request_id!r} would reach {piece.start + len(piece.tokens)} tokens; "
                                      f"the model's max_position_embeddings is {limit}")
-        return build_batch(slices, len(self.cache.groups), self.device, self.model.spec.vocab_size)
+        batch = build_batch(slices, len(self.cache.groups), self.device, self.model.spec.vocab_size)
+        self.last_batch_bytes = batch.host_bytes
+        return batch
 
     def run(self, entries: List[StepEntry]) -> torch.Tensor:
         """Runs one step; returns logits [wanted, vocab] (float32) in the order of the entries and of

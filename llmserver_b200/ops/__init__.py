@@ -11,11 +11,11 @@ from typing import Optional
 
 import torch
 
-from .library import (KernelError, call, check, declare, dtype_code, library, pointer, require_device,
-                      stream_handle)
+from .library import (KernelError, call, check, declare, dtype_code, launch_count, library, pointer,
+                      require_device, stream_handle)
 
 __all__ = ["KernelError", "embedding", "add_rmsnorm", "rmsnorm", "silu_mul", "sample", "qk_norm_rope_kv_write",
-           "attention_generic", "gemm_f32", "linear", "require_device", "library"]
+           "attention_generic", "gemm_f32", "linear", "require_device", "library", "launch_count"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -79,7 +79,17 @@ def require_device() -> None:
     _arch_checked = True
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many of this package's kernel launchers have been called in this process."""
+    return _launches
+
+
 def call(name: str, *args) -> None:
+    global _launches
+    _launches += 1
     status = getattr(library(), name)(*args)
     if status != 0:
         raise KernelError(f"{name} failed ({status}): {library().llm_last_error().decode()}")
