@@ -24,8 +24,8 @@ from typing import Dict, Iterable, List, Optional, Sequence
 
 import torch
 
-from .. import ops
 from ..cache import CacheManager, KVCacheExhaustedError
+from ..sampling import Sampler, SamplingRow
 from .request import Request, RequestFinishReason, RequestStatus
 from .scheduler import PageBudget, Scheduler, SchedulerOutput
 from .step import StepFunction
@@ -45,7 +45,7 @@ class Engine:
                  kv_cache_block_size: int = 16, ignore_eos: bool = False, cuda_graphs: Optional[bool] = None,
                  prefix_caching: bool = True, eos_token_ids: Optional[Iterable[int]] = None, dtype="bfloat16",
                  device="cuda:0", max_context: Optional[int] = None, cache: Optional[CacheManager] = None,
-                 step_function: Optional[StepFunction] = None):
+                 step_function: Optional[StepFunction] = None, sampler=None):
         """``model``: a model folder (config.json + model.safetensors) or a loaded ``DecoderModel``.
 
         ``kv_cache_num_blocks`` defaults to the reference benchmark's sizing rule
@@ -76,6 +76,7 @@ class Engine:
         self.num_blocks = cache.groups[0].pool.num_pages if cache.groups else 0
         self.step_function = step_function or StepFunction(model, self.cache)
         self.budget = PageBudget(self.cache)
+        self.sampler = sampler or Sampler(self.device)
         self.eos_token_ids = set(model.spec.eos_token_ids if eos_token_ids is None else eos_token_ids)
         self.active_requests: Dict[str, Request] = {}
         self.finished_requests: Dict[str, Request] = {}
@@ -212,15 +213,8 @@ class Engine:
     def _sample(self, logits: torch.Tensor, requests: List[Request]) -> List[int]:
         """One kernel for the whole step and the step's only device-to-host read
         (utils/engine.py:295-297 reads the argmax the same way)."""
-        if any(request.temperature > 0 for request in requests):
-            host = torch.tensor([[request.temperature for request in requests]], dtype=torch.float32)
-            temperatures = host.to(self.device, non_blocking=True).view(-1)
-            seeds = torch.tensor([request.seed for request in requests], dtype=torch.int64).to(self.device, non_blocking=True)
-            steps = torch.tensor([len(request.generated_token_ids) for request in requests], dtype=torch.int32).to(self.device, non_blocking=True)
-            tokens = ops.sample(logits, temperatures, seeds, steps)
-        else:
-            tokens = ops.sample(logits)
-        result = tokens.tolist()
+        result = self.sampler(logits, [SamplingRow(request.temperature, request.seed, len(request.generated_token_ids))
+                                       for request in requests])
         self.step_function.check_errors()
         return result
 
