@@ -1,0 +1,129 @@
+"""Generation through the Python entry point on the GPU, against the plain implementation."""
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+from helpers import TOLERANCE, plain_folder, plain_logits, tokens_for
+from tiny_configs import TINY
+
+pytestmark = pytest.mark.gpu
+
+
+def plain_greedy(folder, prompt, count):
+    config, weights = plain_folder(folder)
+    tokens = list(prompt)
+    for _ in range(count):
+        tokens.append(plain_model.greedy(plain_model.forward(config, weights, tokens)[-1]))
+    return tokens[len(prompt):]
+
+
+def assert_tokens_are_argmax_of_plain(folder, prompt, generated, dtype, temperature=0.0, seed=0):
+    """Every generated token must (nearly) maximise the plain implementation's score for its own prefix:
+    logits for greedy, logits / T + Gumbel noise for sampling.  'Nearly' is the logit tolerance of the dtype."""
+    logits = plain_logits(folder, list(prompt) + list(generated))
+    for index, token in enumerate(generated):
+        row = torch.from_numpy(logits[len(prompt) - 1 + index])
+        slack = TOLERANCE[dtype] * row.abs().max().item() * 2
+        if temperature > 0:
+            scores = plain_model.gumbel_scores(row, temperature, seed, index)
+            slack /= temperature
+        else:
+            scores = row.double()
+        assert scores[token] >= scores.max() - slack, f"token {index} ({token}) is not the best choice"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_tiny_a_three_requests_greedy(tiny_folders, dtype):
+    """3 requests with prompts of 5 / 9 / 13 tokens, 8 greedy tokens each, pages of 4 tokens."""
+    from llmserver_b200 import Engine
+    folder = tiny_folders["a"]
+    prompts = [tokens_for(256, length, 50 + length) for length in (5, 9, 13)]
+    engine = Engine(folder, max_new_tokens=8, max_batch_size=4, max_num_batched_tokens=64, kv_cache_num_blocks=24,
+                    kv_cache_block_size=4, ignore_eos=True, dtype=dtype)
+    generated = engine.generate(prompts)
+    assert all(len(tokens) == 8 for tokens in generated)
+    for prompt, tokens in zip(prompts, generated):
+        assert_tokens_are_argmax_of_plain(folder, prompt, tokens, dtype)
+        if dtype == "float32":
+            assert tokens == plain_greedy(folder, prompt, 8)
+    engine.cache.check_invariants()
+    assert engine.cache.available() == [24]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_tiny_b_chunks_mixed_with_decode_shared_prefix_and_temperature(tiny_folders, dtype):
+    """4 requests with prompts of 1 / 7 / 17 / 37 tokens, the first 16 tokens shared by two of them,
+    prefilled in portions of 6 beside decoding requests, 12 tokens each at temperature 0.8, pages of 8."""
+    from llmserver_b200 import Engine
+    folder = tiny_folders["b"]
+    shared = tokens_for(509, 16, 1)
+    prompts = [tokens_for(509, 1, 2), tokens_for(509, 7, 3), shared + tokens_for(509, 1, 4), shared + tokens_for(509, 21, 5)]
+    engine = Engine(folder, max_new_tokens=12, max_batch_size=4, max_num_batched_tokens=16, prefill_chunk_size=6,
+                    kv_cache_num_blocks=40, kv_cache_block_size=8, ignore_eos=True, dtype=dtype)
+    requests = [engine.add_request(prompt_token_ids=prompt, temperature=0.8, seed=100 + index)
+                for index, prompt in enumerate(prompts[:3])]
+    # the fourth request arrives once the third one's prompt is in the cache, so it finds the shared pages
+    while requests[2].status.value != "Decoding":
+        engine.step()
+    requests.append(engine.add_request(prompt_token_ids=prompts[3], temperature=0.8, seed=103))
+    while engine.step():
+        pass
+    for index, (prompt, request) in enumerate(zip(prompts, requests)):
+        assert len(request.generated_token_ids) == 12
+        assert_tokens_are_argmax_of_plain(folder, prompt, request.generated_token_ids, dtype, 0.8, 100 + index)
+    # the second request with the shared beginning took the first one's two complete pages over
+    assert engine.stats["prefill_tokens"] == sum(len(p) for p in prompts) - 16
+    engine.cache.check_invariants()
+    # sampled tokens do not depend on the batch: each request alone gives the same tokens (32-bit logits
+    # are bit-identical however the work is cut)
+    if dtype == "float32":
+        for index, prompt in enumerate(prompts):
+            alone = Engine(engine.model, max_new_tokens=12, max_batch_size=1, max_num_batched_tokens=64,
+                           kv_cache_num_blocks=16, kv_cache_block_size=8, ignore_eos=True)
+            request = alone.add_request(prompt_token_ids=prompt, temperature=0.8, seed=100 + index)
+            while alone.step():
+                pass
+            assert request.generated_token_ids == requests[index].generated_token_ids
+
+
+def test_running_out_of_pages_preempts_and_changes_no_token(tiny_folders):
+    from llmserver_b200 import Engine
+    folder = tiny_folders["c"]
+    prompts = [tokens_for(301, length, 70 + length) for length in (30, 21, 44, 9)]
+    roomy = Engine(folder, max_new_tokens=40, max_batch_size=4, max_num_batched_tokens=32, kv_cache_num_blocks=128,
+                   kv_cache_block_size=4, ignore_eos=True, dtype="float32")
+    expected = roomy.generate(prompts)
+    assert roomy.stats["preemptions"] == 0
+    tight = Engine(roomy.model, max_new_tokens=40, max_batch_size=4, max_num_batched_tokens=32, kv_cache_num_blocks=48,
+                   kv_cache_block_size=4, ignore_eos=True)
+    assert tight.generate(prompts) == expected
+    assert tight.stats["preemptions"] > 0
+    tight.cache.check_invariants()
+    assert tight.cache.available() == [48, 48]
+    for prompt, tokens in zip(prompts, expected):
+        assert_tokens_are_argmax_of_plain(folder, prompt, tokens, "float32")
+
+
+def test_eos_stops_a_request(tiny_folders):
+    from llmserver_b200 import Engine
+    folder = tiny_folders["a"]
+    prompt = tokens_for(256, 6, 9)
+    free_run = plain_greedy(folder, prompt, 10)
+    engine = Engine(folder, max_new_tokens=10, max_batch_size=2, kv_cache_num_blocks=16, kv_cache_block_size=4,
+                    dtype="float32", eos_token_ids=[free_run[3]])
+    stop = free_run.index(free_run[3])
+    assert engine.generate([prompt]) == [free_run[:stop + 1]]
+
+
+def test_the_first_tokens_of_a_sequence(tiny_folders):
+    """Prompts of one and two tokens: the first positions have no history, pages are nearly empty."""
+    from llmserver_b200 import Engine
+    for name in ("a", "b", "c"):
+        folder = tiny_folders[name]
+        vocab = TINY[name][0]["vocab_size"]
+        engine = Engine(folder, max_new_tokens=5, max_batch_size=3, kv_cache_num_blocks=12, kv_cache_block_size=16,
+                        ignore_eos=True, dtype="float32")
+        prompts = [[vocab - 1], [0, 1], [5]]
+        for prompt, tokens in zip(prompts, engine.generate(prompts)):
+            assert tokens == plain_greedy(folder, prompt, 5)

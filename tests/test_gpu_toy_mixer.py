@@ -1,0 +1,144 @@
+"""A toy mixer with state of its own, defined here, is registered, built and stepped without a change
+to the framework's files: it keeps a decaying sum of its inputs per request in a state slot.  The model
+alternates it with the framework's attention, so pages and state slots are used side by side."""
+import pytest
+import torch
+
+import plain_model
+from helpers import assert_close, tokens_for
+
+pytestmark = pytest.mark.gpu
+DEVICE = torch.device("cuda:0")
+DECAY = 0.7
+
+
+def register_toy():
+    from llmserver_b200.cache import StateNeed
+    from llmserver_b200.parts import MIXERS, Mixer
+    from llmserver_b200.weights.declare import WeightDecl
+
+    @MIXERS.register("toy_decaying_sum")
+    class DecayingSum(Mixer):
+        """state <- decay * state + x_t ; out_t = state W^T.  State: one float32 [hidden] row per request."""
+
+        @classmethod
+        def declare_weights(cls, params):
+            return {"mix.weight": WeightDecl((params["hidden"], params["hidden"]))}
+
+        @classmethod
+        def cache_need(cls, params):
+            return StateNeed((params["hidden"],), "float32")
+
+        def __init__(self, params, weights, runtime):
+            super().__init__(params, weights, runtime)
+            self.weight, self.decay = weights["mix.weight"].float(), float(params["decay"])
+
+        def forward(self, x, batch, cache):
+            out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+            slots, begin = batch.state_slots.tolist(), 0
+            for slot, count in zip(slots, batch.q_lens):
+                state = cache.state[slot]
+                for row in range(begin, begin + count):
+                    state.mul_(self.decay).add_(x[row].float())
+                    out[row] = state @ self.weight.T
+                begin += count
+            return out.to(x.dtype)
+
+    return DecayingSum
+
+
+def toy_spec(hidden=48, vocab=120):
+    from llmserver_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    norm = PartSpec.of("rmsnorm", width=hidden, eps=1e-5)
+    block = PartSpec.of("pre_norm", mixer_prefix="mixer.", feed_forward_prefix="ffn.", mixer_norm_prefix="norm1.",
+                        feed_forward_norm_prefix="norm2.")
+    feed_forward = PartSpec.of("swiglu", hidden=hidden, intermediate=80)
+    attention = PartSpec.of("gqa_attention", hidden=hidden, heads=3, kv_heads=1, head_dim=16, scale=0.25, qk_norm=True,
+                            eps=1e-5, window=None)
+    toy = PartSpec.of("toy_decaying_sum", hidden=hidden, decay=DECAY)
+    layers = [LayerSpec(f"toy.layers.{i}.", block, mixer, feed_forward, norm, norm, "rotary" if mixer is attention else None)
+              for i, mixer in enumerate((attention, toy, attention))]
+    return ModelSpec(architecture="ToyForTests", vocab_size=vocab, hidden_size=hidden, layers=layers,
+                     schedule=[ScheduleEntry(i) for i in range(3)],
+                     positions={"rotary": PartSpec.of("rotary", head_dim=16, theta=10000.0)}, final_norm=norm,
+                     embedding_name="toy.embed.weight", final_norm_prefix="toy.norm.", head_name="toy.head.weight")
+
+
+class MovedSource:
+    """Random tensors drawn on the CPU (so the plain side sees the same values), moved to the device."""
+
+    def __init__(self, spec, seed, dtype):
+        from llmserver_b200.weights import RandomSource
+        self.inner, self.dtype = RandomSource(spec, seed, torch.float32, "cpu"), dtype
+        self.seen = {}
+
+    def get(self, name):
+        self.seen[name] = self.inner.get(name).to(self.dtype)
+        return self.seen[name].to(DEVICE)
+
+
+def plain_toy_forward(weights, tokens):
+    """Whole sequence, no cache: the same model written with the plain functions."""
+    w = {name: tensor.double() for name, tensor in weights.items()}
+    h = w["toy.embed.weight"][torch.tensor(tokens)]
+    cosine, sine = plain_model.rope_tables(torch.arange(len(tokens)), 16, 10000.0, torch.float64)
+    for index in range(3):
+        p = f"toy.layers.{index}."
+        normed = plain_model.rms_norm(h, w[p + "norm1.weight"], 1e-5)
+        if index == 1:
+            state, rows = torch.zeros(h.shape[1], dtype=torch.float64), []
+            for row in normed:
+                state = DECAY * state + row
+                rows.append(state @ w[p + "mixer.mix.weight"].T)
+            mixed = torch.stack(rows)
+        else:
+            layer = {"self_attn." + k[len(p + "mixer."):]: v for k, v in w.items() if k.startswith(p + "mixer.")}
+            q, k, v = plain_model.project_qkv(normed, layer, 3, 1, 16, 1e-5, cosine, sine)
+            mixed = plain_model.causal_attention(q, k, v, 0.25) @ layer["self_attn.o_proj.weight"].T
+        h = h + mixed
+        normed = plain_model.rms_norm(h, w[p + "norm2.weight"], 1e-5)
+        h = h + plain_model.swiglu_mlp(normed, {"mlp." + k[len(p + "ffn."):]: v for k, v in w.items() if k.startswith(p + "ffn.")})
+    return (plain_model.rms_norm(h, w["toy.norm.weight"], 1e-5) @ w["toy.head.weight"].T).numpy()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
+    from llmserver_b200.cache import CacheManager, StateNeed
+    from llmserver_b200.engine.step import StepFunction
+    from llmserver_b200.models import DecoderModel
+    from llmserver_b200.parts import Runtime
+
+    register_toy()
+    spec = toy_spec()
+    source = MovedSource(spec, 5, dtype)
+    model = DecoderModel(spec, source, Runtime(dtype, DEVICE))
+    needs = model.cache_needs()
+    assert isinstance(needs[1], StateNeed) and needs[1].shape == (48,)
+    cache = CacheManager(needs, 4, 40, num_slots=2, prefix_sharing=True)
+    assert not cache.prefix_sharing           # a mixer with state rules shared prefixes out
+    cache.materialize(DEVICE, dtype)
+    step = StepFunction(model, cache)
+    first, second = tokens_for(120, 37, 1), tokens_for(120, 22, 2)
+    want_first, want_second = plain_toy_forward(source.seen, first), plain_toy_forward(source.seen, second)
+    name = "float32" if dtype == torch.float32 else "bfloat16"
+    # two requests interleaved, cut differently, one of them ended and its slot reused
+    step.admit("x")
+    step.admit("y")
+    got_x = [step.run([("x", first[:20], list(range(20)))])]
+    both = step.run([("x", first[20:23], [0, 1, 2]), ("y", second[:9], list(range(9)))])
+    got_x.append(both[:3])
+    got_y = [both[3:]]
+    both = step.run([("y", second[9:10], [0]), ("x", first[23:], list(range(14)))])
+    got_y.append(both[:1])
+    got_x.append(both[1:])
+    step.release("x")
+    got_y.append(step.run([("y", second[10:], list(range(12)))]))
+    assert_close(torch.cat(got_x).cpu().numpy(), want_first, name, "toy model, request x")
+    assert_close(torch.cat(got_y).cpu().numpy(), want_second, name, "toy model, request y")
+    step.admit("z")                            # takes x's slot, which must start from zero again
+    again = step.run([("z", first, list(range(len(first))))])
+    assert_close(again.cpu().numpy(), want_first, name, "toy model, reused slot")
+    step.check_errors()
+    step.release("y")
+    step.release("z")
+    cache.check_invariants()
