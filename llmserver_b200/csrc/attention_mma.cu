@@ -1,0 +1,586 @@
+// bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16, 32-bit accumulation
+// and 32-bit online softmax), for head sizes 64 and 128, any number of heads and groups, any page size.
+//
+// Two kernels share one warp-level tile routine:
+//
+//   * portions (q_len > 1): one block per (sequence, kv head, 64-row tile).  "Rows" are (token, head of
+//     the group) pairs of one kv head, so the G query heads that share a kv head also share every K/V
+//     tile the block loads.  Four warps take 16 rows each and walk the sequence's keys in tiles of 64,
+//     from the first key the tile's window can see to the last token's own position (causal).
+//   * decode (q_len == 1): one block per (split of the keys, kv head, sequence).  The G heads are the
+//     rows (padded to 16); the four warps take 16 keys each of every 64-key tile, then merge.  With more
+//     than one split per sequence the partial results go to scratch memory and a second kernel merges
+//     them (split-KV, as the reference's paged decode: utils/paged_attention.py:168-237).
+//
+// K and V tiles travel global -> shared with cp.async (16-byte chunks, two stages), each key's page
+// looked up in the block table, so a page size is only a divisor here.  Shared tiles are XOR-swizzled by
+// 16-byte chunk so that ldmatrix reads are conflict-free.  Scores are S = Q K^T * scale with keys after
+// the query's position (and, with a window, keys at or before position - window) masked; softmax and
+// the P V sum follow utils/attention.py:186-198 with the running-max recurrence of
+// utils/attention.py:75-96.  Probabilities are rounded to bfloat16 for the P V product; the normaliser
+// is summed in 32-bit from the unrounded values.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kTileKeys = 64;
+constexpr int kTileRows = 64;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct AttnParams {
+    const __nv_bfloat16* q;
+    int q_stride;
+    const __nv_bfloat16* k_pages;
+    const __nv_bfloat16* v_pages;
+    const int* block_tables;
+    int max_blocks;
+    const int* q_start;      // [S + 1]
+    const int* context_len;  // [S]
+    __nv_bfloat16* out;      // [N, Hq * D]
+    int n_seqs, n_q_heads, n_kv_heads, page_size;
+    float scale_log2;
+    int window;
+    int skip_single;         // portions kernel: leave sequences with one token to the decode kernel
+    int split_len;           // decode kernel: keys per split (multiple of 64)
+    int max_splits;
+    float* partial_out;      // [N, Hq, max_splits, D]
+    float* partial_ml;       // [N, Hq, max_splits, 2]
+};
+
+__device__ __forceinline__ uint32_t smem_address(const void* pointer) {
+    return (uint32_t)__cvta_generic_to_shared(pointer);
+}
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(address));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(address));
+}
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float low, float high) {
+    __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
+    return *reinterpret_cast<uint32_t*>(&pair);
+}
+
+// Element offset of (row, 16-byte chunk) in a swizzled tile whose rows hold D bfloat16.
+template <int D>
+__device__ __forceinline__ int swizzled(int row, int chunk) {
+    return row * D + ((chunk ^ (row & 7)) << 3);
+}
+
+// Loads rows [first_key, first_key + 64) of one kv head into a swizzled shared tile; keys at or past
+// `end_key` are zero-filled.  All 128 threads take part.
+template <int D>
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_tile, __nv_bfloat16* v_tile, const AttnParams& p,
+                                             const int* table, int kv_head, int first_key, int end_key) {
+    constexpr int kChunks = D / 8;                        // 16-byte chunks per row
+    constexpr int kPerThread = kTileKeys * kChunks / kThreads;
+    constexpr int kRowsPerPass = kThreads / kChunks;
+    const int chunk = threadIdx.x % kChunks;
+    const int row0 = threadIdx.x / kChunks;
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+        const int row = row0 + i * kRowsPerPass;
+        const int key = first_key + row;
+        const bool valid = key < end_key;
+        size_t offset = 0;
+        if (valid) {
+            const int page = table[key / p.page_size];
+            offset = (((size_t)page * p.n_kv_heads + kv_head) * p.page_size + key % p.page_size) * D + chunk * 8;
+        }
+        const int destination = swizzled<D>(row, chunk);
+        cp_async_16(smem_address(k_tile + destination), p.k_pages + offset, valid ? 16 : 0);
+        cp_async_16(smem_address(v_tile + destination), p.v_pages + offset, valid ? 16 : 0);
+    }
+}
+
+// One warp: 16 query rows against NT * 8 keys of a shared tile, starting at tile row `key_row`, whose
+// absolute key index is `key_index`.  Rows g = lane / 4 and g + 8 of the warp see keys in
+// [row_low[h], row_high[h]] (row_high < 0: the row does not exist).
+template <int D, int NT>
+__device__ __forceinline__ void warp_tile(const uint32_t (&q_frag)[D / 16][4], const __nv_bfloat16* k_tile,
+                                          const __nv_bfloat16* v_tile, int key_row, int key_index,
+                                          const int (&row_low)[2], const int (&row_high)[2], float scale_log2,
+                                          float (&o_acc)[D / 8][4], float (&row_max)[2], float (&row_sum)[2]) {
+    const int lane = threadIdx.x & 31;
+    const int matrix = lane >> 3, matrix_row = lane & 7;
+    float s_acc[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s_acc[n][i] = 0.0f;
+
+    // S = Q K^T
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+        for (int pair = 0; pair < NT / 2; ++pair) {
+            uint32_t b[4];
+            const int row = key_row + pair * 16 + (matrix >> 1) * 8 + matrix_row;
+            ldmatrix_x4(b, smem_address(k_tile + swizzled<D>(row, 2 * ks + (matrix & 1))));
+            mma_bf16(s_acc[2 * pair], q_frag[ks], b[0], b[1]);
+            mma_bf16(s_acc[2 * pair + 1], q_frag[ks], b[2], b[3]);
+        }
+    }
+
+    // mask, scale, running maximum
+    const int t = lane & 3;
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int h = i >> 1;
+            const int key = key_index + n * 8 + 2 * t + (i & 1);
+            const bool seen = key >= row_low[h] && key <= row_high[h];
+            s_acc[n][i] = seen ? s_acc[n][i] * scale_log2 : -INFINITY;
+            tile_max[h] = fmaxf(tile_max[h], s_acc[n][i]);
+        }
+    }
+    float correction[2], reference[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 1));
+        tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
+        const float new_max = fmaxf(row_max[h], tile_max[h]);
+        reference[h] = new_max == -INFINITY ? 0.0f : new_max;   // nothing seen yet: exp2(-inf - 0) = 0
+        correction[h] = exp2f(row_max[h] - reference[h]);
+        row_max[h] = new_max;
+        row_sum[h] *= correction[h];
+    }
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+        o_acc[n][0] *= correction[0];
+        o_acc[n][1] *= correction[0];
+        o_acc[n][2] *= correction[1];
+        o_acc[n][3] *= correction[1];
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int h = i >> 1;
+            s_acc[n][i] = exp2f(s_acc[n][i] - reference[h]);
+            row_sum[h] += s_acc[n][i];
+        }
+    }
+
+    // O += P V
+#pragma unroll
+    for (int kk = 0; kk < NT / 2; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s_acc[2 * kk][0], s_acc[2 * kk][1]);
+        a[1] = pack_bf16(s_acc[2 * kk][2], s_acc[2 * kk][3]);
+        a[2] = pack_bf16(s_acc[2 * kk + 1][0], s_acc[2 * kk + 1][1]);
+        a[3] = pack_bf16(s_acc[2 * kk + 1][2], s_acc[2 * kk + 1][3]);
+#pragma unroll
+        for (int j = 0; j < D / 16; ++j) {
+            uint32_t b[4];
+            const int row = key_row + kk * 16 + (matrix & 1) * 8 + matrix_row;
+            ldmatrix_x4_trans(b, smem_address(v_tile + swizzled<D>(row, 2 * j + (matrix >> 1))));
+            mma_bf16(o_acc[2 * j], a, b[0], b[1]);
+            mma_bf16(o_acc[2 * j + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// portions of prompts
+// ------------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(kThreads) attention_portions_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) unsigned char shared_raw[];
+    __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(shared_raw);   // [64][D]
+    __nv_bfloat16* kv_tiles = q_tile + kTileRows * D;                        // [2 stages][K, V][64][D]
+
+    const int group = p.n_q_heads / p.n_kv_heads;
+    const int kv_head = blockIdx.y;
+    // which sequence and which of its row tiles this block has
+    int seq = 0, tile = blockIdx.x;
+    for (; seq < p.n_seqs; ++seq) {
+        const int q_len = p.q_start[seq + 1] - p.q_start[seq];
+        const int tiles = (q_len == 1 && p.skip_single) ? 0 : (q_len * group + kTileRows - 1) / kTileRows;
+        if (tile < tiles) break;
+        tile -= tiles;
+    }
+    if (seq >= p.n_seqs) return;
+    const int token0 = p.q_start[seq];
+    const int q_len = p.q_start[seq + 1] - token0;
+    const int context = p.context_len[seq];
+    const int n_rows = q_len * group;
+    const int first_row = tile * kTileRows;
+    const int* table = p.block_tables + (size_t)seq * p.max_blocks;
+
+    // gather the Q rows of the tile: row r is token r / group, head kv_head * group + r % group
+    {
+        constexpr int kChunks = D / 8;
+        for (int c = threadIdx.x; c < kTileRows * kChunks; c += kThreads) {
+            const int row = c / kChunks, chunk = c % kChunks;
+            const int r = first_row + row;
+            const bool valid = r < n_rows;
+            const __nv_bfloat16* src = p.q;
+            if (valid)
+                src = p.q + (size_t)(token0 + r / group) * p.q_stride + (size_t)(kv_head * group + r % group) * D + chunk * 8;
+            cp_async_16(smem_address(q_tile + swizzled<D>(row, chunk)), src, valid ? 16 : 0);
+        }
+    }
+    // key range of the tile: from the first token's window start to the last token's position
+    const int first_token = first_row / group;
+    const int last_row = min(first_row + kTileRows, n_rows) - 1;
+    const int last_token = last_row / group;
+    const int base_position = context - q_len;
+    const int high_key = base_position + last_token;
+    int low_key = 0;
+    if (p.window > 0) low_key = max(0, base_position + first_token - p.window + 1);
+    const int first_tile_key = (low_key / kTileKeys) * kTileKeys;
+    const int n_tiles = (high_key - first_tile_key) / kTileKeys + 1;
+
+    load_kv_tile<D>(kv_tiles, kv_tiles + kTileKeys * D, p, table, kv_head, first_tile_key, context);
+    cp_async_commit();
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2;
+    int row_low[2], row_high[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = first_row + warp * 16 + g + 8 * h;
+        if (r < n_rows) {
+            const int position = base_position + r / group;
+            row_high[h] = position;
+            row_low[h] = p.window > 0 ? max(0, position - p.window + 1) : 0;
+        } else {
+            row_high[h] = -1;
+            row_low[h] = 0;
+        }
+    }
+    float o_acc[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o_acc[n][i] = 0.0f;
+    float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
+    uint32_t q_frag[D / 16][4];
+    const int warp_high = __reduce_max_sync(0xffffffffu, max(row_high[0], row_high[1]));
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const int stage = it & 1;
+        __nv_bfloat16* k_tile = kv_tiles + stage * 2 * kTileKeys * D;
+        __nv_bfloat16* v_tile = k_tile + kTileKeys * D;
+        if (it + 1 < n_tiles) {
+            __nv_bfloat16* next_k = kv_tiles + (stage ^ 1) * 2 * kTileKeys * D;
+            load_kv_tile<D>(next_k, next_k + kTileKeys * D, p, table, kv_head, first_tile_key + (it + 1) * kTileKeys, context);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (it == 0) {
+            const int matrix = lane >> 3, matrix_row = lane & 7;
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                const int row = warp * 16 + (matrix & 1) * 8 + matrix_row;
+                ldmatrix_x4(q_frag[ks], smem_address(q_tile + swizzled<D>(row, 2 * ks + (matrix >> 1))));
+            }
+        }
+        const int tile_key = first_tile_key + it * kTileKeys;
+        // a warp whose rows all end before this tile has nothing to add (the causal upper triangle)
+        if (tile_key <= warp_high)
+            warp_tile<D, 8>(q_frag, k_tile, v_tile, 0, tile_key, row_low, row_high, p.scale_log2, o_acc, row_max, row_sum);
+        __syncthreads();   // the stage is overwritten by the load issued in the next iteration
+    }
+
+    // normalise and store: thread holds rows g, g + 8 and columns 8 n + 2 t, + 1
+    const int t = lane & 3;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float total = row_sum[h];
+        total += __shfl_xor_sync(0xffffffffu, total, 1);
+        total += __shfl_xor_sync(0xffffffffu, total, 2);
+        const int r = first_row + warp * 16 + g + 8 * h;
+        if (r >= n_rows) continue;
+        const float inverse = 1.0f / total;
+        __nv_bfloat16* dst = p.out + (size_t)(token0 + r / group) * p.n_q_heads * D + (size_t)(kv_head * group + r % group) * D;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            const uint32_t packed = pack_bf16(o_acc[n][2 * h] * inverse, o_acc[n][2 * h + 1] * inverse);
+            *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * t) = packed;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// decode: one token per sequence, keys split across blocks
+// ------------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) unsigned char shared_raw[];
+    __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(shared_raw);   // [16][D]
+    __nv_bfloat16* kv_tiles = q_tile + 16 * D;                               // [2 stages][K, V][64][D]
+
+    const int seq = blockIdx.z, kv_head = blockIdx.y, split = blockIdx.x;
+    const int token = p.q_start[seq];
+    if (p.q_start[seq + 1] - token != 1) return;
+    const int group = p.n_q_heads / p.n_kv_heads;
+    const int context = p.context_len[seq];
+    const int position = context - 1;
+    const int low_key = p.window > 0 ? max(0, position - p.window + 1) : 0;
+    const int first_key = (low_key / kTileKeys) * kTileKeys;
+    const int n_splits = (context - first_key + p.split_len - 1) / p.split_len;
+    if (split >= n_splits) return;
+    const int split_begin = first_key + split * p.split_len;
+    const int split_end = min(split_begin + p.split_len, context);
+    const int n_tiles = (split_end - split_begin + kTileKeys - 1) / kTileKeys;
+    const int* table = p.block_tables + (size_t)seq * p.max_blocks;
+
+    {
+        constexpr int kChunks = D / 8;
+        for (int c = threadIdx.x; c < 16 * kChunks; c += kThreads) {
+            const int row = c / kChunks, chunk = c % kChunks;
+            const bool valid = row < group;
+            const __nv_bfloat16* src = p.q;
+            if (valid) src = p.q + (size_t)token * p.q_stride + (size_t)(kv_head * group + row) * D + chunk * 8;
+            cp_async_16(smem_address(q_tile + swizzled<D>(row, chunk)), src, valid ? 16 : 0);
+        }
+    }
+    load_kv_tile<D>(kv_tiles, kv_tiles + kTileKeys * D, p, table, kv_head, split_begin, split_end);
+    cp_async_commit();
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2;
+    int row_low[2], row_high[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const bool exists = g + 8 * h < group;
+        row_high[h] = exists ? position : -1;
+        row_low[h] = low_key;
+    }
+    float o_acc[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o_acc[n][i] = 0.0f;
+    float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
+    uint32_t q_frag[D / 16][4];
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const int stage = it & 1;
+        __nv_bfloat16* k_tile = kv_tiles + stage * 2 * kTileKeys * D;
+        __nv_bfloat16* v_tile = k_tile + kTileKeys * D;
+        if (it + 1 < n_tiles) {
+            __nv_bfloat16* next_k = kv_tiles + (stage ^ 1) * 2 * kTileKeys * D;
+            load_kv_tile<D>(next_k, next_k + kTileKeys * D, p, table, kv_head, split_begin + (it + 1) * kTileKeys, split_end);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (it == 0) {
+            const int matrix = lane >> 3, matrix_row = lane & 7;
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                const int row = (matrix & 1) * 8 + matrix_row;
+                ldmatrix_x4(q_frag[ks], smem_address(q_tile + swizzled<D>(row, 2 * ks + (matrix >> 1))));
+            }
+        }
+        // each warp takes 16 of the tile's 64 keys
+        const int key_index = split_begin + it * kTileKeys + warp * 16;
+        if (key_index < split_end)
+            warp_tile<D, 2>(q_frag, k_tile, v_tile, warp * 16, key_index, row_low, row_high, p.scale_log2, o_acc, row_max, row_sum);
+        __syncthreads();
+    }
+
+    // merge the four warps through shared memory (the K/V stages are free now)
+    float* merge = reinterpret_cast<float*>(kv_tiles);        // [4 warps][16 rows][D + 2]
+    const int t = lane & 3;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float total = row_sum[h];
+        total += __shfl_xor_sync(0xffffffffu, total, 1);
+        total += __shfl_xor_sync(0xffffffffu, total, 2);
+        float* row = merge + ((size_t)warp * 16 + g + 8 * h) * (D + 2);
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            row[n * 8 + 2 * t] = o_acc[n][2 * h];
+            row[n * 8 + 2 * t + 1] = o_acc[n][2 * h + 1];
+        }
+        if (t == 0) {
+            row[D] = row_max[h];
+            row[D + 1] = total;
+        }
+    }
+    __syncthreads();
+    for (int index = threadIdx.x; index < group * D; index += kThreads) {
+        const int r = index / D, d = index % D;
+        float best = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) best = fmaxf(best, merge[((size_t)w * 16 + r) * (D + 2) + D]);
+        float numerator = 0.0f, denominator = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float* row = merge + ((size_t)w * 16 + r) * (D + 2);
+            const float weight = row[D] == -INFINITY ? 0.0f : exp2f(row[D] - best);
+            numerator += row[d] * weight;
+            denominator += row[D + 1] * weight;
+        }
+        const int head = kv_head * group + r;
+        if (n_splits == 1) {
+            p.out[(size_t)token * p.n_q_heads * D + (size_t)head * D + d] = __float2bfloat16_rn(numerator / denominator);
+        } else {
+            const size_t slot = ((size_t)token * p.n_q_heads + head) * p.max_splits + split;
+            p.partial_out[slot * D + d] = numerator / denominator;
+            if (d == 0) {
+                p.partial_ml[slot * 2] = best;
+                p.partial_ml[slot * 2 + 1] = denominator;
+            }
+        }
+    }
+}
+
+// out = sum_s O_s * l_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)   (utils/paged_attention.py:220-237)
+template <int D>
+__global__ void attention_decode_merge_kernel(const AttnParams p) {
+    const int seq = blockIdx.y, head = blockIdx.x;
+    const int token = p.q_start[seq];
+    if (p.q_start[seq + 1] - token != 1) return;
+    const int context = p.context_len[seq];
+    const int low_key = p.window > 0 ? max(0, context - p.window) : 0;
+    const int first_key = (low_key / kTileKeys) * kTileKeys;
+    const int n_splits = (context - first_key + p.split_len - 1) / p.split_len;
+    if (n_splits <= 1) return;
+    const size_t slot0 = ((size_t)token * p.n_q_heads + head) * p.max_splits;
+    float best = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) best = fmaxf(best, p.partial_ml[(slot0 + s) * 2]);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float numerator = 0.0f, denominator = 0.0f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float weight = p.partial_ml[(slot0 + s) * 2 + 1] * exp2f(p.partial_ml[(slot0 + s) * 2] - best);
+            numerator += p.partial_out[(slot0 + s) * D + d] * weight;
+            denominator += weight;
+        }
+        p.out[(size_t)token * p.n_q_heads * D + (size_t)head * D + d] = __float2bfloat16_rn(numerator / denominator);
+    }
+}
+
+template <int D>
+int launch_portions(const AttnParams& p, int total_tiles, cudaStream_t stream) {
+    const size_t shared = (size_t)(kTileRows * D + 4 * kTileKeys * D) * sizeof(__nv_bfloat16);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t status = cudaFuncSetAttribute(attention_portions_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        if (status != cudaSuccess) {
+            llm_set_error("attention_portions: cannot get %zu bytes of shared memory: %s", shared, cudaGetErrorString(status));
+            return (int)status;
+        }
+        configured = true;
+    }
+    dim3 grid(total_tiles, p.n_kv_heads);
+    attention_portions_kernel<D><<<grid, kThreads, shared, stream>>>(p);
+    return llm_check_launch("attention_portions");
+}
+
+template <int D>
+int launch_decode(const AttnParams& p, cudaStream_t stream) {
+    size_t shared = (size_t)(16 * D + 4 * kTileKeys * D) * sizeof(__nv_bfloat16);
+    const size_t merge = (size_t)4 * 16 * (D + 2) * sizeof(float) + 16 * D * sizeof(__nv_bfloat16);
+    if (merge > shared) shared = merge;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t status = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        if (status != cudaSuccess) {
+            llm_set_error("attention_decode: cannot get %zu bytes of shared memory: %s", shared, cudaGetErrorString(status));
+            return (int)status;
+        }
+        configured = true;
+    }
+    dim3 grid(p.max_splits, p.n_kv_heads, p.n_seqs);
+    attention_decode_kernel<D><<<grid, kThreads, shared, stream>>>(p);
+    int status = llm_check_launch("attention_decode");
+    if (status != LLM_OK || p.max_splits <= 1) return status;
+    dim3 merge_grid(p.n_q_heads, p.n_seqs);
+    attention_decode_merge_kernel<D><<<merge_grid, D < 128 ? D : 128, 0, stream>>>(p);
+    return llm_check_launch("attention_decode_merge");
+}
+
+}  // namespace
+
+// Sizes the tensor-core kernels take; everything else goes to the generic kernel.
+LLM_EXPORT int llm_attention_mma_supports(int head_dim, int n_q_heads, int n_kv_heads) {
+    if (head_dim != 64 && head_dim != 128) return 0;
+    if (n_kv_heads <= 0 || n_q_heads % n_kv_heads) return 0;
+    return n_q_heads / n_kv_heads <= 16;
+}
+
+// run_portions / run_decode: which of the two kernels to launch (a mixed batch launches both; each
+// skips the other's sequences).  total_tiles: sum over sequences of ceil(q_len * group / 64), counting
+// sequences of one token only when the decode kernel is not run.
+LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+                                 const int* block_tables, int max_blocks, const int* q_start, const int* context_len,
+                                 void* out, int n_seqs, int n_q_heads, int n_kv_heads, int head_dim, int page_size,
+                                 float scale, int window, int run_portions, int total_tiles, int run_decode,
+                                 int split_len, int max_splits, float* partial_out, float* partial_ml,
+                                 cudaStream_t stream) {
+    if (!llm_attention_mma_supports(head_dim, n_q_heads, n_kv_heads)) {
+        llm_set_error("attention_mma: head_dim %d with %d/%d heads is not supported (head_dim 64 or 128, group <= 16)",
+                      head_dim, n_q_heads, n_kv_heads);
+        return LLM_REFUSED;
+    }
+    if (run_decode && (split_len <= 0 || split_len % kTileKeys || max_splits <= 0)) {
+        llm_set_error("attention_mma: split_len %d must be a positive multiple of %d", split_len, kTileKeys);
+        return LLM_REFUSED;
+    }
+    if (n_seqs > 65535 || n_kv_heads > 65535) {
+        llm_set_error("attention_mma: at most 65535 sequences per launch, got %d", n_seqs);
+        return LLM_REFUSED;
+    }
+    AttnParams p;
+    p.q = (const __nv_bfloat16*)q;
+    p.q_stride = q_stride;
+    p.k_pages = (const __nv_bfloat16*)k_pages;
+    p.v_pages = (const __nv_bfloat16*)v_pages;
+    p.block_tables = block_tables;
+    p.max_blocks = max_blocks;
+    p.q_start = q_start;
+    p.context_len = context_len;
+    p.out = (__nv_bfloat16*)out;
+    p.n_seqs = n_seqs;
+    p.n_q_heads = n_q_heads;
+    p.n_kv_heads = n_kv_heads;
+    p.page_size = page_size;
+    p.scale_log2 = scale * kLog2e;
+    p.window = window;
+    p.skip_single = run_decode;
+    p.split_len = split_len;
+    p.max_splits = max_splits;
+    p.partial_out = partial_out;
+    p.partial_ml = partial_ml;
+    int status = LLM_OK;
+    if (run_portions && total_tiles > 0)
+        status = head_dim == 128 ? launch_portions<128>(p, total_tiles, stream) : launch_portions<64>(p, total_tiles, stream);
+    if (status == LLM_OK && run_decode)
+        status = head_dim == 128 ? launch_decode<128>(p, stream) : launch_decode<64>(p, stream);
+    return status;
+}

@@ -1,9 +1,66 @@
-"""bfloat16 tensor-core attention kernels over the paged cache (prefill portions and split-KV decode).
+"""bfloat16 tensor-core attention kernels over the paged cache (prompt portions and split-KV decode).
 
-``try_attention`` returns None when no tensor-core kernel takes the sizes; the caller then uses the
-generic 32-bit-arithmetic kernel, which takes every size."""
+``try_attention`` returns None when the tensor-core kernels do not take the sizes; the caller then
+uses the generic 32-bit-arithmetic kernel, which takes every size."""
 from __future__ import annotations
+
+import torch
+
+from .library import call, check, library, stream_handle
+
+TILE = 64          # rows per block of the portions kernel, keys per tile of both kernels
+MIN_SPLIT = 256    # fewest keys one decode block walks
+TARGET_BLOCKS = 592   # 4 blocks per SM on 148 SMs
+
+
+def supported(head_dim: int, n_q_heads: int, n_kv_heads: int) -> bool:
+    return bool(library().llm_attention_mma_supports(head_dim, n_q_heads, n_kv_heads))
+
+
+def plan(batch, group: int, n_kv_heads: int):
+    """Launch shape of a batch, derived once per step from its host-side lengths."""
+    key = ("attention_mma", group, n_kv_heads)
+    cached = batch.scratch.get(key)
+    if cached is not None:
+        return cached
+    singles = sum(1 for length in batch.q_lens if length == 1)
+    run_decode = singles > 0
+    run_portions = singles < batch.n_seqs
+    tiles = sum(-(-length * group // TILE) for length in batch.q_lens if length > 1)
+    split_len, max_splits = MIN_SPLIT, 1
+    if run_decode:
+        longest = max(context for context, length in zip(batch.context_lens, batch.q_lens) if length == 1)
+        # the longest splits that still fill the machine; never shorter than MIN_SPLIT keys
+        while split_len * 2 < longest and singles * n_kv_heads * -(-longest // (split_len * 2)) >= TARGET_BLOCKS:
+            split_len *= 2
+        max_splits = -(-longest // split_len) + 1     # + 1: a window may start inside a tile
+    cached = (run_portions, tiles, run_decode, split_len, max_splits)
+    batch.scratch[key] = cached
+    return cached
 
 
 def try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim, scale, window):
-    return None
+    if not supported(head_dim, n_q_heads, n_kv_heads):
+        return None
+    check(qkv, "qkv", torch.bfloat16)
+    check(k_pages, "k pages", torch.bfloat16, head_dim)
+    check(v_pages, "v pages", torch.bfloat16, head_dim)
+    check(block_tables, "block_tables", torch.int32)
+    run_portions, tiles, run_decode, split_len, max_splits = plan(batch, n_q_heads // n_kv_heads, n_kv_heads)
+    out = torch.empty((batch.n_tokens, n_q_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    partial_out = partial_ml = None
+    if run_decode and max_splits > 1:
+        # scratch of the split-KV decode, shared by every layer of the step
+        key = ("attention_mma_scratch", n_q_heads, head_dim, max_splits)
+        scratch = batch.scratch.get(key)
+        if scratch is None:
+            scratch = (torch.empty((batch.n_tokens, n_q_heads, max_splits, head_dim), dtype=torch.float32, device=qkv.device),
+                       torch.empty((batch.n_tokens, n_q_heads, max_splits, 2), dtype=torch.float32, device=qkv.device))
+            batch.scratch[key] = scratch
+        partial_out, partial_ml = scratch
+    call("llm_attention_mma", qkv.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(), block_tables.data_ptr(),
+         block_tables.shape[-1], batch.q_start.data_ptr(), batch.context_len.data_ptr(), out.data_ptr(), batch.n_seqs,
+         n_q_heads, n_kv_heads, head_dim, k_pages.shape[2], float(scale), int(window), int(run_portions), tiles,
+         int(run_decode), split_len, max_splits, 0 if partial_out is None else partial_out.data_ptr(),
+         0 if partial_ml is None else partial_ml.data_ptr(), stream_handle())
+    return out

@@ -24,6 +24,8 @@ SIGNATURES = {
     "llm_qk_norm_rope_kv_write": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _I, _S],
     "llm_attention_generic": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _S],
     "llm_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _S],
+    "llm_attention_mma_supports": [_I, _I, _I],
+    "llm_attention_mma": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _I, _I, _P, _P, _S],
 }
 
 _lock = threading.Lock()

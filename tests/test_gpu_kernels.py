@@ -291,3 +291,85 @@ def test_sampling_follows_the_distribution():
     tokens = ops.sample(logits, temperatures, seeds, steps).cpu()
     observed = torch.bincount(tokens.long(), minlength=4).double() / draws
     assert (observed - probabilities.double()).abs().max() < 4 * math.sqrt(0.25 / draws)
+
+
+class FakeBatch:
+    """The fields of a step batch that the attention wrappers read."""
+
+    def __init__(self, contexts, q_lens):
+        self.q_lens, self.context_lens = list(q_lens), list(contexts)
+        self.n_seqs, self.n_tokens = len(q_lens), sum(q_lens)
+        self.max_context = max(contexts)
+        starts = [0]
+        for n in q_lens:
+            starts.append(starts[-1] + n)
+        self.q_start = torch.tensor(starts, dtype=torch.int32, device=DEVICE)
+        self.context_len = torch.tensor(contexts, dtype=torch.int32, device=DEVICE)
+        self.positions = torch.cat([torch.arange(c - n, c) for c, n in zip(contexts, q_lens)]).to(torch.int32).to(DEVICE)
+        self.seq_of_token = torch.cat([torch.full((n,), i) for i, n in enumerate(q_lens)]).to(torch.int32).to(DEVICE)
+        self.scratch = {}
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim,page_size,window", [
+    (32, 8, 128, 16, None), (6, 1, 64, 8, None), (8, 8, 128, 1, None), (16, 1, 64, 16, 100), (12, 4, 128, 32, 300),
+    (5, 5, 64, 3, None)])
+@pytest.mark.parametrize("shape", ["decode", "portions", "mixed"])
+def test_attention_tensor_core_kernels(heads, kv_heads, dim, page_size, window, shape):
+    """The bfloat16 tensor-core kernels (prompt portions, split-KV decode, both in one mixed batch)
+    against plain attention: contexts long enough for several splits, portions that start in the middle
+    of a page and of a 64-key tile, a single first token, rows that are no multiple of the tile."""
+    from llmserver_b200 import ops
+    from llmserver_b200.ops import attention_bf16
+    assert attention_bf16.supported(dim, heads, kv_heads)
+    dtype = torch.bfloat16
+    if shape == "decode":
+        contexts, q_lens = [1500, 257, 64, 1, 700], [1, 1, 1, 1, 1]
+    elif shape == "portions":
+        contexts, q_lens = [333, 150, 37, 900], [41, 150, 2, 130]
+    else:
+        contexts, q_lens = [1100, 333, 1, 77, 513], [1, 70, 1, 77, 1]
+    scale = dim ** -0.5
+    dense_k = [rand((c, kv_heads, dim), dtype, 120 + i).cpu() for i, c in enumerate(contexts)]
+    dense_v = [rand((c, kv_heads, dim), dtype, 130 + i).cpu() for i, c in enumerate(contexts)]
+    k_pages, v_pages, tables = paged(dense_k, dense_v, page_size, 7, dtype)
+    queries = [rand((n, heads, dim), dtype, 140 + i).cpu() for i, n in enumerate(q_lens)]
+    q_stride = (heads + 2 * kv_heads) * dim
+    packed = torch.zeros((sum(q_lens), q_stride), dtype=dtype)
+    packed[:, :heads * dim] = torch.cat(queries).reshape(-1, heads * dim)
+    batch = FakeBatch(contexts, q_lens)
+    out = attention_bf16.try_attention(packed.to(DEVICE), q_stride, batch, tables, k_pages, v_pages, heads, kv_heads,
+                                       dim, scale, window or 0)
+    assert out is not None
+    want = torch.cat([plain_attention_rows(q.double(), k.double(), v.double(), scale, window, c - n)
+                      for q, k, v, c, n in zip(queries, dense_k, dense_v, contexts, q_lens)])
+    close(out, want, dtype, f"tensor-core attention ({shape})")
+    # and the generic kernel agrees on the same inputs
+    generic = ops.attention_generic(packed.to(DEVICE), q_stride, k_pages, v_pages, tables, batch.seq_of_token,
+                                    batch.positions, heads, kv_heads, dim, scale, window or 0)
+    close(generic, want, dtype, "generic attention on the same batch")
+
+
+def test_tensor_core_attention_finds_a_far_key_and_respects_the_window_edge():
+    from llmserver_b200.ops import attention_bf16
+    heads, kv_heads, dim, page_size, context = 4, 1, 128, 16, 1300
+    dtype = torch.bfloat16
+    direction = torch.zeros(dim)
+    direction[9] = 1.0
+    for q_len in (1, 40):
+        for hot, window, found in ((3, 0, True), (255, 0, True), (256, 0, True), (1299 - 40, 0, True),
+                                   (context - 200, 200, True), (context - 201, 200, False)):
+            k = torch.randn((context, kv_heads, dim), generator=torch.Generator().manual_seed(1)) * 0.1
+            v = torch.randn((context, kv_heads, dim), generator=torch.Generator().manual_seed(2))
+            k[hot, 0] = direction * 40.0
+            q = torch.zeros((q_len, heads, dim))
+            q[-1] = direction * 40.0       # the last query looks for the hot key
+            k_pages, v_pages, tables = paged([k.to(dtype)], [v.to(dtype)], page_size, 3, dtype)
+            q_stride = (heads + 2 * kv_heads) * dim
+            packed = torch.zeros((q_len, q_stride), dtype=dtype)
+            packed[:, :heads * dim] = q.reshape(q_len, -1).to(dtype)
+            batch = FakeBatch([context], [q_len])
+            out = attention_bf16.try_attention(packed.to(DEVICE), q_stride, batch, tables, k_pages, v_pages, heads,
+                                               kv_heads, dim, 1.0, window)
+            last = out[-1].float().cpu().view(heads, dim)[2]
+            target = v.to(dtype).float()[hot, 0]
+            assert torch.allclose(last, target, atol=3e-2) == found, f"q_len {q_len}, hot key {hot}, window {window}"

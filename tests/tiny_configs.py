@@ -19,5 +19,12 @@ TINY_C = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size
               hidden_act="silu", attention_bias=False, sliding_window=24,
               layer_types=["sliding_attention", "full_attention", "sliding_attention"])
 
+# head_dim 64: the size from which the bfloat16 path runs its tensor-core attention kernels
+TINY_D = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=400, hidden_size=128,
+              intermediate_size=192, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2, head_dim=64,
+              rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096,
+              hidden_act="silu", attention_bias=False, sliding_window=70,
+              layer_types=["full_attention", "sliding_attention"])
+
 # name -> (config.json dict, weight seed)
-TINY = {"a": (TINY_A, 0), "b": (TINY_B, 1), "c": (TINY_C, 2)}
+TINY = {"a": (TINY_A, 0), "b": (TINY_B, 1), "c": (TINY_C, 2), "d": (TINY_D, 3)}
