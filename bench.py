@@ -159,29 +159,45 @@ class Harness:
         from llmserver_b200 import ops
         start_context = max(1, MEAN_DECODE_CONTEXT - steps // 2 - warmup)
         ids = self.place(batch, start_context)
+        from llmserver_b200.sampling import SamplingRow
+        if self.step_function.graphs is None:
+            self.step_function.enable_graphs(CONTEXT, 64)
         tokens = self.tokens(batch)
         events = []
         launches_before = None
+        rows = [SamplingRow() for _ in ids]
         for step in range(warmup + steps):
             if step == warmup:
                 torch.cuda.synchronize()
                 launches_before = ops.launch_count()
             begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             begin.record()
-            logits = self.step_function.run([(request_id, [token], [0]) for request_id, token in zip(ids, tokens)])
-            sampled = ops.sample(logits)
+            # one decode step: batch in (one copy), forward, sampling, tokens out (one copy)
+            tokens = self.step_function.run_and_sample([(request_id, [token], [0]) for request_id, token in zip(ids, tokens)], rows)
             end.record()
             if step >= warmup:
                 events.append((begin, end))
-            tokens = sampled.tolist()      # the next step's inputs are this step's outputs
         torch.cuda.synchronize()
         launches = ops.launch_count() - launches_before
+        if self.step_function.graph_steps:      # replayed steps launch the captured kernels: count them per step
+            launches = steps * self.launches_per_step(batch)
         self.step_function.check_errors()
         times = [begin.elapsed_time(end) for begin, end in events]
         total_ms = sum(times)
         mean_context = start_context + warmup + (steps + 1) / 2
         return {"ms_per_step": total_ms / steps, "tokens_per_s": batch * steps / (total_ms / 1e3),
                 "launches": launches, "mean_context": mean_context}
+
+    def launches_per_step(self, batch: int) -> int:
+        """Kernels of this package in one decode step, counted on an eager step of the same shape."""
+        from llmserver_b200 import ops
+        ids = list(self.step_function.computed)[:batch]
+        graphs, self.step_function.graphs = self.step_function.graphs, None
+        before = ops.launch_count()
+        self.step_function.run([(request_id, [0], [0]) for request_id in ids])
+        count = ops.launch_count() - before + 1     # + the sampling kernel
+        self.step_function.graphs = graphs
+        return count
 
     def time_prefill(self, tokens: int, repeats: int = 3):
         torch = self.torch

@@ -6,18 +6,24 @@ kernels the batch carries, on the device as int32:
 
     token_ids[N], positions[N] (absolute), seq_of_token[N] (row of the block tables),
     q_start[S + 1] (first token of each sequence on the token axis), context_len[S] (tokens the
-    sequence holds after this step), block_tables[group][S, max_blocks], state_slots[S],
-    logit_rows[R] (indices into the token axis).
+    sequence holds after this step), block_tables[group][S, width], state_slots[S],
+    logit_rows[R] (indices into the token axis),
+    and per wanted row the sampling inputs: temperatures[R] (float32), seeds[R] (int64), sample_steps[R].
 
-Everything is packed into one pinned host buffer and crosses to the device in a single copy.
+Everything is packed into ONE pinned host buffer and crosses to the device in a single copy; the
+``BatchLayout`` says where each section lies.  A layout depends only on (N, S, R, table widths), so a
+decode step of a given batch size always has the same layout: that is what lets a CUDA graph replay it
+from a fixed device buffer.
+
 The reference builds either a padded [B, T] prefill batch or a [B, 1] decode batch with an additive
 mask (utils/batch.py:4-81) and never mixes the two in one forward (utils/engine.py:437-443).
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Sequence
+from typing import List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 
@@ -32,6 +38,35 @@ class SequenceSlice:
     state_slot: int = 0
 
 
+def _align(count: int, to: int = 4) -> int:
+    return -(-max(count, 1) // to) * to
+
+
+@dataclass(frozen=True)
+class BatchLayout:
+    """Offsets (in int32 words) of the sections of the packed buffer."""
+    n_tokens: int
+    n_seqs: int
+    n_logits: int
+    widths: Tuple[int, ...]
+
+    def __post_init__(self):
+        offsets, total = {}, 0
+        for name, count in (("token_ids", self.n_tokens), ("positions", self.n_tokens), ("seq_of_token", self.n_tokens),
+                            ("q_start", self.n_seqs + 1), ("context_len", self.n_seqs), ("state_slots", self.n_seqs),
+                            ("logit_rows", self.n_logits), ("temperatures", self.n_logits), ("seeds", 2 * self.n_logits),
+                            ("sample_steps", self.n_logits), ("error_flag", 1)):
+            offsets[name] = total
+            total += _align(count)
+        tables = []
+        for width in self.widths:
+            tables.append(total)
+            total += _align(self.n_seqs * width)
+        object.__setattr__(self, "offsets", offsets)
+        object.__setattr__(self, "table_offsets", tuple(tables))
+        object.__setattr__(self, "total", total)
+
+
 @dataclass
 class StepBatch:
     n_tokens: int
@@ -44,6 +79,9 @@ class StepBatch:
     context_len: torch.Tensor
     state_slots: torch.Tensor
     logit_rows: torch.Tensor
+    temperatures: torch.Tensor
+    seeds: torch.Tensor
+    sample_steps: torch.Tensor
     block_tables: List[torch.Tensor]
     error_flag: torch.Tensor
     # host-side copies that kernels' launch logic needs
@@ -56,82 +94,92 @@ class StepBatch:
     scratch: dict = field(default_factory=dict)   # per-step data kernels' wrappers derive once
 
 
-def _align(count: int, to: int = 4) -> int:
-    return -(-count // to) * to
+def layout_of(slices: List[SequenceSlice], n_groups: int, min_table_width: int = 1) -> BatchLayout:
+    n_tokens = sum(len(piece.tokens) for piece in slices)
+    n_logits = sum(len(piece.want) for piece in slices)
+    widths = tuple(max(min_table_width, max(len(piece.tables[group]) for piece in slices)) for group in range(n_groups))
+    return BatchLayout(n_tokens, len(slices), n_logits, widths)
 
 
-def build_batch(slices: List[SequenceSlice], n_groups: int, device, vocab_size: int = None,
-                min_table_width: int = 1) -> StepBatch:
+def pack(slices: List[SequenceSlice], layout: BatchLayout, host: np.ndarray, vocab_size: Optional[int] = None,
+         sampling: Optional[Sequence] = None) -> None:
+    """Fills ``host`` (int32 [layout.total]) with the step.  ``sampling``: per wanted row, in order, an
+    object with ``temperature``, ``seed`` and ``step`` (absent: greedy)."""
     if not slices:
         raise ValueError("a step needs at least one request")
-    n_seqs = len(slices)
-    tokens: List[int] = []
-    positions: List[int] = []
-    seq_of_token: List[int] = []
+    off = layout.offsets
+    host[:] = 0
+    at, row_at = 0, 0
     q_start = [0]
-    context_len: List[int] = []
-    logit_rows: List[int] = []
     for row, piece in enumerate(slices):
         count = len(piece.tokens)
         if count == 0:
             raise ValueError(f"request {piece.request_id!r} brings no tokens to the step")
-        if vocab_size is not None:
-            for token in piece.tokens:
-                if not 0 <= int(token) < vocab_size:
-                    raise ValueError(f"request {piece.request_id!r}: token id {token} is outside the vocabulary of {vocab_size}")
-        base = len(tokens)
-        tokens.extend(int(t) for t in piece.tokens)
-        positions.extend(range(piece.start, piece.start + count))
-        seq_of_token.extend([row] * count)
-        q_start.append(base + count)
-        context_len.append(piece.start + count)
+        tokens = np.asarray(piece.tokens, dtype=np.int64)
+        if vocab_size is not None and (tokens.min() < 0 or tokens.max() >= vocab_size):
+            raise ValueError(f"request {piece.request_id!r}: a token id is outside the vocabulary of {vocab_size}")
+        host[off["token_ids"] + at:off["token_ids"] + at + count] = tokens
+        host[off["positions"] + at:off["positions"] + at + count] = np.arange(piece.start, piece.start + count)
+        host[off["seq_of_token"] + at:off["seq_of_token"] + at + count] = row
+        host[off["context_len"] + row] = piece.start + count
+        host[off["state_slots"] + row] = piece.state_slot
         for place in piece.want:
             if not 0 <= place < count:
                 raise ValueError(f"request {piece.request_id!r}: logits wanted at place {place} of {count} tokens")
-            logit_rows.append(base + place)
-    n_tokens, n_logits = len(tokens), len(logit_rows)
-    widths = []
-    for group in range(n_groups):
-        width = max(min_table_width, max(len(piece.tables[group]) for piece in slices))
-        widths.append(width)
-    sections = [tokens, positions, seq_of_token, q_start, context_len, [piece.state_slot for piece in slices], logit_rows]
-    offsets, total = [], 0
-    for section in sections:
-        offsets.append(total)
-        total += _align(max(len(section), 1))
-    table_offsets = []
-    for width in widths:
-        table_offsets.append(total)
-        total += _align(n_seqs * width)
-    flag_offset = total
-    total += 4
-    host = torch.zeros(total, dtype=torch.int32)
-    for section, offset in zip(sections, offsets):
-        if section:
-            host[offset:offset + len(section)] = torch.tensor(section, dtype=torch.int32)
-    for group, (width, offset) in enumerate(zip(widths, table_offsets)):
-        table = torch.zeros((n_seqs, width), dtype=torch.int32)
-        for row, piece in enumerate(slices):
-            pages = [page if page >= 0 else 0 for page in piece.tables[group]]  # released pages are never read
-            if pages:
-                table[row, :len(pages)] = torch.tensor(pages, dtype=torch.int32)
-        host[offset:offset + n_seqs * width] = table.view(-1)
-    if torch.device(device).type == "cuda":
-        host = host.pin_memory()
-    buffer = host.to(device, non_blocking=True)
+            host[off["logit_rows"] + row_at] = at + place
+            row_at += 1
+        at += count
+        q_start.append(at)
+        for group, (width, table_offset) in enumerate(zip(layout.widths, layout.table_offsets)):
+            pages = np.asarray(piece.tables[group], dtype=np.int32)
+            if pages.size > width:
+                raise ValueError(f"request {piece.request_id!r} holds {pages.size} pages; the batch has room for {width}")
+            begin = table_offset + row * width
+            # released pages (negative entries) are never read; they become page 0 on the device
+            host[begin:begin + pages.size] = np.maximum(pages, 0)
+    host[off["q_start"]:off["q_start"] + len(q_start)] = q_start
+    if sampling is not None:
+        if len(sampling) != layout.n_logits:
+            raise ValueError(f"{len(sampling)} sampling rows for {layout.n_logits} wanted logits")
+        if layout.n_logits:
+            host[off["temperatures"]:off["temperatures"] + layout.n_logits] = np.asarray(
+                [row.temperature for row in sampling], dtype=np.float32).view(np.int32)
+            host[off["seeds"]:off["seeds"] + 2 * layout.n_logits] = np.asarray(
+                [row.seed & 0x7FFFFFFFFFFFFFFF for row in sampling], dtype=np.int64).view(np.int32)
+            host[off["sample_steps"]:off["sample_steps"] + layout.n_logits] = [row.step for row in sampling]
 
-    def view(index: int, length: int) -> torch.Tensor:
-        return buffer[offsets[index]:offsets[index] + length]
 
+def views(buffer: torch.Tensor, layout: BatchLayout, slices: List[SequenceSlice]) -> StepBatch:
+    """A StepBatch whose tensors are views of the device copy of the packed buffer."""
+    off = layout.offsets
+
+    def section(name: str, length: int) -> torch.Tensor:
+        return buffer[off[name]:off[name] + length]
+
+    n, s, r = layout.n_tokens, layout.n_seqs, layout.n_logits
     q_lens = [len(piece.tokens) for piece in slices]
+    context_lens = [piece.start + len(piece.tokens) for piece in slices]
     return StepBatch(
-        n_tokens=n_tokens, n_seqs=n_seqs, n_logits=n_logits,
-        token_ids=view(0, n_tokens), positions=view(1, n_tokens), seq_of_token=view(2, n_tokens),
-        q_start=view(3, n_seqs + 1), context_len=view(4, n_seqs), state_slots=view(5, n_seqs),
-        logit_rows=view(6, n_logits),
-        block_tables=[buffer[offset:offset + n_seqs * width].view(n_seqs, width)
-                      for width, offset in zip(widths, table_offsets)],
-        error_flag=buffer[flag_offset:flag_offset + 1],
-        q_lens=q_lens, context_lens=context_len, max_q_len=max(q_lens), max_context=max(context_len),
-        decode_only=all(length == 1 for length in q_lens), host_bytes=total * 4,
+        n_tokens=n, n_seqs=s, n_logits=r,
+        token_ids=section("token_ids", n), positions=section("positions", n), seq_of_token=section("seq_of_token", n),
+        q_start=section("q_start", s + 1), context_len=section("context_len", s), state_slots=section("state_slots", s),
+        logit_rows=section("logit_rows", r), temperatures=section("temperatures", r).view(torch.float32),
+        seeds=section("seeds", 2 * r).view(torch.int64), sample_steps=section("sample_steps", r),
+        block_tables=[buffer[offset:offset + s * width].view(s, width)
+                      for width, offset in zip(layout.widths, layout.table_offsets)],
+        error_flag=section("error_flag", 1),
+        q_lens=q_lens, context_lens=context_lens, max_q_len=max(q_lens), max_context=max(context_lens),
+        decode_only=all(length == 1 for length in q_lens), host_bytes=layout.total * 4,
     )
+
+
+def build_batch(slices: List[SequenceSlice], n_groups: int, device, vocab_size: Optional[int] = None,
+                min_table_width: int = 1, sampling: Optional[Sequence] = None) -> StepBatch:
+    """Packs the step on the host (pinned when the device is a GPU) and copies it over in one go."""
+    if not slices:
+        raise ValueError("a step needs at least one request")
+    layout = layout_of(slices, n_groups, min_table_width)
+    on_gpu = torch.device(device).type == "cuda"
+    host = torch.empty(layout.total, dtype=torch.int32, pin_memory=on_gpu)
+    pack(slices, layout, host.numpy(), vocab_size, sampling)
+    return views(host.to(device, non_blocking=True), layout, slices)

@@ -81,7 +81,10 @@ class Engine:
         self.active_requests: Dict[str, Request] = {}
         self.finished_requests: Dict[str, Request] = {}
         self._ids = itertools.count()
-        self.cuda_graphs = bool(cuda_graphs) if cuda_graphs is not None else False
+        # decode steps replay CUDA graphs unless told otherwise (the reference: utils/engine.py:126-148)
+        self.cuda_graphs = (self.device.type == "cuda") if cuda_graphs is None else bool(cuda_graphs)
+        if self.cuda_graphs and self.step_function.graphs is None:
+            self.step_function.enable_graphs(min(max_context, self.num_blocks * self.block_size), max_batch_size)
         self.stats = {"steps": 0, "preemptions": 0, "tokens": 0, "prefill_tokens": 0, "decode_tokens": 0}
 
     # ------------------------------------------------------------------ requests
@@ -191,8 +194,8 @@ class Engine:
             if wants:
                 sampled.append(request)
             finishing.append(done)
-        logits = self.step_function.run(entries)
-        tokens = self._sample(logits, sampled) if sampled else []
+        rows = [SamplingRow(request.temperature, request.seed, len(request.generated_token_ids)) for request in sampled]
+        tokens = self.step_function.run_and_sample(entries, rows, self.sampler)
         self.stats["steps"] += 1
         self.stats["decode_tokens"] += len(out.decode_requests)
         self.stats["prefill_tokens"] += sum(out.prefill_token_counts)
@@ -209,14 +212,6 @@ class Engine:
         self.scheduler.running[:] = [request for request in self.scheduler.running
                                      if request.status not in (RequestStatus.FINISHED, RequestStatus.CANCELLED)]
         return bool(self.scheduler.waiting or self.scheduler.running)
-
-    def _sample(self, logits: torch.Tensor, requests: List[Request]) -> List[int]:
-        """One kernel for the whole step and the step's only device-to-host read
-        (utils/engine.py:295-297 reads the argmax the same way)."""
-        result = self.sampler(logits, [SamplingRow(request.temperature, request.seed, len(request.generated_token_ids))
-                                       for request in requests])
-        self.step_function.check_errors()
-        return result
 
     def _accept(self, request: Request, token: int) -> None:
         request.append_generated_token(token)

@@ -8,11 +8,12 @@ one function.
 """
 from __future__ import annotations
 
-from typing import List, Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 
-from ..cache import CacheManager
+from .. import ops
+from ..cache import CacheManager, KVCacheExhaustedError
 from .batch import SequenceSlice, StepBatch, build_batch
 
 StepEntry = Tuple[object, Sequence[int], Sequence[int]]  # (request id, next tokens, wanted places)
@@ -27,6 +28,8 @@ class StepFunction:
         self.pending_flags: List[torch.Tensor] = []
         self.steps_run = 0
         self.last_batch_bytes = 0   # size of the last step's host-to-device copy
+        self.graphs = None
+        self.graph_steps = 0
 
     # ------------------------------------------------------------------ request lifetime
     def admit(self, request_id, prompt: Sequence[int] = None) -> int:
@@ -45,8 +48,13 @@ class StepFunction:
         return self.computed[request_id]
 
     # ------------------------------------------------------------------ the step
-    def prepare(self, entries: List[StepEntry]) -> StepBatch:
-        """Allocates the pages the step needs (all or nothing) and builds the device batch."""
+    def enable_graphs(self, max_context: int, max_batch: int = 256) -> None:
+        """Decode-only steps of up to ``max_context`` tokens per request run as CUDA graphs from now on."""
+        from .graphs import DecodeGraphs
+        self.graphs = DecodeGraphs(self.model, len(self.cache.groups), self.cache.page_size, max_context, max_batch)
+
+    def slices_for(self, entries: List[StepEntry]) -> List[SequenceSlice]:
+        """Allocates the pages the step needs (all or nothing) and describes each request's share."""
         seen = set()
         for request_id, tokens, _ in entries:
             if request_id in seen:
@@ -61,24 +69,31 @@ class StepFunction:
             totals = [a + b for a, b in zip(totals, needed)]
         for group, (total, available) in enumerate(zip(totals, self.cache.available())):
             if total > available:
-                from ..cache import KVCacheExhaustedError
                 raise KVCacheExhaustedError(f"the step needs {total} pages in cache group {group}, {available} are available")
+        limit = self.model.spec.max_positions
         slices = []
         for request_id, tokens, want in entries:
             start = self.computed[request_id]
+            if limit is not None and start + len(tokens) > limit:
+                raise ValueError(f"request {request_id!r} would reach {start + len(tokens)} tokens; "
+                                 f"the model's max_position_embeddings is {limit}")
             self.cache.ensure(request_id, start + len(tokens))
             slices.append(SequenceSlice(request_id, tokens, start, want,
                                         [self.cache.table(request_id, group) for group in range(len(self.cache.groups))],
                                         self.cache.slot_of(request_id)))
-        limit = self.model.spec.max_positions
-        if limit is not None:
-            for piece in slices:
-                if piece.start + len(piece.tokens) > limit:
-                    raise ValueError(f"request {piece.request_id!r} would reach {piece.start + len(piece.tokens)} tokens; "
-                                     f"the model's max_position_embeddings is {limit}")
-        batch = build_batch(slices, len(self.cache.groups), self.device, self.model.spec.vocab_size)
+        return slices
+
+    def prepare(self, entries: List[StepEntry], sampling: Optional[Sequence] = None) -> StepBatch:
+        batch = build_batch(self.slices_for(entries), len(self.cache.groups), self.device, self.model.spec.vocab_size,
+                            sampling=sampling)
         self.last_batch_bytes = batch.host_bytes
         return batch
+
+    def _advance(self, entries: List[StepEntry]) -> None:
+        for request_id, tokens, _ in entries:
+            self.computed[request_id] += len(tokens)
+            self.cache.advance(request_id, self.computed[request_id])
+        self.steps_run += 1
 
     def run(self, entries: List[StepEntry]) -> torch.Tensor:
         """Runs one step; returns logits [wanted, vocab] (float32) in the order of the entries and of
@@ -86,11 +101,36 @@ class StepFunction:
         batch = self.prepare(entries)
         logits = self.model.step(batch)
         self.pending_flags.append(batch.error_flag)
-        for request_id, tokens, _ in entries:
-            self.computed[request_id] += len(tokens)
-            self.cache.advance(request_id, self.computed[request_id])
-        self.steps_run += 1
+        self._advance(entries)
         return logits
+
+    def run_and_sample(self, entries: List[StepEntry], sampling: Sequence, sampler=None) -> List[int]:
+        """Runs one step and samples one token per wanted place (``sampling``: one row per wanted place
+        with ``temperature``, ``seed``, ``step``).  Returns the tokens on the host: the step's only
+        device-to-host read, which also brings the kernels' error flag."""
+        if sampler is not None and not hasattr(sampler, "from_batch"):
+            logits = self.run(entries)       # a sampler of the caller's own (tests use one on the CPU)
+            return sampler(logits, sampling) if sampling else []
+        slices = self.slices_for(entries)
+        graph = self.graphs.ready_for(slices) if self.graphs is not None and sampling else None
+        if graph is not None:
+            result = graph.run(slices, sampling)
+            self.last_batch_bytes = graph.layout.total * 4
+            self.graph_steps += 1
+        else:
+            batch = build_batch(slices, len(self.cache.groups), self.device, self.model.spec.vocab_size, sampling=sampling)
+            self.last_batch_bytes = batch.host_bytes
+            logits = self.model.step(batch)
+            if not sampling:
+                self.pending_flags.append(batch.error_flag)
+                self._advance(entries)
+                return []
+            tokens = ops.sample(logits, batch.temperatures, batch.seeds, batch.sample_steps)
+            result = torch.cat([tokens, batch.error_flag]).tolist()
+        self._advance(entries)
+        if result[-1] != 0:
+            raise RuntimeError("a kernel met a block-table entry outside the page pool; the cache bookkeeping is corrupt")
+        return result[:-1]
 
     def check_errors(self) -> None:
         """Reads the kernels' error flags of the steps run since the last check (synchronises)."""

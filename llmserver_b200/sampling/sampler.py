@@ -35,6 +35,10 @@ class Sampler:
             raise ValueError(f"{logits.shape[0]} rows of logits for {len(rows)} requests")
         return self.sample_on_device(logits, rows).tolist()
 
+    def from_batch(self, logits: torch.Tensor, batch) -> torch.Tensor:
+        """Samples with the per-row inputs that crossed to the device inside the step's batch."""
+        return ops.sample(logits, batch.temperatures, batch.seeds, batch.sample_steps)
+
     def sample_on_device(self, logits: torch.Tensor, rows: Sequence[SamplingRow]) -> torch.Tensor:
         if any(row.temperature > 0 for row in rows):
             temperatures = torch.tensor([row.temperature for row in rows], dtype=torch.float32)

@@ -127,3 +127,22 @@ def test_the_first_tokens_of_a_sequence(tiny_folders):
         prompts = [[vocab - 1], [0, 1], [5]]
         for prompt, tokens in zip(prompts, engine.generate(prompts)):
             assert tokens == plain_greedy(folder, prompt, 5)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cuda_graph_decode_gives_the_same_tokens(tiny_folders, dtype):
+    """Decode steps replayed from CUDA graphs against the same steps launched one by one."""
+    from llmserver_b200 import Engine
+    folder = tiny_folders["d"]
+    prompts = [tokens_for(400, length, 90 + length) for length in (33, 5, 71)]
+    outputs = {}
+    for graphs in (False, True):
+        engine = Engine(folder, max_new_tokens=40, max_batch_size=4, max_num_batched_tokens=128, kv_cache_num_blocks=64,
+                        kv_cache_block_size=16, ignore_eos=True, dtype=dtype, cuda_graphs=graphs, max_context=256)
+        outputs[graphs] = engine.generate(prompts)
+        assert (engine.step_function.graph_steps > 20) == graphs
+        engine.cache.check_invariants()
+    if dtype == "float32":
+        assert outputs[True] == outputs[False]
+    for prompt, tokens in zip(prompts, outputs[True]):
+        assert_tokens_are_argmax_of_plain(folder, prompt, tokens, dtype)
