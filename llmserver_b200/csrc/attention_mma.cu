@@ -584,3 +584,85 @@ LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, const void* k_page
         status = head_dim == 128 ? launch_decode<128>(p, stream) : launch_decode<64>(p, stream);
     return status;
 }
+
+// ------------------------------------------------------------------------------------------------
+// The same decode attention for callers that cannot allocate: scratch in a fixed array of the library
+// (see attention_noalloc.h for who needs this and for the rules of use).
+// ------------------------------------------------------------------------------------------------
+#include "attention_noalloc.h"
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[LLM_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+// Device address of g_noalloc_scratch per device.  In host code the array's name is only a handle for
+// cudaGetSymbolAddress; the kernels must be given the address that call returns.
+float* g_noalloc_address[kMaxDevices] = {};
+}  // namespace
+
+LLM_EXPORT int llm_attention_decode_noalloc(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+                                            const int* block_tables, int max_blocks, const int* q_start,
+                                            const int* context_len, void* out, int n_seqs, int n_q_heads,
+                                            int n_kv_heads, int head_dim, int page_size, float scale, int window,
+                                            int split_len, int max_splits, cudaStream_t stream) {
+    if (n_seqs <= 0) return LLM_OK;
+    if (!llm_attention_mma_supports(head_dim, n_q_heads, n_kv_heads)) {
+        llm_set_error("attention_decode_noalloc: head_dim %d with %d/%d heads is not supported (head_dim 64 or 128, group <= 16)",
+                      head_dim, n_q_heads, n_kv_heads);
+        return LLM_REFUSED;
+    }
+    if (split_len <= 0 || split_len % kTileKeys || max_splits <= 0) {
+        llm_set_error("attention_decode_noalloc: split_len %d must be a positive multiple of %d and max_splits %d positive",
+                      split_len, kTileKeys, max_splits);
+        return LLM_REFUSED;
+    }
+    if (n_seqs > 65535) {
+        llm_set_error("attention_decode_noalloc: at most 65535 sequences per call, got %d", n_seqs);
+        return LLM_REFUSED;
+    }
+    const size_t slots = (size_t)n_seqs * n_q_heads * max_splits;
+    const size_t needed = slots * (size_t)(head_dim + 2) * sizeof(float);
+    if (needed > LLM_NOALLOC_SCRATCH_BYTES) {
+        llm_set_error("attention_decode_noalloc: %d sequences x %d heads x %d splits need %zu bytes of scratch; the "
+                      "library's fixed array holds %u (use fewer sequences per call or longer splits)",
+                      n_seqs, n_q_heads, max_splits, needed, (unsigned)LLM_NOALLOC_SCRATCH_BYTES);
+        return LLM_REFUSED;
+    }
+    int device = 0;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status != cudaSuccess || device < 0 || device >= kMaxDevices) {
+        llm_set_error("attention_decode_noalloc: cannot tell the current device: %s", cudaGetErrorString(status));
+        return status != cudaSuccess ? (int)status : LLM_REFUSED;
+    }
+    if (g_noalloc_address[device] == nullptr) {   // first call on this device
+        void* address = nullptr;
+        status = cudaGetSymbolAddress(&address, g_noalloc_scratch);
+        if (status != cudaSuccess || address == nullptr) {
+            llm_set_error("attention_decode_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(status));
+            return status != cudaSuccess ? (int)status : LLM_REFUSED;
+        }
+        g_noalloc_address[device] = static_cast<float*>(address);
+    }
+    AttnParams p;
+    p.q = (const __nv_bfloat16*)q;
+    p.q_stride = q_stride;
+    p.k_pages = (const __nv_bfloat16*)k_pages;
+    p.v_pages = (const __nv_bfloat16*)v_pages;
+    p.block_tables = block_tables;
+    p.max_blocks = max_blocks;
+    p.q_start = q_start;
+    p.context_len = context_len;
+    p.out = (__nv_bfloat16*)out;
+    p.n_seqs = n_seqs;
+    p.n_q_heads = n_q_heads;
+    p.n_kv_heads = n_kv_heads;
+    p.page_size = page_size;
+    p.scale_log2 = scale * kLog2e;
+    p.window = window;
+    p.skip_single = 1;
+    p.split_len = split_len;
+    p.max_splits = max_splits;
+    p.partial_out = g_noalloc_address[device];                       // [slots][head_dim]
+    p.partial_ml = g_noalloc_address[device] + slots * head_dim;      // [slots][2]
+    return head_dim == 128 ? launch_decode<128>(p, stream) : launch_decode<64>(p, stream);
+}

@@ -1,0 +1,48 @@
+// Split-KV decode attention for callers that cannot allocate device memory.
+//
+// This entry point has no counterpart in AshvinSehgal/LLMServer; it exists for users of this library
+// who call it from places where cudaMalloc (or a framework allocator that may fall back to it) is not
+// an option: a serving loop that has handed every free byte of the GPU to its KV cache and must not
+// fail or stall on an allocation in the middle of a step, a latency-critical thread that may not take
+// the driver's allocation locks, or a plain C host program that links this library without PyTorch
+// and has no caching allocator at all.
+//
+// It computes exactly what llm_attention_mma computes for a batch of single-token (decode) sequences,
+// but the scratch memory of the split-KV algorithm (per-split partial outputs, maxima and sums) lives
+// in a fixed array inside the library instead of being passed in.
+//
+//   * The array is LLM_NOALLOC_SCRATCH_BYTES (8 MiB) of device memory per GPU that loads the library,
+//     held until the process exits.  A call needs
+//         n_seqs * n_q_heads * max_splits * (head_dim + 2) * 4 bytes
+//     of it and is refused with LLM_REFUSED (-1) and a message (llm_last_error) if that is more.
+//   * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and sets the
+//     kernels' shared-memory limit.  Make that first call outside any stream capture.
+//   * Every call uses the same array, and what the previous call left there is simply overwritten:
+//     each slot that a call reads it has written first, so nothing has to be cleared.  For the same
+//     reason two calls that run at the same time on one GPU (different streams) would corrupt each
+//     other: keep calls on one stream, or order them yourself.
+//   * No cudaMalloc, cudaFree or other allocating routine is called, here or in the kernels.
+//
+// Arguments are those of llm_attention_mma restricted to decode: `q` holds head h of sequence s at
+// q[s * q_stride + h * head_dim] (bfloat16); pages are [page, kv_head, slot, head_dim]; block_tables is
+// int32 [n_seqs, max_blocks]; q_start is int32 [n_seqs + 1] = 0, 1, 2, ... and context_len int32 [n_seqs],
+// both on the device; `out` is bfloat16 [n_seqs, n_q_heads * head_dim].  split_len is a positive multiple
+// of 64; max_splits must be at least ceil(longest context / split_len) + 1.  Returns 0 on success.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#define LLM_NOALLOC_SCRATCH_BYTES (8u << 20)
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int llm_attention_decode_noalloc(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+                                 const int* block_tables, int max_blocks, const int* q_start, const int* context_len,
+                                 void* out, int n_seqs, int n_q_heads, int n_kv_heads, int head_dim, int page_size,
+                                 float scale, int window, int split_len, int max_splits, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
