@@ -1,0 +1,124 @@
+"""Command-line benchmark in the manner of the reference's ``benchmark_cuda.py``: token-id prompts,
+exactly n forced tokens per request, greedy.
+
+    python -m llmserver_b200.cli.benchmark --model DIR [--prompt-tokens 128,1024] [--batch-sizes 1,8,32]
+           [--output-tokens 128] [--repeats 3] [--dtype bfloat16] [--block-size 16]
+           [--max-num-batched-tokens 16384] [--json] [--out-dir DIR]
+    python -m llmserver_b200.cli.benchmark --random-config config.json --seed 0 ...
+
+Option names and meanings follow benchmark_cuda.py:477-496 where the reference has them
+(``--model``, ``--prompt-tokens``, ``--batch-sizes``, ``--output-tokens``, ``--repeats``, ``--dtype``,
+``--block-size``, ``--max-num-batched-tokens``, ``--json``, ``--out-dir``); ``--random-config`` and
+``--seed`` are this engine's random-weights mode.  Method (benchmark_cuda.py:8-13,228-231): TTFT is the
+time to produce one token for the whole batch; decode tokens/s = batch * (n - 1) / (total - TTFT); the
+median over the repeats is reported; every run gets fresh uniform-random prompts so that no cached prefix
+carries over; cache pages = batch * ceil((prompt + output) / block) + 8 (benchmark_cuda.py:107-111).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import time
+
+
+def _int_list(text: str):
+    return [int(part) for part in text.split(",") if part]
+
+
+def run_once(engine, prompts, output_tokens: int) -> float:
+    import torch
+
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    for prompt in prompts:
+        engine.add_request(prompt_token_ids=prompt, max_new_tokens=output_tokens, ignore_eos=True)
+    while engine.step():
+        pass
+    torch.cuda.synchronize()
+    return time.perf_counter() - started
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--model", help="folder with config.json and model.safetensors")
+    parser.add_argument("--random-config", help="config.json of a model to be given seeded random weights on the device")
+    parser.add_argument("--seed", type=int, default=0)
+    parser.add_argument("--prompt-tokens", type=_int_list, default=[128, 1024])
+    parser.add_argument("--batch-sizes", type=_int_list, default=[1, 8, 32])
+    parser.add_argument("--output-tokens", type=int, default=128)
+    parser.add_argument("--repeats", type=int, default=3)
+    parser.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    parser.add_argument("--device", default="cuda:0")
+    parser.add_argument("--block-size", type=int, default=16)
+    parser.add_argument("--max-num-batched-tokens", type=int, default=16384)
+    parser.add_argument("--no-cuda-graphs", action="store_true")
+    parser.add_argument("--json", action="store_true", help="print the results as JSON")
+    parser.add_argument("--out-dir", help="also write results.json there")
+    args = parser.parse_args(argv)
+    if bool(args.model) == bool(args.random_config):
+        parser.error("give exactly one of --model and --random-config")
+    os.environ["PATH"] = os.path.dirname(sys.executable) + os.pathsep + os.environ.get("PATH", "")
+
+    import torch
+
+    from ..config.registry import architecture_of
+    from ..engine.engine import Engine
+    from ..models import load_model, random_model
+
+    load_started = time.perf_counter()
+    if args.model:
+        model = load_model(args.model, args.dtype, args.device)
+    else:
+        with open(args.random_config) as handle:
+            raw = json.load(handle)
+        model = random_model(architecture_of(raw).config_class.from_dict(raw), args.seed, args.dtype, args.device)
+    torch.cuda.synchronize()
+    load_seconds = time.perf_counter() - load_started
+    vocab = model.spec.vocab_size
+    generator = torch.Generator().manual_seed(args.seed)
+    results = []
+    for prompt_tokens in args.prompt_tokens:
+        for batch in args.batch_sizes:
+            longest = prompt_tokens + args.output_tokens
+            engine = Engine(model, max_new_tokens=args.output_tokens, max_batch_size=batch,
+                            max_num_batched_tokens=max(args.max_num_batched_tokens, batch),
+                            kv_cache_num_blocks=batch * -(-longest // args.block_size) + 8,
+                            kv_cache_block_size=args.block_size, ignore_eos=True, prefix_caching=False,
+                            cuda_graphs=not args.no_cuda_graphs, max_context=longest)
+
+            def fresh():
+                return [torch.randint(0, vocab, (prompt_tokens,), generator=generator).tolist() for _ in range(batch)]
+
+            run_once(engine, fresh(), min(4, args.output_tokens))      # warm-up (benchmark_cuda.py:208)
+            ttfts, totals = [], []
+            for _ in range(args.repeats):
+                ttfts.append(run_once(engine, fresh(), 1))
+                totals.append(run_once(engine, fresh(), args.output_tokens))
+            ttft, total = statistics.median(ttfts), statistics.median(totals)
+            decode = batch * (args.output_tokens - 1) / (total - ttft) if args.output_tokens > 1 and total > ttft else None
+            row = {"prompt_tokens": prompt_tokens, "batch_size": batch, "output_tokens": args.output_tokens,
+                   "ttft_ms": round(ttft * 1e3, 3), "total_ms": round(total * 1e3, 3),
+                   "decode_tokens_per_s": None if decode is None else round(decode, 1),
+                   "generation_tokens_per_s": round(batch * args.output_tokens / total, 1)}
+            results.append(row)
+            if not args.json:
+                print(f"prompt {prompt_tokens:6d}  batch {batch:4d}  TTFT {row['ttft_ms']:9.2f} ms  "
+                      f"decode {row['decode_tokens_per_s']} tok/s  total {row['total_ms']:.1f} ms", flush=True)
+            del engine
+            torch.cuda.empty_cache()
+    report = {"model": args.model or args.random_config, "dtype": args.dtype, "load_seconds": round(load_seconds, 2),
+              "block_size": args.block_size, "repeats": args.repeats, "results": results}
+    if args.json:
+        print(json.dumps(report))
+    if args.out_dir:
+        os.makedirs(args.out_dir, exist_ok=True)
+        with open(os.path.join(args.out_dir, "results.json"), "w") as handle:
+            json.dump(report, handle, indent=2)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
