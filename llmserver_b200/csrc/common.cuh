@@ -33,6 +33,81 @@ struct Num<__nv_bfloat16> {
     static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 };
 
+// 16-byte vector access: VEC = 16 / sizeof(T) elements (8 bfloat16 or 4 float) to and from 32-bit values.
+template <typename T>
+struct Vec16;
+
+template <>
+struct Vec16<float> {
+    static constexpr int kCount = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 raw = *reinterpret_cast<const float4*>(p);
+        v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+
+template <>
+struct Vec16<__nv_bfloat16> {
+    static constexpr int kCount = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 pair = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&words[i]));
+            v[2 * i] = pair.x;
+            v[2 * i + 1] = pair.y;
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+        uint32_t words[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 pair = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            words[i] = *reinterpret_cast<const uint32_t*>(&pair);
+        }
+        *reinterpret_cast<uint4*>(p) = make_uint4(words[0], words[1], words[2], words[3]);
+    }
+};
+
+// Eight consecutive elements of either type to and from 32-bit values (pointers 16-byte aligned).
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&v)[8]) {
+    if constexpr (sizeof(T) == 2) {
+        Vec16<T>::load(p, v);
+    } else {
+        float low[4], high[4];
+        Vec16<float>::load(reinterpret_cast<const float*>(p), low);
+        Vec16<float>::load(reinterpret_cast<const float*>(p) + 4, high);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            v[j] = low[j];
+            v[4 + j] = high[j];
+        }
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&v)[8]) {
+    if constexpr (sizeof(T) == 2) {
+        Vec16<T>::store(p, v);
+    } else {
+        float low[4], high[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            low[j] = v[j];
+            high[j] = v[4 + j];
+        }
+        Vec16<float>::store(reinterpret_cast<float*>(p), low);
+        Vec16<float>::store(reinterpret_cast<float*>(p) + 4, high);
+    }
+}
+
+__host__ __device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);

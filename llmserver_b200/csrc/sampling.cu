@@ -32,19 +32,25 @@ __device__ __forceinline__ void take_better(float& best, int& best_index, float 
     }
 }
 
+// One block scans a slice of a row; grid (slices, rows).  With one slice the token goes straight to
+// `out`; with more, each block leaves its best (score, index) in `partial` and sample_merge_kernel picks.
 __global__ void sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperatures,
                               const uint64_t* __restrict__ seeds, const int* __restrict__ steps,
-                              int* __restrict__ out, int vocab) {
+                              int* __restrict__ out, int vocab, float* __restrict__ partial_scores,
+                              int* __restrict__ partial_indices) {
     __shared__ float best_values[32];
     __shared__ int best_indices[32];
-    const int row = blockIdx.x;
+    const int row = blockIdx.y, slices = gridDim.x;
     const float* src = logits + (size_t)row * vocab;
     const float temperature = temperatures ? temperatures[row] : 0.0f;
     const uint64_t seed = seeds ? seeds[row] : 0;
     const uint32_t step = steps ? (uint32_t)steps[row] : 0;
+    const int per_slice = (vocab + slices - 1) / slices;
+    const int begin = blockIdx.x * per_slice;
+    const int end = min(vocab, begin + per_slice);
     float best = -INFINITY;
     int best_index = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
         float score = src[i];
         if (temperature > 0.0f) {
             const float u = uniform_for(seed, step, (uint32_t)i);
@@ -75,14 +81,60 @@ __global__ void sample_kernel(const float* __restrict__ logits, const float* __r
             const int other_index = __shfl_xor_sync(0xffffffffu, best_index, offset);
             take_better(best, best_index, other, other_index);
         }
-        if (lane == 0) out[row] = best_index == 0x7fffffff ? 0 : best_index;
+        if (lane == 0) {
+            if (slices == 1) {
+                out[row] = best_index == 0x7fffffff ? 0 : best_index;
+            } else {
+                partial_scores[row * slices + blockIdx.x] = best;
+                partial_indices[row * slices + blockIdx.x] = best_index;
+            }
+        }
     }
 }
 
+__global__ void sample_merge_kernel(const float* __restrict__ partial_scores, const int* __restrict__ partial_indices,
+                                    int* __restrict__ out, int slices) {
+    const int row = blockIdx.x, lane = threadIdx.x;
+    float best = -INFINITY;
+    int best_index = 0x7fffffff;
+    for (int s = lane; s < slices; s += 32) take_better(best, best_index, partial_scores[row * slices + s], partial_indices[row * slices + s]);
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+        const int other_index = __shfl_xor_sync(0xffffffffu, best_index, offset);
+        take_better(best, best_index, other, other_index);
+    }
+    if (lane == 0) out[row] = best_index == 0x7fffffff ? 0 : best_index;
+}
+
+// How many slices a row of `vocab` logits is scanned in (the caller sizes the scratch by it).
+LLM_EXPORT int llm_sample_slices(int n_rows, int vocab) {
+    if (vocab < 16384) return 1;
+    int slices = (vocab + 8191) / 8192;
+    if (slices > 32) slices = 32;
+    return slices;
+}
+
+// partial_scores / partial_indices: [n_rows, slices] each, needed only when slices > 1.
 LLM_EXPORT int llm_sample(const float* logits, const float* temperatures, const uint64_t* seeds, const int* steps,
-                          int* out, int n_rows, int vocab, cudaStream_t stream) {
+                          int* out, int n_rows, int vocab, float* partial_scores, int* partial_indices,
+                          cudaStream_t stream) {
     if (n_rows == 0) return LLM_OK;
-    const int threads = vocab >= 8192 ? 1024 : 256;
-    sample_kernel<<<n_rows, threads, 0, stream>>>(logits, temperatures, seeds, steps, out, vocab);
-    return llm_check_launch("sample");
+    if (n_rows > 65535) {
+        llm_set_error("sample: at most 65535 rows per launch, got %d", n_rows);
+        return LLM_REFUSED;
+    }
+    const int slices = llm_sample_slices(n_rows, vocab);
+    if (slices > 1 && (partial_scores == nullptr || partial_indices == nullptr)) {
+        llm_set_error("sample: a vocabulary of %d is scanned in %d slices and needs scratch for them", vocab, slices);
+        return LLM_REFUSED;
+    }
+    const int threads = vocab >= 4096 ? 512 : 256;
+    dim3 grid(slices, n_rows);
+    sample_kernel<<<grid, threads, 0, stream>>>(logits, temperatures, seeds, steps, out, vocab, partial_scores,
+                                                partial_indices);
+    int status = llm_check_launch("sample");
+    if (status != LLM_OK || slices == 1) return status;
+    sample_merge_kernel<<<n_rows, 32, 0, stream>>>(partial_scores, partial_indices, out, slices);
+    return llm_check_launch("sample_merge");
 }

@@ -103,8 +103,13 @@ def sample(logits: torch.Tensor, temperatures: Optional[torch.Tensor] = None, se
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     check(out, "sampled tokens", torch.int32)
+    slices = library().llm_sample_slices(rows, vocab)
+    scores = indices = None
+    if slices > 1:      # large vocabularies are scanned by several blocks per row, merged by a second kernel
+        scores = torch.empty((rows, slices), dtype=torch.float32, device=logits.device)
+        indices = torch.empty((rows, slices), dtype=torch.int32, device=logits.device)
     call("llm_sample", logits.data_ptr(), pointer(temperatures), pointer(seeds), pointer(steps), out.data_ptr(), rows,
-         vocab, stream_handle())
+         vocab, pointer(scores), pointer(indices), stream_handle())
     return out
 
 

@@ -280,6 +280,25 @@ def test_sampling_greedy_and_temperature():
     assert drawn[0] != drawn[3] or True  # different steps usually differ; not required
 
 
+def test_sampling_over_a_large_vocabulary():
+    """Vocabularies from 16384 up are scanned by several blocks per row and merged by a second kernel."""
+    from llmserver_b200 import ops
+    vocab = 151936
+    logits = rand((3, vocab), torch.float32, 61, 2.0)
+    logits[1, 150000] = logits[1, 9000] = logits[1].max() + 1.0     # a tie across slices: the lower index wins
+    assert ops.sample(logits).cpu().tolist() == torch.argmax(logits.cpu(), dim=-1).tolist()
+    assert ops.sample(logits)[1].item() == 9000
+    temperatures = torch.tensor([0.7, 1.0, 0.0], dtype=torch.float32, device=DEVICE)
+    seeds = torch.tensor([5, 6, 7], dtype=torch.int64, device=DEVICE)
+    steps = torch.tensor([3, 4, 5], dtype=torch.int32, device=DEVICE)
+    drawn = ops.sample(logits, temperatures, seeds, steps).cpu().tolist()
+    host = logits.cpu()
+    for row in (0, 1):
+        scores = plain_model.gumbel_scores(host[row], temperatures[row].item(), int(seeds[row]), int(steps[row]))
+        assert scores[drawn[row]] >= scores.max() - 1e-4
+    assert drawn[2] == int(torch.argmax(host[2]))
+
+
 def test_sampling_follows_the_distribution():
     from llmserver_b200 import ops
     probabilities = torch.tensor([0.5, 0.25, 0.125, 0.125])
