@@ -1,0 +1,375 @@
+// y[M, N] = x[M, K] * W[N, K]^T in bfloat16 with 32-bit accumulation, for few rows (M <= 64: decode steps
+// and the output head), written for the fifth-generation tensor cores: TMA loads into 128-byte-swizzled
+// shared tiles, tcgen05.mma with the accumulator in tensor memory, tcgen05.ld for the epilogue.
+//
+// With few rows the product is a stream of W through the SM: every weight is read once and used M times.
+// So the roles of the operands are swapped for the hardware: a CTA owns 128 rows of W as the MMA's
+// M = 128 dimension and the (padded) token rows as its N dimension (16..64), walks its share of K in
+// blocks of 64 through a ring of shared-memory stages, and ends with a 128 x M tile of y^T in tensor
+// memory, which the epilogue writes transposed.  When N / 128 tiles are too few to fill 148 SMs, K is
+// split across a thread-block cluster; the partial tiles are added through distributed shared memory in
+// a fixed order (rank 0, 1, ...), so results do not depend on timing.
+//
+// One elected thread issues the TMA copies, one issues the MMAs; mbarriers carry "stage full" (TMA
+// transaction bytes), "stage free" and "accumulator ready" (tcgen05.commit).  Every wait is bounded: a
+// wait that runs out sets an error flag that the host reads, and the CTA still frees its tensor memory
+// and leaves in step with its cluster.
+//
+// Out-of-range rows of W (N not a multiple of 128), token rows beyond M and a K that is no multiple of
+// 64 are zero-filled by TMA.  K must be a multiple of 8 (16-byte row pitch) and the pointers 16-byte
+// aligned; otherwise the launcher refuses and the caller uses the library product.
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace {
+
+constexpr int kBlockRows = 128;     // rows of W per CTA (UMMA M)
+constexpr int kBlockK = 64;         // one 128-byte swizzle atom of bfloat16
+constexpr int kThreads = 128;
+constexpr int kMaxStages = 8;
+constexpr uint32_t kWaitLimit = 1u << 20;
+constexpr int kMaxSplit = 8;
+
+struct GemmParams {
+    void* out;
+    int out_is_f32;
+    int m, n, k;        // tokens, rows of W, inner size
+    int ldc;
+    int token_pad;      // UMMA N: m rounded up to 16
+    int stages;
+    int split;          // cluster size along K
+    int* error_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded wait: false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kWaitLimit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows are 128 bytes, groups of
+// 8 rows are 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_descriptor(uint32_t smem_address) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_address & 0x3FFFF) >> 4);          // start address
+    d |= (uint64_t)1 << 16;                                   // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                         // stride byte offset: 8 rows * 128 bytes
+    d |= (uint64_t)1 << 46;                                   // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                                   // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: bfloat16 x bfloat16 -> float32, both operands K-major, M x N tile.
+__device__ __forceinline__ uint32_t umma_instruction(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load_16(uint32_t address, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(address));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    return rank;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float load_peer(uint32_t local_address, uint32_t rank) {
+    uint32_t remote;
+    float value;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote) : "memory");
+    return value;
+}
+
+__global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                const __grid_constant__ CUtensorMap map_x,
+                                                                const GemmParams p) {
+    extern __shared__ __align__(1024) unsigned char shared_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+    __shared__ __align__(8) uint64_t accum_bar;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int failed;
+
+    // the dynamic region is aligned to 1024 bytes by hand (the swizzle atoms need it)
+    const uint32_t raw = smem_u32(shared_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char* aligned = shared_raw + (base - raw);
+    const uint32_t a_bytes = kBlockRows * kBlockK * 2;               // 16 KiB
+    const uint32_t b_bytes = (uint32_t)p.token_pad * kBlockK * 2;     // 2..8 KiB
+    const uint32_t stage_bytes = a_bytes + ((b_bytes + 1023u) & ~1023u);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = p.split > 1 ? cluster_rank() : 0;
+    const int tile = blockIdx.x / p.split;
+    const int n0 = tile * kBlockRows;
+    const int total_kb = (p.k + kBlockK - 1) / kBlockK;
+    const int kb_begin = (int)((long long)total_kb * rank / p.split);
+    const int kb_end = (int)((long long)total_kb * (rank + 1) / p.split);
+    const int n_kb = kb_end - kb_begin;
+
+    if (threadIdx.x == 0) {
+        failed = 0;
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        mbar_init(smem_u32(&accum_bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {   // this warp owns the tensor-memory allocation (64 columns: up to 64 token columns of float)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(64));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer: TMA copies of the W tile and the token tile of each K block
+        for (int i = 0; i < n_kb; ++i) {
+            const int s = i % p.stages;
+            if (i >= p.stages && !mbar_wait(smem_u32(&empty_bar[s]), ((i / p.stages) - 1) & 1)) {
+                failed = 1;
+                break;
+            }
+            const uint32_t a_dst = base + s * stage_bytes, b_dst = a_dst + a_bytes;
+            const uint32_t bar = smem_u32(&full_bar[s]);
+            mbar_expect_tx(bar, a_bytes + b_bytes);
+            tma_load_2d(a_dst, &map_w, bar, (kb_begin + i) * kBlockK, n0);
+            tma_load_2d(b_dst, &map_x, bar, (kb_begin + i) * kBlockK, 0);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer
+        const uint32_t idesc = umma_instruction(kBlockRows, p.token_pad);
+        bool ok = true;
+        for (int i = 0; i < n_kb && ok; ++i) {
+            const int s = i % p.stages;
+            if (!mbar_wait(smem_u32(&full_bar[s]), (i / p.stages) & 1)) {
+                failed = 1;
+                ok = false;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_src = base + s * stage_bytes, b_src = a_src + a_bytes;
+            const uint64_t desc_a = umma_descriptor(a_src), desc_b = umma_descriptor(b_src);
+#pragma unroll
+            for (int k = 0; k < kBlockK / 16; ++k)   // 16 bfloat16 = 32 bytes further along the swizzled row
+                umma_bf16(tmem_base, desc_a + (uint64_t)(k * 2), desc_b + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+            umma_commit(smem_u32(&empty_bar[s]));     // the stage is free once these MMAs have read it
+        }
+        umma_commit(smem_u32(&accum_bar));            // the accumulator is complete once all MMAs are done
+    }
+
+    // ---- epilogue: all four warps; warp w reads tensor-memory lanes 32 w .. 32 w + 31 = rows of the tile
+    __syncwarp();
+    bool ready = true;
+    if (n_kb > 0) ready = mbar_wait(smem_u32(&accum_bar), 0);
+    if (!ready) failed = 1;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    __syncthreads();            // every copy has landed and every MMA retired (or the wait ran out)
+    const bool bad = failed != 0;
+    if (bad) {
+        // a wait ran out: report it, give copies that may still be in flight time to land, then leave in order
+        if (threadIdx.x == 0) atomicExch(p.error_flag, 2);
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
+
+    const int row = warp * 32 + lane;                 // row of the W tile
+    float* reduce = reinterpret_cast<float*>(aligned);   // [token_pad][128], reuses the stage memory
+    const int n = n0 + row;
+    for (int c0 = 0; c0 < p.token_pad; c0 += 16) {
+        float values[16];
+        if (n_kb > 0 && !bad) {
+            tmem_load_16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, values);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) values[i] = 0.0f;
+        }
+        if (p.split > 1) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) reduce[(c0 + i) * kBlockRows + row] = values[i];
+        } else if (n < p.n) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int m = c0 + i;
+                if (m < p.m) {
+                    if (p.out_is_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldc + n] = values[i];
+                    else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(values[i]);
+                }
+            }
+        }
+    }
+    if (p.split > 1) {
+        cluster_sync();          // every CTA's partial tile is in its shared memory
+        const uint32_t reduce_address = smem_u32(reduce);
+        for (int m = (int)rank; m < p.m; m += p.split) {      // token rows are dealt round-robin to the ranks
+            float total = 0.0f;
+            for (uint32_t peer = 0; peer < (uint32_t)p.split; ++peer)
+                total += load_peer(reduce_address + (uint32_t)(m * kBlockRows + row) * 4u, peer);
+            if (n < p.n) {
+                if (p.out_is_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldc + n] = total;
+                else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(total);
+            }
+        }
+        cluster_sync();          // nobody leaves while a peer may still read its shared memory
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(64));
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled cached = nullptr;
+    if (cached == nullptr) {
+        void* symbol = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &symbol, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            cached = reinterpret_cast<EncodeTiled>(symbol);
+    }
+    return cached;
+}
+
+// Tensor map of a row-major [rows, k] bfloat16 matrix, box = [box_rows, 64] with 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* pointer, int rows, int k, int box_rows) {
+    EncodeTiled encode = encode_tiled();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
+    const cuuint32_t element_strides[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pointer), dims, strides, box, element_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+// 1 when the kernel takes the sizes, else 0 (the caller then uses the library product).
+LLM_EXPORT int llm_gemm_small_m_supports(int m, int n, int k) {
+    return m >= 1 && m <= 64 && n >= 1 && k >= 8 && k % 8 == 0;
+}
+
+LLM_EXPORT int llm_gemm_small_m(const void* x, const void* w, void* out, int m, int n, int k, int ldc, int out_is_f32,
+                                int* error_flag, cudaStream_t stream) {
+    if (m == 0 || n == 0) return LLM_OK;
+    if (!llm_gemm_small_m_supports(m, n, k) || !aligned16(x) || !aligned16(w)) {
+        llm_set_error("gemm_small_m: takes 1..64 rows, K a multiple of 8 and 16-byte aligned operands (got m %d, n %d, k %d)", m, n, k);
+        return LLM_REFUSED;
+    }
+    GemmParams p;
+    p.out = out;
+    p.out_is_f32 = out_is_f32;
+    p.m = m;
+    p.n = n;
+    p.k = k;
+    p.ldc = ldc;
+    p.token_pad = ((m + 15) / 16) * 16;
+    p.error_flag = error_flag;
+    const int tiles = (n + kBlockRows - 1) / kBlockRows;
+    const int total_kb = (k + kBlockK - 1) / kBlockK;
+    // split K across a cluster so that about one wave of 148 SMs is filled; each rank keeps >= 4 K blocks
+    int split = 148 / tiles;
+    if (split > total_kb / 4) split = total_kb / 4;
+    if (split > kMaxSplit) split = kMaxSplit;
+    if (split < 1) split = 1;
+    p.split = split;
+    const size_t a_bytes = (size_t)kBlockRows * kBlockK * 2;
+    const size_t b_bytes = ((size_t)p.token_pad * kBlockK * 2 + 1023) & ~(size_t)1023;
+    const size_t stage_bytes = a_bytes + b_bytes;
+    int stages = (int)((100 * 1024) / stage_bytes);      // about 100 KiB per CTA: two CTAs fit on an SM
+    if (stages > kMaxStages) stages = kMaxStages;
+    const int my_kb = (total_kb + split - 1) / split;
+    if (stages > my_kb) stages = my_kb < 1 ? 1 : my_kb;
+    p.stages = stages;
+    size_t shared = (size_t)stages * stage_bytes;
+    const size_t reduce_bytes = (size_t)p.token_pad * kBlockRows * sizeof(float);
+    if (shared < reduce_bytes) shared = reduce_bytes;
+    shared += 1024;   // room to align the region to 1024 bytes
+
+    CUtensorMap map_w, map_x;
+    if (!make_map(&map_w, w, n, k, kBlockRows) || !make_map(&map_x, x, m, k, p.token_pad)) {
+        llm_set_error("gemm_small_m: cuTensorMapEncodeTiled failed (m %d, n %d, k %d)", m, n, k);
+        return LLM_REFUSED;
+    }
+    static size_t configured = 0;
+    if (shared > configured) {
+        cudaError_t status = cudaFuncSetAttribute(gemm_small_m_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
+        if (status != cudaSuccess) {
+            llm_set_error("gemm_small_m: cannot raise the shared-memory limit: %s", cudaGetErrorString(status));
+            return (int)status;
+        }
+        configured = 200 * 1024;
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)(tiles * split), 1, 1);
+    config.blockDim = dim3(kThreads, 1, 1);
+    config.dynamicSmemBytes = shared;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = (unsigned)split;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = split > 1 ? 1 : 0;
+    cudaError_t status = cudaLaunchKernelEx(&config, gemm_small_m_kernel, map_w, map_x, p);
+    if (status != cudaSuccess) {
+        llm_set_error("gemm_small_m launch: %s", cudaGetErrorString(status));
+        return (int)status;
+    }
+    return llm_check_launch("gemm_small_m");
+}

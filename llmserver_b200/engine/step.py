@@ -134,6 +134,8 @@ class StepFunction:
 
     def check_errors(self) -> None:
         """Reads the kernels' error flags of the steps run since the last check (synchronises)."""
+        from ..ops import gemm_bf16
+        gemm_bf16.check_errors()
         flags, self.pending_flags = self.pending_flags, []
         if flags and int(torch.stack([flag.reshape(()) for flag in flags]).max().item()) != 0:
             raise RuntimeError("a kernel met a block-table entry outside the page pool; the cache bookkeeping is corrupt")

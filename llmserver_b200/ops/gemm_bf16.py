@@ -1,16 +1,106 @@
 """bfloat16 matrix products y = x W^T with 32-bit accumulation.
 
 The reference's engine runs every projection through a library matrix product (nn.Linear on
-cuBLAS: utils/attention.py:119-124,181; utils/layers.py:205-217; utils/model.py:170).  This module
-chooses, per call, between that library product and this package's own kernels.
+cuBLAS: utils/attention.py:119-124,181; utils/layers.py:205-217; utils/model.py:170).  Here:
+
+* up to 64 rows (decode steps, the output head): this package's tcgen05 / TMA kernel
+  (``csrc/gemm_tcgen05.cu``), which streams the weights once and can write float32 directly, or the
+  library product, whichever a one-time measurement per shape finds faster;
+* more rows (prompt portions): the library product (cuBLAS through PyTorch).
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
 
-from .library import KernelError
+from .library import KernelError, call, library, stream_handle
+
+SMALL_M = 64
+_error_flags = {}
+_use_small_m = os.environ.get("LLMSERVER_B200_SMALL_M_GEMM", "1") != "0"
+
+
+def error_flag(device) -> torch.Tensor:
+    """Device word the kernel sets when one of its bounded waits ran out (never expected)."""
+    device = torch.device(device)
+    if device not in _error_flags:
+        _error_flags[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _error_flags[device]
+
+
+def check_errors() -> None:
+    for flag in _error_flags.values():
+        if int(flag.item()) != 0:
+            flag.zero_()
+            raise KernelError("the small-M matrix product gave up waiting on one of its barriers; its result is invalid")
+
+
+def small_m_supported(rows: int, cols: int, inner: int) -> bool:
+    return _use_small_m and bool(library().llm_gemm_small_m_supports(rows, cols, inner))
+
+
+# (row bucket, N, K, out dtype) -> True when this package's kernel is the faster one for that product.
+_choice = {}
+
+
+def _row_bucket(rows: int) -> int:
+    for bucket in (1, 2, 4, 8, 16, 32, 48, 64):
+        if rows <= bucket:
+            return bucket
+    return SMALL_M
+
+
+_flush_buffer = {}
+
+
+def _time_once(run, device, repeats: int = 3) -> float:
+    """Fastest of a few runs, each from a cold L2: a buffer larger than the cache is overwritten before
+    every run, so that the weights come from HBM as they do inside a model step."""
+    if device not in _flush_buffer:
+        _flush_buffer[device] = torch.empty(256 << 20, dtype=torch.int8, device=device)
+    run()
+    best = float("inf")
+    for _ in range(repeats):
+        _flush_buffer[device].zero_()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        run()
+        end.record()
+        end.synchronize()
+        best = min(best, begin.elapsed_time(end))
+    return best
+
+
+def _prefer_small_m(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> bool:
+    """Measures both products once per (rows bucket, shape) and remembers which is faster.  Both read
+    the same operands and give the same result up to rounding, so the choice changes speed only.
+    While a CUDA graph is being captured nothing can be timed: an unknown shape then uses this
+    package's kernel."""
+    rows, inner = x.shape
+    key = (_row_bucket(rows), weight.shape[0], inner, out_dtype)
+    known = _choice.get(key)
+    if known is not None:
+        return known
+    if torch.cuda.is_current_stream_capturing():
+        return True
+    cols = weight.shape[0]
+    out = torch.empty((rows, cols), dtype=out_dtype, device=x.device)
+    flag = error_flag(x.device)
+
+    def ours():
+        call("llm_gemm_small_m", x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, cols, inner, cols,
+             int(out_dtype == torch.float32), flag.data_ptr(), stream_handle())
+
+    def theirs():
+        if out_dtype == torch.bfloat16:
+            torch.matmul(x, weight.t(), out=out)
+        else:
+            out.copy_(torch.matmul(x, weight.t()))
+
+    _choice[key] = _time_once(ours, x.device) <= _time_once(theirs, x.device) * 1.02
+    return _choice[key]
 
 
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -18,6 +108,17 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tenso
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
         raise KernelError(f"linear_bf16 takes bfloat16 operands, got {x.dtype} and {weight.dtype}")
     out_dtype = out_dtype or torch.bfloat16
+    rows, inner = x.shape
+    cols = weight.shape[0]
+    if rows <= SMALL_M and x.is_contiguous() and weight.is_contiguous() and small_m_supported(rows, cols, inner) \
+            and out_dtype in (torch.bfloat16, torch.float32) and _prefer_small_m(x, weight, out_dtype):
+        if out is None:
+            out = torch.empty((rows, cols), dtype=out_dtype, device=x.device)
+        elif out.dtype != out_dtype or not out.is_contiguous() or out.shape != (rows, cols):
+            raise KernelError("linear_bf16: the output tensor does not match")
+        call("llm_gemm_small_m", x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, cols, inner, cols,
+             int(out_dtype == torch.float32), error_flag(x.device).data_ptr(), stream_handle())
+        return out
     if out_dtype == torch.bfloat16:
         if out is not None:
             return torch.matmul(x, weight.t(), out=out)

@@ -108,6 +108,26 @@ def test_linear_bf16():
         close(out32, want, torch.bfloat16, f"linear bf16 -> f32 {(m, n, k)}")
 
 
+@pytest.mark.parametrize("shape", [(1, 300, 128), (8, 509, 96), (64, 1000, 512), (17, 4096, 12288), (33, 200, 4096),
+                                   (5, 128, 64), (3, 130, 72), (48, 6144, 4096), (16, 40000, 1024)])
+def test_gemm_small_m_tcgen05(shape):
+    """The tcgen05 / TMA product for few rows, called directly: ragged N and K, one K block, K split across a
+    cluster (few tiles, long K), float32 and bfloat16 outputs."""
+    from llmserver_b200.ops import gemm_bf16
+    from llmserver_b200.ops.library import call, stream_handle
+    m, n, k = shape
+    assert gemm_bf16.small_m_supported(m, n, k)
+    x, w = rand((m, k), torch.bfloat16, 12), rand((n, k), torch.bfloat16, 13, 0.05)
+    want = x.double() @ w.double().T
+    for out_dtype in (torch.float32, torch.bfloat16):
+        out = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEVICE)
+        call("llm_gemm_small_m", x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, n, int(out_dtype == torch.float32),
+             gemm_bf16.error_flag(DEVICE).data_ptr(), stream_handle())
+        torch.cuda.synchronize()
+        gemm_bf16.check_errors()
+        close(out, want, out_dtype, f"small-M product {shape} -> {out_dtype}", factor=4.0 if out_dtype == torch.float32 else 1.0)
+
+
 def paged(dense_k, dense_v, page_size, seed, dtype):
     """Scatters per-sequence dense K/V ([T, Hkv, D] each) into shuffled pages; returns pages, tables."""
     kv_heads, dim = dense_k[0].shape[1:]
