@@ -20,6 +20,7 @@
 // utils/attention.py:75-96.  Probabilities are rounded to bfloat16 for the P V product; the normaliser
 // is summed in 32-bit from the unrounded values.
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace {
 
@@ -46,6 +47,7 @@ struct AttnParams {
     int max_splits;
     float* partial_out;      // [N, Hq, max_splits, D]
     float* partial_ml;       // [N, Hq, max_splits, 2]
+    int* error_flag;         // set when a bounded wait of the TMA decode kernel runs out (may be null)
 };
 
 __device__ __forceinline__ uint32_t smem_address(const void* pointer) {
@@ -90,6 +92,20 @@ __device__ __forceinline__ int swizzled(int row, int chunk) {
     return row * D + ((chunk ^ (row & 7)) << 3);
 }
 
+// The two shared-memory tile layouts.  XorLayout: rows of D elements, chunks XOR-ed with the row (tiles
+// filled by cp.async).  TmaLayout: what TMA writes with 128-byte swizzle: the tile is split into column
+// halves of 64 elements, each half holds ROWS rows of 128 bytes whose 16-byte chunks are XOR-ed with the row.
+template <int D>
+struct XorLayout {
+    static __device__ __forceinline__ int at(int row, int chunk) { return swizzled<D>(row, chunk); }
+};
+template <int D, int ROWS>
+struct TmaLayout {
+    static __device__ __forceinline__ int at(int row, int chunk) {
+        return (chunk >> 3) * (ROWS * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
+    }
+};
+
 // Loads rows [first_key, first_key + 64) of one kv head into a swizzled shared tile; keys at or past
 // `end_key` are zero-filled.  All 128 threads take part.
 template <int D>
@@ -119,7 +135,7 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_tile, __nv_bfloat1
 // One warp: 16 query rows against NT * 8 keys of a shared tile, starting at tile row `key_row`, whose
 // absolute key index is `key_index`.  Rows g = lane / 4 and g + 8 of the warp see keys in
 // [row_low[h], row_high[h]] (row_high < 0: the row does not exist).
-template <int D, int NT>
+template <int D, int NT, class Layout = XorLayout<D>>
 __device__ __forceinline__ void warp_tile(const uint32_t (&q_frag)[D / 16][4], const __nv_bfloat16* k_tile,
                                           const __nv_bfloat16* v_tile, int key_row, int key_index,
                                           const int (&row_low)[2], const int (&row_high)[2], float scale_log2,
@@ -139,7 +155,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&q_frag)[D / 16][4], c
         for (int pair = 0; pair < NT / 2; ++pair) {
             uint32_t b[4];
             const int row = key_row + pair * 16 + (matrix >> 1) * 8 + matrix_row;
-            ldmatrix_x4(b, smem_address(k_tile + swizzled<D>(row, 2 * ks + (matrix & 1))));
+            ldmatrix_x4(b, smem_address(k_tile + Layout::at(row, 2 * ks + (matrix & 1))));
             mma_bf16(s_acc[2 * pair], q_frag[ks], b[0], b[1]);
             mma_bf16(s_acc[2 * pair + 1], q_frag[ks], b[2], b[3]);
         }
@@ -199,7 +215,7 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&q_frag)[D / 16][4], c
         for (int j = 0; j < D / 16; ++j) {
             uint32_t b[4];
             const int row = key_row + kk * 16 + (matrix & 1) * 8 + matrix_row;
-            ldmatrix_x4_trans(b, smem_address(v_tile + swizzled<D>(row, 2 * j + (matrix >> 1))));
+            ldmatrix_x4_trans(b, smem_address(v_tile + Layout::at(row, 2 * j + (matrix >> 1))));
             mma_bf16(o_acc[2 * j], a, b[0], b[1]);
             mma_bf16(o_acc[2 * j + 1], a, b[2], b[3]);
         }
@@ -460,6 +476,190 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnPa
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// decode with TMA: the same split-KV kernel, but K and V travel page by page as TMA tiles
+// (cp.async.bulk.tensor, 128-byte swizzle) into a ring of kDecodeStages stages, each completion counted
+// by an mbarrier.  One elected thread issues a 64-key tile as (64 / page_size) pages x (D / 64) column
+// halves x {K, V} copies of page_size x 128 bytes; no thread computes addresses per 16 bytes.  Needs a
+// page size of 8, 16, 32 or 64 tokens (whole pages per tile, whole swizzle atoms per page).
+// ------------------------------------------------------------------------------------------------
+constexpr int kDecodeStages = 3;
+constexpr int kDecodeThreads = kThreads + 32;   // four consumer warps and one producer warp
+
+template <int D>
+__global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                                              const __grid_constant__ CUtensorMap map_v,
+                                                                              const AttnParams p) {
+    extern __shared__ __align__(16) unsigned char shared_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kDecodeStages];
+    __shared__ __align__(8) uint64_t empty_bar[kDecodeStages];
+    __shared__ int failed;
+    using Layout = TmaLayout<D, kTileKeys>;
+    constexpr int kHalves = D / 64;
+    constexpr uint32_t kTileBytes = kTileKeys * D * 2;          // one of K or V
+    constexpr uint32_t kStageBytes = 2 * kTileBytes;
+
+    const uint32_t raw = tma::smem_u32(shared_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;                 // swizzle atoms need 1024-byte alignment
+    unsigned char* stages = shared_raw + (base - raw);
+    __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(stages + kDecodeStages * kStageBytes);   // [16][D]
+
+    const int seq = blockIdx.z, kv_head = blockIdx.y, split = blockIdx.x;
+    const int token = p.q_start[seq];
+    if (p.q_start[seq + 1] - token != 1) return;
+    const int group = p.n_q_heads / p.n_kv_heads;
+    const int context = p.context_len[seq];
+    const int position = context - 1;
+    const int low_key = p.window > 0 ? max(0, position - p.window + 1) : 0;
+    const int first_key = (low_key / kTileKeys) * kTileKeys;
+    const int n_splits = (context - first_key + p.split_len - 1) / p.split_len;
+    if (split >= n_splits) return;
+    const int split_begin = first_key + split * p.split_len;
+    const int split_end = min(split_begin + p.split_len, context);
+    const int n_tiles = (split_end - split_begin + kTileKeys - 1) / kTileKeys;
+    const int* table = p.block_tables + (size_t)seq * p.max_blocks;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        failed = 0;
+        for (int s = 0; s < kDecodeStages; ++s) {
+            tma::mbar_init(tma::smem_u32(&full_bar[s]), 1);
+            tma::mbar_init(tma::smem_u32(&empty_bar[s]), 4);      // one arrival per consumer warp
+        }
+        tma::mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == 4) {
+        // ---- producer warp.  A tile is (64 / page_size) pages x (D / 64) column halves x {K, V} copies of
+        // page_size x 128 bytes; each lane issues one of them.  Every tile is copied whole: pages past the
+        // end of the sequence come from whatever the (zero-padded) block table names there, an existing
+        // page whose finite contents are masked out, so no row of a stage holds bits that were not loaded.
+        const int pages_per_tile = kTileKeys / p.page_size;
+        const int copies = pages_per_tile * kHalves * 2;
+        const int my_page = lane / (kHalves * 2), my_half = (lane / 2) % kHalves, my_v = lane & 1;
+        for (int t = 0; t < n_tiles; ++t) {
+            const int s = t % kDecodeStages;
+            bool ok = true;
+            if (t >= kDecodeStages) ok = tma::mbar_wait(tma::smem_u32(&empty_bar[s]), ((t / kDecodeStages) - 1) & 1);
+            if (!ok) {
+                failed = 1;
+                break;
+            }
+            const uint32_t bar = tma::smem_u32(&full_bar[s]);
+            if (lane == 0) tma::mbar_expect_tx(bar, 2u * kTileBytes);
+            __syncwarp();
+            if (lane < copies) {
+                const int key = split_begin + t * kTileKeys + my_page * p.page_size;
+                const int page = table[min(key / p.page_size, p.max_blocks - 1)];
+                const int y = (page * p.n_kv_heads + kv_head) * p.page_size;
+                const uint32_t dst = base + s * kStageBytes + (my_v ? kTileBytes : 0u) + my_half * (kTileKeys * 128u) +
+                                     (uint32_t)(my_page * p.page_size) * 128u;
+                tma::load_2d(dst, my_v ? &map_v : &map_k, bar, my_half * 64, y);
+            }
+        }
+        return;
+    }
+
+    // ---- consumer warps: gather Q (plain loads into the XOR layout), then walk the tiles
+    {
+        constexpr int kChunks = D / 8;
+        for (int c = threadIdx.x; c < 16 * kChunks; c += kThreads) {
+            const int row = c / kChunks, chunk = c % kChunks;
+            uint4 value = make_uint4(0, 0, 0, 0);
+            if (row < group)
+                value = *reinterpret_cast<const uint4*>(p.q + (size_t)token * p.q_stride + (size_t)(kv_head * group + row) * D + chunk * 8);
+            *reinterpret_cast<uint4*>(q_tile + swizzled<D>(row, chunk)) = value;
+        }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");     // the four consumer warps only
+    const int g = lane >> 2;
+    int row_low[2], row_high[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const bool exists = g + 8 * h < group;
+        row_high[h] = exists ? position : -1;
+        row_low[h] = low_key;
+    }
+    float o_acc[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o_acc[n][i] = 0.0f;
+    float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
+    uint32_t q_frag[D / 16][4];
+    {
+        const int matrix = lane >> 3, matrix_row = lane & 7;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            const int row = (matrix & 1) * 8 + matrix_row;
+            ldmatrix_x4(q_frag[ks], smem_address(q_tile + swizzled<D>(row, 2 * ks + (matrix >> 1))));
+        }
+    }
+
+    bool ok = true;
+    for (int it = 0; it < n_tiles; ++it) {
+        const int s = it % kDecodeStages;
+        if (ok && !tma::mbar_wait(tma::smem_u32(&full_bar[s]), (it / kDecodeStages) & 1)) ok = false;
+        const __nv_bfloat16* k_tile = reinterpret_cast<const __nv_bfloat16*>(stages + s * kStageBytes);
+        const __nv_bfloat16* v_tile = k_tile + kTileKeys * D;
+        const int key_index = split_begin + it * kTileKeys + warp * 16;
+        if (key_index < split_end)
+            warp_tile<D, 2, Layout>(q_frag, k_tile, v_tile, warp * 16, key_index, row_low, row_high, p.scale_log2, o_acc, row_max, row_sum);
+        __syncwarp();
+        if (lane == 0) tma::mbar_arrive(tma::smem_u32(&empty_bar[s]));     // this warp is done with the stage
+    }
+    if (!ok) failed = 1;
+    asm volatile("bar.sync 1, 128;" ::: "memory");     // all tiles consumed; the stages can be reused
+    if (failed && threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 3);
+
+    // merge the four warps through shared memory (every copy has landed: each tile was waited for)
+    float* merge = reinterpret_cast<float*>(stages);        // [4 warps][16 rows][D + 2]
+    const int t = lane & 3;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float total = row_sum[h];
+        total += __shfl_xor_sync(0xffffffffu, total, 1);
+        total += __shfl_xor_sync(0xffffffffu, total, 2);
+        float* row = merge + ((size_t)warp * 16 + g + 8 * h) * (D + 2);
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            row[n * 8 + 2 * t] = o_acc[n][2 * h];
+            row[n * 8 + 2 * t + 1] = o_acc[n][2 * h + 1];
+        }
+        if (t == 0) {
+            row[D] = row_max[h];
+            row[D + 1] = total;
+        }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    for (int index = threadIdx.x; index < group * D; index += kThreads) {
+        const int r = index / D, d = index % D;
+        float best = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) best = fmaxf(best, merge[((size_t)w * 16 + r) * (D + 2) + D]);
+        float numerator = 0.0f, denominator = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float* row = merge + ((size_t)w * 16 + r) * (D + 2);
+            const float weight = row[D] == -INFINITY ? 0.0f : exp2f(row[D] - best);
+            numerator += row[d] * weight;
+            denominator += row[D + 1] * weight;
+        }
+        const int head = kv_head * group + r;
+        if (n_splits == 1) {
+            p.out[(size_t)token * p.n_q_heads * D + (size_t)head * D + d] = __float2bfloat16_rn(numerator / denominator);
+        } else {
+            const size_t slot = ((size_t)token * p.n_q_heads + head) * p.max_splits + split;
+            p.partial_out[slot * D + d] = numerator / denominator;
+            if (d == 0) {
+                p.partial_ml[slot * 2] = best;
+                p.partial_ml[slot * 2 + 1] = denominator;
+            }
+        }
+    }
+}
+
 // out = sum_s O_s * l_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)   (utils/paged_attention.py:220-237)
 template <int D>
 __global__ void attention_decode_merge_kernel(const AttnParams p) {
@@ -503,7 +703,7 @@ int launch_portions(const AttnParams& p, int total_tiles, cudaStream_t stream) {
 }
 
 template <int D>
-int launch_decode(const AttnParams& p, cudaStream_t stream) {
+int launch_decode_cp_async(const AttnParams& p, cudaStream_t stream) {
     size_t shared = (size_t)(16 * D + 4 * kTileKeys * D) * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)4 * 16 * (D + 2) * sizeof(float) + 16 * D * sizeof(__nv_bfloat16);
     if (merge > shared) shared = merge;
@@ -518,7 +718,38 @@ int launch_decode(const AttnParams& p, cudaStream_t stream) {
     }
     dim3 grid(p.max_splits, p.n_kv_heads, p.n_seqs);
     attention_decode_kernel<D><<<grid, kThreads, shared, stream>>>(p);
-    int status = llm_check_launch("attention_decode");
+    return llm_check_launch("attention_decode");
+}
+
+template <int D>
+int launch_decode_tma(const AttnParams& p, cudaStream_t stream) {
+    // rows of the page pool seen as a [pages * kv_heads * page_size, D] matrix; the extent only bounds
+    // address generation, so a generous one is fine when the number of pages is not known
+    const uint64_t rows = (uint64_t)1 << 30;
+    CUtensorMap map_k, map_v;
+    if (!tma::make_map_bf16(&map_k, p.k_pages, rows, D, (uint32_t)p.page_size) ||
+        !tma::make_map_bf16(&map_v, p.v_pages, rows, D, (uint32_t)p.page_size))
+        return launch_decode_cp_async<D>(p, stream);
+    const size_t shared = (size_t)kDecodeStages * 2 * kTileKeys * D * 2 + (size_t)16 * D * 2 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t status = cudaFuncSetAttribute(attention_decode_tma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        if (status != cudaSuccess) {
+            llm_set_error("attention_decode_tma: cannot get %zu bytes of shared memory: %s", shared, cudaGetErrorString(status));
+            return (int)status;
+        }
+        configured = true;
+    }
+    dim3 grid(p.max_splits, p.n_kv_heads, p.n_seqs);
+    attention_decode_tma_kernel<D><<<grid, kDecodeThreads, shared, stream>>>(map_k, map_v, p);
+    return llm_check_launch("attention_decode_tma");
+}
+
+template <int D>
+int launch_decode(const AttnParams& p, cudaStream_t stream) {
+    const bool whole_pages = p.page_size >= 8 && p.page_size <= kTileKeys && kTileKeys % p.page_size == 0 && p.page_size % 8 == 0;
+    int status = (whole_pages && aligned16(p.k_pages) && aligned16(p.v_pages)) ? launch_decode_tma<D>(p, stream)
+                                                                                : launch_decode_cp_async<D>(p, stream);
     if (status != LLM_OK || p.max_splits <= 1) return status;
     dim3 merge_grid(p.n_q_heads, p.n_seqs);
     attention_decode_merge_kernel<D><<<merge_grid, D < 128 ? D : 128, 0, stream>>>(p);
@@ -542,7 +773,7 @@ LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, const void* k_page
                                  void* out, int n_seqs, int n_q_heads, int n_kv_heads, int head_dim, int page_size,
                                  float scale, int window, int run_portions, int total_tiles, int run_decode,
                                  int split_len, int max_splits, float* partial_out, float* partial_ml,
-                                 cudaStream_t stream) {
+                                 int* error_flag, cudaStream_t stream) {
     if (!llm_attention_mma_supports(head_dim, n_q_heads, n_kv_heads)) {
         llm_set_error("attention_mma: head_dim %d with %d/%d heads is not supported (head_dim 64 or 128, group <= 16)",
                       head_dim, n_q_heads, n_kv_heads);
@@ -577,6 +808,7 @@ LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, const void* k_page
     p.max_splits = max_splits;
     p.partial_out = partial_out;
     p.partial_ml = partial_ml;
+    p.error_flag = error_flag;
     int status = LLM_OK;
     if (run_portions && total_tiles > 0)
         status = head_dim == 128 ? launch_portions<128>(p, total_tiles, stream) : launch_portions<64>(p, total_tiles, stream);
@@ -664,5 +896,6 @@ LLM_EXPORT int llm_attention_decode_noalloc(const void* q, int q_stride, const v
     p.max_splits = max_splits;
     p.partial_out = g_noalloc_address[device];                       // [slots][head_dim]
     p.partial_ml = g_noalloc_address[device] + slots * head_dim;      // [slots][2]
+    p.error_flag = nullptr;
     return head_dim == 128 ? launch_decode<128>(p, stream) : launch_decode<64>(p, stream);
 }

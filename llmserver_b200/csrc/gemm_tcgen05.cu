@@ -19,8 +19,7 @@
 // 64 are zero-filled by TMA.  K must be a multiple of 8 (16-byte row pitch) and the pointers 16-byte
 // aligned; otherwise the launcher refuses and the caller uses the library product.
 #include "common.cuh"
-
-#include <cuda.h>
+#include "tma.cuh"
 
 namespace {
 
@@ -28,7 +27,6 @@ constexpr int kBlockRows = 128;     // rows of W per CTA (UMMA M)
 constexpr int kBlockK = 64;         // one 128-byte swizzle atom of bfloat16
 constexpr int kThreads = 128;
 constexpr int kMaxStages = 8;
-constexpr uint32_t kWaitLimit = 1u << 20;
 constexpr int kMaxSplit = 8;
 
 struct GemmParams {
@@ -42,35 +40,13 @@ struct GemmParams {
     int* error_flag;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-// Bounded wait: false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kWaitLimit; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
+using tma::mbar_expect_tx;
+using tma::mbar_init;
+using tma::mbar_wait;
+using tma::smem_u32;
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-        : "memory");
+    tma::load_2d(dst, map, bar, x, y);
 }
 
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows are 128 bytes, groups of
@@ -161,7 +137,7 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
         mbar_init(smem_u32(&accum_bar), 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        tma::mbar_fence_init();
     }
     if (warp == 1) {   // this warp owns the tensor-memory allocation (64 columns: up to 64 token columns of float)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(64));
@@ -267,33 +243,9 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(64));
 }
 
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_tiled() {
-    static EncodeTiled cached = nullptr;
-    if (cached == nullptr) {
-        void* symbol = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &symbol, cudaEnableDefault, &result) == cudaSuccess &&
-            result == cudaDriverEntryPointSuccess)
-            cached = reinterpret_cast<EncodeTiled>(symbol);
-    }
-    return cached;
-}
-
 // Tensor map of a row-major [rows, k] bfloat16 matrix, box = [box_rows, 64] with 128-byte swizzle.
 bool make_map(CUtensorMap* map, const void* pointer, int rows, int k, int box_rows) {
-    EncodeTiled encode = encode_tiled();
-    if (encode == nullptr) return false;
-    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
-    const cuuint32_t element_strides[2] = {1, 1};
-    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pointer), dims, strides, box, element_strides,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return tma::make_map_bf16(map, pointer, (uint64_t)rows, (uint64_t)k, (uint32_t)box_rows);
 }
 
 }  // namespace

@@ -1,0 +1,82 @@
+// mbarrier and TMA (cp.async.bulk.tensor) helpers shared by the kernels that stage tiles with the
+// tensor memory accelerator, and the host-side construction of tensor maps.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tma {
+
+constexpr uint32_t kWaitLimit = 1u << 20;   // polls of a barrier before a wait gives up
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded wait: false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kWaitLimit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+// Tile (x = innermost coordinate in elements, y = row) -> shared memory, completion on the mbarrier.
+__device__ __forceinline__ void load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+// Makes earlier generic-proxy writes to shared memory visible to the async proxy (TMA).
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiled encode_tiled() {
+    static EncodeTiled cached = nullptr;
+    if (cached == nullptr) {
+        void* symbol = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &symbol, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            cached = reinterpret_cast<EncodeTiled>(symbol);
+    }
+    return cached;
+}
+
+// Tensor map of a row-major [rows, columns] bfloat16 matrix (row pitch = columns), box = [box_rows, 64
+// columns], 128-byte swizzle, zero fill outside the matrix.
+inline bool make_map_bf16(CUtensorMap* map, const void* pointer, uint64_t rows, uint64_t columns, uint32_t box_rows) {
+    EncodeTiled encode = encode_tiled();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)columns, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)columns * 2};
+    const cuuint32_t box[2] = {64u, box_rows};
+    const cuuint32_t element_strides[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pointer), dims, strides, box, element_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace tma

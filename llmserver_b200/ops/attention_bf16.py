@@ -6,11 +6,12 @@ from __future__ import annotations
 
 import torch
 
+from . import gemm_bf16
 from .library import call, check, library, stream_handle
 
 TILE = 64          # rows per block of the portions kernel, keys per tile of both kernels
 MIN_SPLIT = 256    # fewest keys one decode block walks
-TARGET_BLOCKS = 592   # 4 blocks per SM on 148 SMs
+TARGET_BLOCKS = 296   # one wave of two blocks per SM on 148 SMs
 
 
 def supported(head_dim: int, n_q_heads: int, n_kv_heads: int) -> bool:
@@ -62,5 +63,5 @@ def try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_head
          block_tables.shape[-1], batch.q_start.data_ptr(), batch.context_len.data_ptr(), out.data_ptr(), batch.n_seqs,
          n_q_heads, n_kv_heads, head_dim, k_pages.shape[2], float(scale), int(window), int(run_portions), tiles,
          int(run_decode), split_len, max_splits, 0 if partial_out is None else partial_out.data_ptr(),
-         0 if partial_ml is None else partial_ml.data_ptr(), stream_handle())
+         0 if partial_ml is None else partial_ml.data_ptr(), gemm_bf16.error_flag(qkv.device).data_ptr(), stream_handle())
     return out

@@ -34,7 +34,7 @@ def check_errors() -> None:
     for flag in _error_flags.values():
         if int(flag.item()) != 0:
             flag.zero_()
-            raise KernelError("the small-M matrix product gave up waiting on one of its barriers; its result is invalid")
+            raise KernelError("a kernel gave up waiting on one of its barriers (TMA or MMA completion); the step's result is invalid")
 
 
 def small_m_supported(rows: int, cols: int, inner: int) -> bool:
