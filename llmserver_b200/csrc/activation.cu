@@ -7,6 +7,8 @@
 template <typename T>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int intermediate,
                                     size_t total_vectors) {
+    pdl_trigger();   // let the next kernel start launching
+    pdl_wait();      // everything before this kernel in the stream is complete and visible
     constexpr int kCount = Vec16<T>::kCount;
     const int vectors_per_row = intermediate / kCount;
     for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < total_vectors; v += (size_t)gridDim.x * blockDim.x) {
@@ -24,6 +26,8 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict
 
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int intermediate, size_t total) {
+    pdl_trigger();   // let the next kernel start launching
+    pdl_wait();      // everything before this kernel in the stream is complete and visible
     for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
         const size_t row = e / intermediate;
         const int column = (int)(e % intermediate);
@@ -44,10 +48,10 @@ LLM_EXPORT int llm_silu_mul(const void* gate_up, void* out, int n_rows, int inte
     size_t blocks = (work + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (vector_form) {
-        LLM_DISPATCH_DTYPE(dtype, (silu_mul_vec_kernel<T><<<(unsigned)blocks, threads, 0, stream>>>(
+        LLM_DISPATCH_DTYPE(dtype, (llm_launch(silu_mul_vec_kernel<T>, (unsigned)blocks, threads, 0, stream, 
                                       (const T*)gate_up, (T*)out, intermediate, work)));
     } else {
-        LLM_DISPATCH_DTYPE(dtype, (silu_mul_kernel<T><<<(unsigned)blocks, threads, 0, stream>>>(
+        LLM_DISPATCH_DTYPE(dtype, (llm_launch(silu_mul_kernel<T>, (unsigned)blocks, threads, 0, stream, 
                                       (const T*)gate_up, (T*)out, intermediate, work)));
     }
     return llm_check_launch("silu_mul");

@@ -22,6 +22,8 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, int q_stride, 
                                          int max_blocks, const int* __restrict__ seq_of_token,
                                          const int* __restrict__ positions, T* __restrict__ out, int n_q_heads,
                                          int n_kv_heads, int head_dim, int page_size, float scale, int window) {
+    pdl_trigger();   // let the next kernel start launching
+    pdl_wait();      // everything before this kernel in the stream is complete and visible
     extern __shared__ float q_shared[];  // [warps][head_dim]
     const int token = blockIdx.y;
     const int warps_per_block = blockDim.x >> 5;
@@ -106,7 +108,7 @@ LLM_EXPORT int llm_attention_generic(const void* q, int q_stride, const void* k_
     const int warps = 4;
     dim3 grid((n_q_heads + warps - 1) / warps, n_tokens);
     const size_t shared = (size_t)warps * head_dim * sizeof(float);
-    LLM_DISPATCH_DTYPE(dtype, (attention_generic_kernel<T><<<grid, warps * 32, shared, stream>>>(
+    LLM_DISPATCH_DTYPE(dtype, (llm_launch(attention_generic_kernel<T>, grid, warps * 32, shared, stream, 
                                   (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_tables,
                                   max_blocks, seq_of_token, positions, (T*)out, n_q_heads, n_kv_heads, head_dim,
                                   page_size, scale, window)));

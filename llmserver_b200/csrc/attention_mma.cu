@@ -227,6 +227,8 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&q_frag)[D / 16][4], c
 // ------------------------------------------------------------------------------------------------
 template <int D>
 __global__ void __launch_bounds__(kThreads) attention_portions_kernel(const AttnParams p) {
+    pdl_trigger();   // let the next kernel start launching
+    pdl_wait();      // everything before this kernel in the stream is complete and visible
     extern __shared__ __align__(16) unsigned char shared_raw[];
     __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(shared_raw);   // [64][D]
     __nv_bfloat16* kv_tiles = q_tile + kTileRows * D;                        // [2 stages][K, V][64][D]
@@ -352,6 +354,8 @@ __global__ void __launch_bounds__(kThreads) attention_portions_kernel(const Attn
 // ------------------------------------------------------------------------------------------------
 template <int D>
 __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnParams p) {
+    pdl_trigger();   // let the next kernel start launching
+    pdl_wait();      // everything before this kernel in the stream is complete and visible
     extern __shared__ __align__(16) unsigned char shared_raw[];
     __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(shared_raw);   // [16][D]
     __nv_bfloat16* kv_tiles = q_tile + 16 * D;                               // [2 stages][K, V][64][D]
@@ -490,6 +494,8 @@ template <int D>
 __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                               const __grid_constant__ CUtensorMap map_v,
                                                                               const AttnParams p) {
+    pdl_trigger();   // let the next kernel start launching
+    pdl_wait();      // everything before this kernel in the stream is complete and visible
     extern __shared__ __align__(16) unsigned char shared_raw[];
     __shared__ __align__(8) uint64_t full_bar[kDecodeStages];
     __shared__ __align__(8) uint64_t empty_bar[kDecodeStages];
@@ -663,6 +669,8 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
 // out = sum_s O_s * l_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)   (utils/paged_attention.py:220-237)
 template <int D>
 __global__ void attention_decode_merge_kernel(const AttnParams p) {
+    pdl_trigger();   // let the next kernel start launching
+    pdl_wait();      // everything before this kernel in the stream is complete and visible
     const int seq = blockIdx.y, head = blockIdx.x;
     const int token = p.q_start[seq];
     if (p.q_start[seq + 1] - token != 1) return;
@@ -698,7 +706,7 @@ int launch_portions(const AttnParams& p, int total_tiles, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid(total_tiles, p.n_kv_heads);
-    attention_portions_kernel<D><<<grid, kThreads, shared, stream>>>(p);
+    llm_launch(attention_portions_kernel<D>, grid, kThreads, shared, stream, p);
     return llm_check_launch("attention_portions");
 }
 
@@ -717,7 +725,7 @@ int launch_decode_cp_async(const AttnParams& p, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid(p.max_splits, p.n_kv_heads, p.n_seqs);
-    attention_decode_kernel<D><<<grid, kThreads, shared, stream>>>(p);
+    llm_launch(attention_decode_kernel<D>, grid, kThreads, shared, stream, p);
     return llm_check_launch("attention_decode");
 }
 
@@ -741,7 +749,7 @@ int launch_decode_tma(const AttnParams& p, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid(p.max_splits, p.n_kv_heads, p.n_seqs);
-    attention_decode_tma_kernel<D><<<grid, kDecodeThreads, shared, stream>>>(map_k, map_v, p);
+    llm_launch(attention_decode_tma_kernel<D>, grid, kDecodeThreads, shared, stream, map_k, map_v, p);
     return llm_check_launch("attention_decode_tma");
 }
 
@@ -752,7 +760,7 @@ int launch_decode(const AttnParams& p, cudaStream_t stream) {
                                                                                 : launch_decode_cp_async<D>(p, stream);
     if (status != LLM_OK || p.max_splits <= 1) return status;
     dim3 merge_grid(p.n_q_heads, p.n_seqs);
-    attention_decode_merge_kernel<D><<<merge_grid, D < 128 ? D : 128, 0, stream>>>(p);
+    llm_launch(attention_decode_merge_kernel<D>, merge_grid, D < 128 ? D : 128, 0, stream, p);
     return llm_check_launch("attention_decode_merge");
 }
 

@@ -18,6 +18,33 @@ enum : int { LLM_OK = 0, LLM_REFUSED = -1 };
 void llm_set_error(const char* format, ...);
 int llm_check_launch(const char* what);
 
+// Programmatic dependent launch: a kernel launched with the attribute below may start while the kernel
+// before it in the stream is still running; it calls pdl_wait() before it touches anything that kernel
+// wrote (or anything it will overwrite), and pdl_trigger() as early as possible so that its own successor
+// can start.  Without the attribute both calls do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool llm_pdl_enabled();
+
+// Launches `kernel` on `stream` with programmatic stream serialization (unless switched off with
+// LLMSERVER_B200_PDL=0).  Every kernel launched this way begins with pdl_trigger(); pdl_wait();
+template <typename... Params, typename... Args>
+inline void llm_launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared, cudaStream_t stream,
+                       Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = llm_pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);   // errors surface in llm_check_launch
+}
+
 template <typename T>
 struct Num;
 

@@ -5,6 +5,8 @@
 template <typename T>
 __global__ void embedding_gather_kernel(float* __restrict__ out, const T* __restrict__ table,
                                         const int* __restrict__ ids, int hidden, int vocab, int vector_form) {
+    pdl_trigger();   // let the next kernel start launching
+    pdl_wait();      // everything before this kernel in the stream is complete and visible
     const int token = blockIdx.x;
     int id = ids[token];
     // ids are validated on the host; clamp so that a bad id can never read outside the table
@@ -28,7 +30,7 @@ LLM_EXPORT int llm_embedding_gather(float* out, const void* table, const int* id
     const int vector_form = hidden % 8 == 0 && aligned16(out) && aligned16(table);
     int threads = vector_form ? (hidden / 8 + 31) / 32 * 32 : (hidden >= 1024 ? 256 : 128);
     if (threads > 512) threads = 512;
-    LLM_DISPATCH_DTYPE(dtype, (embedding_gather_kernel<T><<<n_tokens, threads, 0, stream>>>(
+    LLM_DISPATCH_DTYPE(dtype, (llm_launch(embedding_gather_kernel<T>, n_tokens, threads, 0, stream, 
                                   out, (const T*)table, ids, hidden, vocab, vector_form)));
     return llm_check_launch("embedding_gather");
 }

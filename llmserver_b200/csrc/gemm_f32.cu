@@ -14,6 +14,8 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;  // 256 threads, 4x4 ou
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__ a, const float* __restrict__ w,
                                                        float* __restrict__ c, int m_total, int n_total, int k_total,
                                                        int lda, int ldw, int ldc) {
+    pdl_trigger();   // let the next kernel start launching
+    pdl_wait();      // everything before this kernel in the stream is complete and visible
     __shared__ float a_tile[BK][BM + 4];
     __shared__ float w_tile[BK][BN + 4];
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -71,6 +73,6 @@ LLM_EXPORT int llm_gemm_f32(const float* a, const float* w, float* c, int m, int
         return LLM_REFUSED;
     }
     dim3 grid((n + BN - 1) / BN, blocks_m);
-    gemm_f32_kernel<<<grid, 256, 0, stream>>>(a, w, c, m, n, k, lda, ldw, ldc);
+    llm_launch(gemm_f32_kernel, grid, 256, 0, stream, a, w, c, m, n, k, lda, ldw, ldc);
     return llm_check_launch("gemm_f32");
 }

@@ -21,12 +21,14 @@
 #include "common.cuh"
 #include "tma.cuh"
 
+#include <stdlib.h>
+
 namespace {
 
 constexpr int kBlockRows = 128;     // rows of W per CTA (UMMA M)
 constexpr int kBlockK = 64;         // one 128-byte swizzle atom of bfloat16
 constexpr int kThreads = 128;
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 12;
 constexpr int kMaxSplit = 8;
 
 struct GemmParams {
@@ -121,6 +123,7 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
     const uint32_t b_bytes = (uint32_t)p.token_pad * kBlockK * 2;     // 2..8 KiB
     const uint32_t stage_bytes = a_bytes + ((b_bytes + 1023u) & ~1023u);
 
+    pdl_trigger();   // let the next kernel start launching
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = p.split > 1 ? cluster_rank() : 0;
     const int tile = blockIdx.x / p.split;
@@ -149,10 +152,21 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
     const uint32_t tmem_base = tmem_base_slot;
 
     if (warp == 0 && lane == 0) {
-        // ---- producer: TMA copies of the W tile and the token tile of each K block
-        for (int i = 0; i < n_kb; ++i) {
+        // ---- producer: TMA copies of the W tile and the token tile of each K block.  The weights do not
+        // depend on the kernel before this one, so the W tiles of the first ring of stages are requested
+        // before pdl_wait(); the token tiles, which that kernel may just have written, after it.
+        const int first = n_kb < p.stages ? n_kb : p.stages;
+        for (int i = 0; i < first; ++i) {
+            const uint32_t bar = smem_u32(&full_bar[i]);
+            mbar_expect_tx(bar, a_bytes + b_bytes);
+            tma_load_2d(base + i * stage_bytes, &map_w, bar, (kb_begin + i) * kBlockK, n0);
+        }
+        pdl_wait();
+        for (int i = 0; i < first; ++i)
+            tma_load_2d(base + i * stage_bytes + a_bytes, &map_x, smem_u32(&full_bar[i]), (kb_begin + i) * kBlockK, 0);
+        for (int i = first; i < n_kb; ++i) {
             const int s = i % p.stages;
-            if (i >= p.stages && !mbar_wait(smem_u32(&empty_bar[s]), ((i / p.stages) - 1) & 1)) {
+            if (!mbar_wait(smem_u32(&empty_bar[s]), ((i / p.stages) - 1) & 1)) {
                 failed = 1;
                 break;
             }
@@ -186,6 +200,7 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
 
     // ---- epilogue: all four warps; warp w reads tensor-memory lanes 32 w .. 32 w + 31 = rows of the tile
     __syncwarp();
+    pdl_wait();     // global memory is written below: the kernels before this one must be done with it
     bool ready = true;
     if (n_kb > 0) ready = mbar_wait(smem_u32(&accum_bar), 0);
     if (!ready) failed = 1;
@@ -282,7 +297,16 @@ LLM_EXPORT int llm_gemm_small_m(const void* x, const void* w, void* out, int m, 
     const size_t a_bytes = (size_t)kBlockRows * kBlockK * 2;
     const size_t b_bytes = ((size_t)p.token_pad * kBlockK * 2 + 1023) & ~(size_t)1023;
     const size_t stage_bytes = a_bytes + b_bytes;
-    int stages = (int)((100 * 1024) / stage_bytes);      // about 100 KiB per CTA: two CTAs fit on an SM
+    // The ring of stages (about 100 KiB: two CTAs fit on an SM) lets a CTA that was launched early, while the kernels
+    // before it still run, request that many bytes of weights before it has to wait for its input.
+    static int ring_kib = -1;
+    if (ring_kib < 0) {
+        const char* value = getenv("LLMSERVER_B200_GEMM_RING_KIB");
+        ring_kib = value ? atoi(value) : 100;
+        if (ring_kib < 32) ring_kib = 32;
+        if (ring_kib > 200) ring_kib = 200;
+    }
+    int stages = (int)(((size_t)ring_kib * 1024) / stage_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
     const int my_kb = (total_kb + split - 1) / split;
     if (stages > my_kb) stages = my_kb < 1 ? 1 : my_kb;
@@ -299,25 +323,34 @@ LLM_EXPORT int llm_gemm_small_m(const void* x, const void* w, void* out, int m, 
     }
     static size_t configured = 0;
     if (shared > configured) {
-        cudaError_t status = cudaFuncSetAttribute(gemm_small_m_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
+        cudaError_t status = cudaFuncSetAttribute(gemm_small_m_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(226 * 1024));
         if (status != cudaSuccess) {
             llm_set_error("gemm_small_m: cannot raise the shared-memory limit: %s", cudaGetErrorString(status));
             return (int)status;
         }
-        configured = 200 * 1024;
+        configured = 226 * 1024;
     }
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)(tiles * split), 1, 1);
     config.blockDim = dim3(kThreads, 1, 1);
     config.dynamicSmemBytes = shared;
     config.stream = stream;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeClusterDimension;
-    attribute[0].val.clusterDim.x = (unsigned)split;
-    attribute[0].val.clusterDim.y = 1;
-    attribute[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attribute[2];
+    int count = 0;
+    if (llm_pdl_enabled()) {
+        attribute[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute[count].val.programmaticStreamSerializationAllowed = 1;
+        ++count;
+    }
+    if (split > 1) {
+        attribute[count].id = cudaLaunchAttributeClusterDimension;
+        attribute[count].val.clusterDim.x = (unsigned)split;
+        attribute[count].val.clusterDim.y = 1;
+        attribute[count].val.clusterDim.z = 1;
+        ++count;
+    }
     config.attrs = attribute;
-    config.numAttrs = split > 1 ? 1 : 0;
+    config.numAttrs = count;
     cudaError_t status = cudaLaunchKernelEx(&config, gemm_small_m_kernel, map_w, map_x, p);
     if (status != cudaSuccess) {
         llm_set_error("gemm_small_m launch: %s", cudaGetErrorString(status));

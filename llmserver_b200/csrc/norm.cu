@@ -24,6 +24,8 @@ template <typename T, typename W>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                        const W* __restrict__ weight, T* __restrict__ out,
                                        const int* __restrict__ rows, int width, float eps, int write_residual) {
+    pdl_trigger();   // let the next kernel start launching
+    pdl_wait();      // everything before this kernel in the stream is complete and visible
     __shared__ float scratch[33];
     const int o = blockIdx.x;
     const int r = rows ? rows[o] : o;
@@ -68,6 +70,8 @@ template <typename T, typename W>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                    const W* __restrict__ weight, T* __restrict__ out,
                                    const int* __restrict__ rows, int width, float eps, int write_residual) {
+    pdl_trigger();   // let the next kernel start launching
+    pdl_wait();      // everything before this kernel in the stream is complete and visible
     __shared__ float scratch[33];
     const int o = blockIdx.x;
     const int r = rows ? rows[o] : o;
@@ -97,6 +101,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
 template <typename T, typename W>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, const W* __restrict__ weight, T* __restrict__ out,
                                int width, float eps) {
+    pdl_trigger();   // let the next kernel start launching
+    pdl_wait();      // everything before this kernel in the stream is complete and visible
     __shared__ float scratch[33];
     const T* src = x + (size_t)blockIdx.x * width;
     float sum_squares = 0.0f;
@@ -125,13 +131,13 @@ LLM_EXPORT int llm_add_rmsnorm(float* residual, const void* delta, const void* w
                              aligned16(delta) && aligned16(weight) && chunks <= threads * kMaxChunks;
     if (vector_form) {
         LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype,
-                                  (add_rmsnorm_vec_kernel<T, W><<<n_rows, threads, 0, stream>>>(
+                                  (llm_launch(add_rmsnorm_vec_kernel<T, W>, n_rows, threads, 0, stream, 
                                       residual, (const T*)delta, (const W*)weight, (T*)out, rows, width, eps,
                                       write_residual)));
         return llm_check_launch("add_rmsnorm");
     }
     LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype,
-                              (add_rmsnorm_kernel<T, W><<<n_rows, norm_threads(width), 0, stream>>>(
+                              (llm_launch(add_rmsnorm_kernel<T, W>, n_rows, norm_threads(width), 0, stream, 
                                   residual, (const T*)delta, (const W*)weight, (T*)out, rows, width, eps,
                                   write_residual)));
     return llm_check_launch("add_rmsnorm");
@@ -141,7 +147,7 @@ LLM_EXPORT int llm_rmsnorm(const void* x, const void* weight, void* out, int n_r
                            int dtype, int weight_dtype, cudaStream_t stream) {
     if (n_rows == 0) return LLM_OK;
     LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype,
-                              (rmsnorm_kernel<T, W><<<n_rows, norm_threads(width), 0, stream>>>(
+                              (llm_launch(rmsnorm_kernel<T, W>, n_rows, norm_threads(width), 0, stream, 
                                   (const T*)x, (const W*)weight, (T*)out, width, eps)));
     return llm_check_launch("rmsnorm");
 }

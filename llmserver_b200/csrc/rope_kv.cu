@@ -32,6 +32,8 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const W* __res
                                              T* __restrict__ k_pages, T* __restrict__ v_pages, int n_q_heads,
                                              int n_kv_heads, int head_dim, int page_size, int num_pages, float eps,
                                              int write_cache, int* __restrict__ error_flag, int vector_form) {
+    pdl_trigger();   // let the next kernel start launching
+    pdl_wait();      // everything before this kernel in the stream is complete and visible
     const int token = blockIdx.y;
     const int warps_per_block = blockDim.x >> 5;
     const int head = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
@@ -155,7 +157,7 @@ LLM_EXPORT int llm_qk_norm_rope_kv_write(void* qkv, const void* q_weight, const 
     const int vector_form = head_dim % per_vector == 0 && head_dim % 4 == 0 && aligned16(qkv) && aligned16(k_pages) &&
                             aligned16(v_pages) && aligned16(q_weight) && aligned16(k_weight);
     dim3 grid((total_heads + warps - 1) / warps, n_tokens);
-    LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype, (qk_norm_rope_kv_write_kernel<T, W><<<grid, warps * 32, 0, stream>>>(
+    LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype, (llm_launch(qk_norm_rope_kv_write_kernel<T, W>, grid, warps * 32, 0, stream, 
                                   (T*)qkv, (const W*)q_weight, (const W*)k_weight, inv_freq, positions, seq_of_token,
                                   block_tables, max_blocks, (T*)k_pages, (T*)v_pages, n_q_heads, n_kv_heads, head_dim,
                                   page_size, num_pages, eps, write_cache, error_flag, vector_form)));

@@ -3,6 +3,7 @@
 
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 static thread_local char g_last_error[512] = "";
 
@@ -20,6 +21,15 @@ int llm_check_launch(const char* what) {
         return (int)status;
     }
     return LLM_OK;
+}
+
+bool llm_pdl_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* value = getenv("LLMSERVER_B200_PDL");
+        enabled = (value != nullptr && value[0] == '0') ? 0 : 1;
+    }
+    return enabled == 1;
 }
 
 LLM_EXPORT const char* llm_last_error() { return g_last_error; }

@@ -38,6 +38,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, const float* __r
                               const uint64_t* __restrict__ seeds, const int* __restrict__ steps,
                               int* __restrict__ out, int vocab, float* __restrict__ partial_scores,
                               int* __restrict__ partial_indices) {
+    pdl_trigger();   // let the next kernel start launching
+    pdl_wait();      // everything before this kernel in the stream is complete and visible
     __shared__ float best_values[32];
     __shared__ int best_indices[32];
     const int row = blockIdx.y, slices = gridDim.x;
@@ -94,6 +96,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, const float* __r
 
 __global__ void sample_merge_kernel(const float* __restrict__ partial_scores, const int* __restrict__ partial_indices,
                                     int* __restrict__ out, int slices) {
+    pdl_trigger();   // let the next kernel start launching
+    pdl_wait();      // everything before this kernel in the stream is complete and visible
     const int row = blockIdx.x, lane = threadIdx.x;
     float best = -INFINITY;
     int best_index = 0x7fffffff;
@@ -131,10 +135,10 @@ LLM_EXPORT int llm_sample(const float* logits, const float* temperatures, const 
     }
     const int threads = vocab >= 4096 ? 512 : 256;
     dim3 grid(slices, n_rows);
-    sample_kernel<<<grid, threads, 0, stream>>>(logits, temperatures, seeds, steps, out, vocab, partial_scores,
+    llm_launch(sample_kernel, grid, threads, 0, stream, logits, temperatures, seeds, steps, out, vocab, partial_scores,
                                                 partial_indices);
     int status = llm_check_launch("sample");
     if (status != LLM_OK || slices == 1) return status;
-    sample_merge_kernel<<<n_rows, 32, 0, stream>>>(partial_scores, partial_indices, out, slices);
+    llm_launch(sample_merge_kernel, n_rows, 32, 0, stream, partial_scores, partial_indices, out, slices);
     return llm_check_launch("sample_merge");
 }
