@@ -240,7 +240,10 @@ __global__ void __launch_bounds__(kThreads) attention_portions_kernel(const Attn
     for (; seq < p.n_seqs; ++seq) {
         const int q_len = p.q_start[seq + 1] - p.q_start[seq];
         const int tiles = (q_len == 1 && p.skip_single) ? 0 : (q_len * group + kTileRows - 1) / kTileRows;
-        if (tile < tiles) break;
+        if (tile < tiles) {
+            tile = tiles - 1 - tile;   // later tiles see more keys: start the long ones first
+            break;
+        }
         tile -= tiles;
     }
     if (seq >= p.n_seqs) return;

@@ -271,7 +271,7 @@ LLM_EXPORT int llm_gemm_small_m_supports(int m, int n, int k) {
 }
 
 LLM_EXPORT int llm_gemm_small_m(const void* x, const void* w, void* out, int m, int n, int k, int ldc, int out_is_f32,
-                                int* error_flag, cudaStream_t stream) {
+                                int requested_split, int* error_flag, cudaStream_t stream) {
     if (m == 0 || n == 0) return LLM_OK;
     if (!llm_gemm_small_m_supports(m, n, k) || !aligned16(x) || !aligned16(w)) {
         llm_set_error("gemm_small_m: takes 1..64 rows, K a multiple of 8 and 16-byte aligned operands (got m %d, n %d, k %d)", m, n, k);
@@ -288,8 +288,9 @@ LLM_EXPORT int llm_gemm_small_m(const void* x, const void* w, void* out, int m, 
     p.error_flag = error_flag;
     const int tiles = (n + kBlockRows - 1) / kBlockRows;
     const int total_kb = (k + kBlockK - 1) / kBlockK;
-    // split K across a cluster so that about one wave of 148 SMs is filled; each rank keeps >= 4 K blocks
-    int split = 148 / tiles;
+    // K is split across a cluster so that the tiles fill the machine; each rank keeps >= 4 K blocks.  The
+    // caller may name the split (it times a few once per shape); 0 asks for about one wave of 148 SMs.
+    int split = requested_split > 0 ? requested_split : 148 / tiles;
     if (split > total_kb / 4) split = total_kb / 4;
     if (split > kMaxSplit) split = kMaxSplit;
     if (split < 1) split = 1;

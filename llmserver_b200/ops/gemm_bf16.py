@@ -41,8 +41,9 @@ def small_m_supported(rows: int, cols: int, inner: int) -> bool:
     return _use_small_m and bool(library().llm_gemm_small_m_supports(rows, cols, inner))
 
 
-# (row bucket, N, K, out dtype) -> True when this package's kernel is the faster one for that product.
+# (row bucket, N, K, out dtype) -> split of K to use with this package's kernel, or 0 for the library product.
 _choice = {}
+SPLITS = (1, 2, 3, 4, 6, 8)
 
 
 def _row_bucket(rows: int) -> int:
@@ -73,34 +74,45 @@ def _time_once(run, device, repeats: int = 3) -> float:
     return best
 
 
-def _prefer_small_m(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> bool:
-    """Measures both products once per (rows bucket, shape) and remembers which is faster.  Both read
+def _small_m(x, weight, out, split: int) -> None:
+    rows, inner = x.shape
+    cols = weight.shape[0]
+    call("llm_gemm_small_m", x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, cols, inner, cols,
+         int(out.dtype == torch.float32), split, error_flag(x.device).data_ptr(), stream_handle())
+
+
+def _plan_for(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> int:
+    """Measures, once per (rows bucket, shape), this package's kernel with a few splits of K and the
+    library product, and remembers the fastest: a split (> 0) or 0 for the library.  All candidates read
     the same operands and give the same result up to rounding, so the choice changes speed only.
     While a CUDA graph is being captured nothing can be timed: an unknown shape then uses this
-    package's kernel."""
+    package's kernel with its default split."""
     rows, inner = x.shape
-    key = (_row_bucket(rows), weight.shape[0], inner, out_dtype)
+    cols = weight.shape[0]
+    key = (_row_bucket(rows), cols, inner, out_dtype)
     known = _choice.get(key)
     if known is not None:
         return known
     if torch.cuda.is_current_stream_capturing():
-        return True
-    cols = weight.shape[0]
+        return -1
     out = torch.empty((rows, cols), dtype=out_dtype, device=x.device)
-    flag = error_flag(x.device)
 
-    def ours():
-        call("llm_gemm_small_m", x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, cols, inner, cols,
-             int(out_dtype == torch.float32), flag.data_ptr(), stream_handle())
-
-    def theirs():
+    def library_product():
         if out_dtype == torch.bfloat16:
             torch.matmul(x, weight.t(), out=out)
         else:
             out.copy_(torch.matmul(x, weight.t()))
 
-    _choice[key] = _time_once(ours, x.device) <= _time_once(theirs, x.device) * 1.02
-    return _choice[key]
+    best_time, best = _time_once(library_product, x.device) * 0.98, 0
+    tiles, k_blocks = -(-cols // 128), -(-inner // 64)
+    for split in SPLITS:
+        if split > 1 and (tiles * split > 600 or k_blocks // split < 4):
+            continue
+        elapsed = _time_once(lambda: _small_m(x, weight, out, split), x.device)
+        if elapsed < best_time:
+            best_time, best = elapsed, split
+    _choice[key] = best
+    return best
 
 
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -111,14 +123,15 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tenso
     rows, inner = x.shape
     cols = weight.shape[0]
     if rows <= SMALL_M and x.is_contiguous() and weight.is_contiguous() and small_m_supported(rows, cols, inner) \
-            and out_dtype in (torch.bfloat16, torch.float32) and _prefer_small_m(x, weight, out_dtype):
-        if out is None:
-            out = torch.empty((rows, cols), dtype=out_dtype, device=x.device)
-        elif out.dtype != out_dtype or not out.is_contiguous() or out.shape != (rows, cols):
-            raise KernelError("linear_bf16: the output tensor does not match")
-        call("llm_gemm_small_m", x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, cols, inner, cols,
-             int(out_dtype == torch.float32), error_flag(x.device).data_ptr(), stream_handle())
-        return out
+            and out_dtype in (torch.bfloat16, torch.float32):
+        split = _plan_for(x, weight, out_dtype)
+        if split != 0:
+            if out is None:
+                out = torch.empty((rows, cols), dtype=out_dtype, device=x.device)
+            elif out.dtype != out_dtype or not out.is_contiguous() or out.shape != (rows, cols):
+                raise KernelError("linear_bf16: the output tensor does not match")
+            _small_m(x, weight, out, max(split, 0))
+            return out
     if out_dtype == torch.bfloat16:
         if out is not None:
             return torch.matmul(x, weight.t(), out=out)

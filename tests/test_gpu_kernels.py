@@ -119,10 +119,10 @@ def test_gemm_small_m_tcgen05(shape):
     assert gemm_bf16.small_m_supported(m, n, k)
     x, w = rand((m, k), torch.bfloat16, 12), rand((n, k), torch.bfloat16, 13, 0.05)
     want = x.double() @ w.double().T
-    for out_dtype in (torch.float32, torch.bfloat16):
+    for out_dtype, split in ((torch.float32, 0), (torch.bfloat16, 0), (torch.float32, 3), (torch.bfloat16, 8)):
         out = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEVICE)
         call("llm_gemm_small_m", x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, n, int(out_dtype == torch.float32),
-             gemm_bf16.error_flag(DEVICE).data_ptr(), stream_handle())
+             split, gemm_bf16.error_flag(DEVICE).data_ptr(), stream_handle())
         torch.cuda.synchronize()
         gemm_bf16.check_errors()
         close(out, want, out_dtype, f"small-M product {shape} -> {out_dtype}", factor=4.0 if out_dtype == torch.float32 else 1.0)
