@@ -1,0 +1,455 @@
+// Causal attention of prompt portions over the paged cache on the fifth-generation tensor cores:
+// S = Q K^T and O += P V are tcgen05.mma instructions whose accumulators live in tensor memory; Q, K and
+// V tiles arrive by TMA (128-byte swizzle); the softmax runs on 128 threads that each own one row.
+//
+// One CTA takes 128 rows of one (sequence, kv head): rows are (token, head of the group) pairs, so the
+// G query heads that share a kv head share every K/V tile.  It walks the keys the rows can see in tiles
+// of 64 (whole cache pages), from the first key in the tile's window to the last token's position:
+//
+//   producer warp   TMA: the Q tile once (a 4-D box: 64 columns x G heads x 1 kv head x 128/G tokens), then
+//                   per key tile the K pages and the V pages into a ring of two stages
+//   MMA warp        one thread: S_b = Q K_j^T (8 x UMMA 128x64x16) into S buffer b = j mod 2, and, one
+//                   tile behind, O += P_{j-1} V_{j-1} (4 x UMMA 128x128x16 with A = P read from tensor
+//                   memory, B = V as an MN-major operand)
+//   4 softmax warps thread r owns row r = lane r of tensor memory: tcgen05.ld of S_b, mask, scale, running
+//                   maximum and sum in 32-bit, exp2, P written back over S_b as packed bfloat16
+//                   (tcgen05.st); O is rescaled only when a row's maximum has grown by more than 2^8 since
+//                   its reference (the reference, not the maximum, is subtracted in the exponent; the
+//                   final division by the sum undoes it); at the end O / sum is stored as bfloat16
+//
+// Formulas as in attention_mma.cu (utils/attention.py:186-198, utils/attention.py:75-96).  Tensor memory:
+// S0 | S1 | O = 64 + 64 + 128 columns; two CTAs fit on an SM (512 columns, 2 x 97 KiB shared memory), so one
+// CTA's softmax overlaps the other's MMAs as well as its own next S tile.
+// Every mbarrier wait is bounded; a wait that runs out sets the error flag, and the CTA still releases its
+// tensor memory.  Takes head_dim 128, groups of 1, 2, 4, 8 or 16 heads, pages of 8, 16, 32 or 64 tokens;
+// other sizes use the mma.sync kernel.
+#include "common.cuh"
+#include "tma.cuh"
+
+namespace {
+
+constexpr int kRows = 128;        // rows per CTA (UMMA M)
+constexpr int kKeys = 64;         // keys per tile (UMMA N of S, K of P V)
+constexpr int kDim = 128;         // head_dim
+constexpr int kStages = 2;        // K/V ring
+constexpr int kThreads = 192;     // 4 softmax warps + producer warp + MMA warp
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.0f;   // log2 units
+
+constexpr uint32_t kQBytes = kRows * kDim * 2;        // 32 KiB
+constexpr uint32_t kKVBytes = kKeys * kDim * 2;       // 16 KiB per K or V tile
+constexpr uint32_t kColS0 = 0, kColS1 = 64, kColO = 128, kTmemCols = 256;
+
+struct PrefillParams {
+    const int* block_tables;
+    int max_blocks;
+    const int* q_start;
+    const int* context_len;
+    __nv_bfloat16* out;
+    int n_seqs, n_q_heads, n_kv_heads, page_size;
+    float scale_log2;
+    int window;
+    int skip_single;
+    int* error_flag;
+};
+
+using tma::mbar_arrive;
+using tma::mbar_expect_tx;
+using tma::mbar_init;
+using tma::mbar_wait;
+using tma::smem_u32;
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+// K-major operand with 128-byte swizzle (rows of 128 bytes, 8-row groups 1024 bytes apart).
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t address) {
+    uint64_t d = 0;
+    d |= (uint64_t)((address & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// MN-major operand with 128-byte swizzle: 64 MN-elements (128 bytes) contiguous, 8 K-rows per 1024-byte
+// atom; atoms along MN `leading` bytes apart, atoms along K 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t address, uint32_t leading) {
+    uint64_t d = 0;
+    d |= (uint64_t)((address & 0x3FFFF) >> 4);
+    d |= (uint64_t)((leading >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// bfloat16 x bfloat16 -> float32; b_mn_major: B is MN-major.
+__device__ __forceinline__ uint32_t instruction(int m, int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// The load and the wait for it are one statement, so that no use of the registers can be scheduled between them.
+__device__ __forceinline__ void tmem_load_32(uint32_t address, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(address)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_store_32(uint32_t address, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(address), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+          "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+          "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_store() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t pack2(float low, float high) {
+    __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
+    return *reinterpret_cast<uint32_t*>(&pair);
+}
+
+__global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                             const __grid_constant__ CUtensorMap map_k,
+                                                                             const __grid_constant__ CUtensorMap map_v,
+                                                                             const PrefillParams p) {
+    extern __shared__ __align__(16) unsigned char shared_raw[];
+    __shared__ __align__(8) uint64_t q_full, k_full[kStages], v_full[kStages], kv_free[kStages], s_ready[2], p_ready[2], o_done;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int failed;
+    pdl_trigger();
+    pdl_wait();
+
+    const uint32_t raw = smem_u32(shared_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    const uint32_t q_smem = base, k_smem = base + kQBytes, v_smem = k_smem + kStages * kKVBytes;
+
+    const int group = p.n_q_heads / p.n_kv_heads;
+    const int tokens_per_tile = kRows / group;
+    const int kv_head = blockIdx.y;
+    int seq = 0, tile = blockIdx.x;
+    for (; seq < p.n_seqs; ++seq) {
+        const int q_len = p.q_start[seq + 1] - p.q_start[seq];
+        const int tiles = (q_len == 1 && p.skip_single) ? 0 : (q_len * group + kRows - 1) / kRows;
+        if (tile < tiles) {
+            tile = tiles - 1 - tile;     // later tiles see more keys: start the long ones first
+            break;
+        }
+        tile -= tiles;
+    }
+    if (seq >= p.n_seqs) return;
+    const int token0 = p.q_start[seq];
+    const int q_len = p.q_start[seq + 1] - token0;
+    const int context = p.context_len[seq];
+    const int n_rows = q_len * group;
+    const int first_row = tile * kRows;
+    const int base_position = context - q_len;
+    const int first_token = first_row / group;
+    const int last_row = min(first_row + kRows, n_rows) - 1;
+    const int high_key = base_position + last_row / group;
+    int low_key = 0;
+    if (p.window > 0) low_key = max(0, base_position + first_token - p.window + 1);
+    const int first_tile_key = (low_key / kKeys) * kKeys;
+    const int n_tiles = (high_key - first_tile_key) / kKeys + 1;
+    const int* table = p.block_tables + (size_t)seq * p.max_blocks;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        failed = 0;
+        mbar_init(smem_u32(&q_full), 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&k_full[s]), 1);
+            mbar_init(smem_u32(&v_full[s]), 1);
+            mbar_init(smem_u32(&kv_free[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&s_ready[b]), 1);
+            mbar_init(smem_u32(&p_ready[b]), 4);      // one arrival per softmax warp
+        }
+        mbar_init(smem_u32(&o_done), 1);
+        tma::mbar_fence_init();
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = tmem_slot;
+
+    if (warp == 4) {
+        // ---------------------------------------------------------------- producer
+        if (lane == 0) {
+            mbar_expect_tx(smem_u32(&q_full), kQBytes);
+            tma_load_4d(q_smem, &map_q, smem_u32(&q_full), 0, 0, kv_head, token0 + tile * tokens_per_tile);
+            tma_load_4d(q_smem + kRows * 128u, &map_q, smem_u32(&q_full), 64, 0, kv_head, token0 + tile * tokens_per_tile);
+        }
+        const int pages_per_tile = kKeys / p.page_size;
+        const int copies = pages_per_tile * 2;               // two column halves per page
+        const int my_page = lane >> 1, my_half = lane & 1;
+        for (int t = 0; t < n_tiles; ++t) {
+            const int s = t % kStages;
+            if (t >= kStages && !mbar_wait(smem_u32(&kv_free[s]), ((t / kStages) - 1) & 1)) {
+                failed = 1;
+                break;
+            }
+            if (lane == 0) {
+                mbar_expect_tx(smem_u32(&k_full[s]), kKVBytes);
+                mbar_expect_tx(smem_u32(&v_full[s]), kKVBytes);
+            }
+            __syncwarp();
+            if (lane < copies) {
+                // whole tiles always: pages past the sequence's end come from whatever the zero-padded table
+                // names (an existing page with finite contents, masked out below)
+                const int key = first_tile_key + t * kKeys + my_page * p.page_size;
+                const int page = table[min(key / p.page_size, p.max_blocks - 1)];
+                const int y = (page * p.n_kv_heads + kv_head) * p.page_size;
+                const uint32_t offset = s * kKVBytes + my_half * (kKeys * 128u) + (uint32_t)(my_page * p.page_size) * 128u;
+                tma::load_2d(k_smem + offset, &map_k, smem_u32(&k_full[s]), my_half * 64, y);
+                tma::load_2d(v_smem + offset, &map_v, smem_u32(&v_full[s]), my_half * 64, y);
+            }
+        }
+    } else if (warp == 5) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc_s = instruction(kRows, kKeys, false);
+            const uint32_t idesc_o = instruction(kRows, kDim, true);
+            bool ok = mbar_wait(smem_u32(&q_full), 0);
+            for (int j = 0; j <= n_tiles && ok; ++j) {
+                if (j < n_tiles) {        // S_b = Q K_j^T
+                    const int s = j % kStages, b = j & 1;
+                    ok = mbar_wait(smem_u32(&k_full[s]), (j / kStages) & 1);
+                    if (!ok) break;
+                    fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < kDim / 16; ++ks) {
+                        const uint32_t half = ks >> 2, within = (ks & 3) * 32;
+                        mma_ss(tmem + (b ? kColS1 : kColS0), desc_k_major(q_smem + half * (kRows * 128u) + within),
+                               desc_k_major(k_smem + s * kKVBytes + half * (kKeys * 128u) + within), idesc_s, ks > 0 ? 1u : 0u);
+                    }
+                    mma_commit(smem_u32(&s_ready[b]));
+                }
+                if (j > 0) {              // O += P_{j-1} V_{j-1}
+                    const int t = j - 1, s = t % kStages, b = t & 1;
+                    ok = mbar_wait(smem_u32(&p_ready[b]), (t >> 1) & 1) && mbar_wait(smem_u32(&v_full[s]), (t / kStages) & 1);
+                    if (!ok) break;
+                    fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < kKeys / 16; ++kk)     // 16 keys = 8 packed columns of P, 2048 bytes of V rows
+                        mma_ts(tmem + kColO, tmem + (b ? kColS1 : kColS0) + kk * 8,
+                               desc_mn_major(v_smem + s * kKVBytes + kk * 2048u, kKeys * 128u), idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+                    mma_commit(smem_u32(&kv_free[s]));
+                    mma_commit(smem_u32(&o_done));
+                }
+            }
+            if (!ok) failed = 1;
+        }
+    } else {
+        // ---------------------------------------------------------------- softmax: thread = row
+        const int row = warp * 32 + lane;
+        const int r = first_row + row;
+        const bool exists = r < n_rows;
+        const int position = exists ? base_position + r / group : -1;
+        const int low = (exists && p.window > 0) ? max(0, position - p.window + 1) : 0;
+        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+        float reference = -INFINITY;     // what is subtracted in the exponent (a stale maximum)
+        float row_sum = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int b = j & 1;
+            if (ok && !mbar_wait(smem_u32(&s_ready[b]), (j >> 1) & 1)) ok = false;
+            fence_after();
+            const uint32_t s_address = lane_base + (b ? kColS1 : kColS0);
+            uint32_t raw_low[32], raw_high[32];
+            tmem_load_32(s_address, raw_low);
+            tmem_load_32(s_address + 32, raw_high);
+            const int tile_key = first_tile_key + j * kKeys;
+            float tile_max = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                const int key_low = tile_key + c, key_high = tile_key + 32 + c;
+                float x = __uint_as_float(raw_low[c]) * p.scale_log2, y = __uint_as_float(raw_high[c]) * p.scale_log2;
+                x = (key_low >= low && key_low <= position) ? x : -INFINITY;
+                y = (key_high >= low && key_high <= position) ? y : -INFINITY;
+                raw_low[c] = __float_as_uint(x);
+                raw_high[c] = __float_as_uint(y);
+                tile_max = fmaxf(tile_max, fmaxf(x, y));
+            }
+            // the reference moves only when the maximum has outgrown it by the threshold (or nothing was seen yet)
+            float factor = 1.0f;
+            if (tile_max > reference + kRescaleThreshold || (reference == -INFINITY && tile_max > -INFINITY)) {
+                factor = reference == -INFINITY ? 0.0f : exp2f(reference - tile_max);
+                reference = tile_max;
+            }
+            const float subtract = reference == -INFINITY ? 0.0f : reference;
+            float tile_sum = 0.0f;
+            uint32_t packed[32];
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const float a0 = exp2f(__uint_as_float(raw_low[2 * c]) - subtract), a1 = exp2f(__uint_as_float(raw_low[2 * c + 1]) - subtract);
+                const float b0 = exp2f(__uint_as_float(raw_high[2 * c]) - subtract), b1 = exp2f(__uint_as_float(raw_high[2 * c + 1]) - subtract);
+                tile_sum += (a0 + a1) + (b0 + b1);
+                packed[c] = pack2(a0, a1);            // keys 2c, 2c + 1
+                packed[16 + c] = pack2(b0, b1);       // keys 32 + 2c, 32 + 2c + 1
+            }
+            row_sum = row_sum * factor + tile_sum;
+            // O is rescaled (by the whole warp, rows that need nothing use 1) once the previous P V is done
+            if (j > 0 && __any_sync(0xffffffffu, factor != 1.0f)) {
+                if (ok && !mbar_wait(smem_u32(&o_done), (j - 1) & 1)) ok = false;
+                fence_after();
+#pragma unroll
+                for (int chunk = 0; chunk < kDim / 32; ++chunk) {
+                    uint32_t o_raw[32];
+                    tmem_load_32(lane_base + kColO + chunk * 32, o_raw);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o_raw[c] = __float_as_uint(__uint_as_float(o_raw[c]) * factor);
+                    tmem_store_32(lane_base + kColO + chunk * 32, o_raw);
+                }
+            }
+            tmem_store_32(s_address, packed);          // P over the first 32 columns of S_b
+            tmem_wait_store();
+            fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&p_ready[b]));
+        }
+        // the last P V, then O / sum
+        if (ok && !mbar_wait(smem_u32(&o_done), (n_tiles - 1) & 1)) ok = false;
+        fence_after();
+        if (!ok) failed = 1;
+        const float inverse = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
+        __nv_bfloat16* dst = exists ? p.out + (size_t)(token0 + r / group) * p.n_q_heads * kDim + (size_t)(kv_head * group + r % group) * kDim
+                                    : nullptr;
+#pragma unroll
+        for (int chunk = 0; chunk < kDim / 32; ++chunk) {
+            uint32_t o_raw[32];
+            tmem_load_32(lane_base + kColO + chunk * 32, o_raw);
+            if (exists) {
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    uint4 words;
+                    words.x = pack2(__uint_as_float(o_raw[8 * v]) * inverse, __uint_as_float(o_raw[8 * v + 1]) * inverse);
+                    words.y = pack2(__uint_as_float(o_raw[8 * v + 2]) * inverse, __uint_as_float(o_raw[8 * v + 3]) * inverse);
+                    words.z = pack2(__uint_as_float(o_raw[8 * v + 4]) * inverse, __uint_as_float(o_raw[8 * v + 5]) * inverse);
+                    words.w = pack2(__uint_as_float(o_raw[8 * v + 6]) * inverse, __uint_as_float(o_raw[8 * v + 7]) * inverse);
+                    *reinterpret_cast<uint4*>(dst + chunk * 32 + v * 8) = words;
+                }
+            }
+        }
+    }
+    fence_before();
+    __syncthreads();
+    if (failed && threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 4);
+    if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
+}
+
+}  // namespace
+
+LLM_EXPORT int llm_attention_prefill_tcgen05_supports(int head_dim, int n_q_heads, int n_kv_heads, int page_size) {
+    if (head_dim != kDim || n_kv_heads <= 0 || n_q_heads % n_kv_heads) return 0;
+    const int group = n_q_heads / n_kv_heads;
+    if (group > 16 || (group & (group - 1))) return 0;
+    return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64;
+}
+
+// total_tiles: sum over the sequences it handles of ceil(q_len * group / 128); sequences of one token are
+// skipped when skip_single is set (the decode kernel takes them).
+LLM_EXPORT int llm_attention_prefill_tcgen05(const void* q, int q_stride, int n_tokens, const void* k_pages, const void* v_pages,
+                                             const int* block_tables, int max_blocks, const int* q_start,
+                                             const int* context_len, void* out, int n_seqs, int n_q_heads, int n_kv_heads,
+                                             int head_dim, int page_size, float scale, int window, int skip_single,
+                                             int total_tiles, int* error_flag, cudaStream_t stream) {
+    if (total_tiles <= 0) return LLM_OK;
+    if (!llm_attention_prefill_tcgen05_supports(head_dim, n_q_heads, n_kv_heads, page_size) || !aligned16(q) || q_stride % 8) {
+        llm_set_error("attention_prefill_tcgen05: unsupported sizes (head_dim %d, %d/%d heads, page %d)", head_dim, n_q_heads,
+                      n_kv_heads, page_size);
+        return LLM_REFUSED;
+    }
+    if (n_kv_heads > 65535) {
+        llm_set_error("attention_prefill_tcgen05: too many kv heads (%d)", n_kv_heads);
+        return LLM_REFUSED;
+    }
+    const int group = n_q_heads / n_kv_heads;
+    tma::EncodeTiled encode = tma::encode_tiled();
+    if (encode == nullptr) {
+        llm_set_error("attention_prefill_tcgen05: cuTensorMapEncodeTiled is not available");
+        return LLM_REFUSED;
+    }
+    // Q as a 4-D tensor (column, head of the group, kv head, token) over the packed projection
+    CUtensorMap map_q, map_k, map_v;
+    {
+        const cuuint64_t dims[4] = {(cuuint64_t)head_dim, (cuuint64_t)group, (cuuint64_t)n_kv_heads, (cuuint64_t)n_tokens};
+        const cuuint64_t strides[3] = {(cuuint64_t)head_dim * 2, (cuuint64_t)group * head_dim * 2, (cuuint64_t)q_stride * 2};
+        const cuuint32_t box[4] = {64u, (cuuint32_t)group, 1u, (cuuint32_t)(kRows / group)};
+        const cuuint32_t ones[4] = {1, 1, 1, 1};
+        if (encode(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(q), dims, strides, box, ones,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+            llm_set_error("attention_prefill_tcgen05: cannot describe Q to TMA");
+            return LLM_REFUSED;
+        }
+    }
+    if (!tma::make_map_bf16(&map_k, k_pages, (uint64_t)1 << 30, head_dim, (uint32_t)page_size) ||
+        !tma::make_map_bf16(&map_v, v_pages, (uint64_t)1 << 30, head_dim, (uint32_t)page_size)) {
+        llm_set_error("attention_prefill_tcgen05: cannot describe the pages to TMA");
+        return LLM_REFUSED;
+    }
+    PrefillParams p;
+    p.block_tables = block_tables;
+    p.max_blocks = max_blocks;
+    p.q_start = q_start;
+    p.context_len = context_len;
+    p.out = (__nv_bfloat16*)out;
+    p.n_seqs = n_seqs;
+    p.n_q_heads = n_q_heads;
+    p.n_kv_heads = n_kv_heads;
+    p.page_size = page_size;
+    p.scale_log2 = scale * kLog2e;
+    p.window = window;
+    p.skip_single = skip_single;
+    p.error_flag = error_flag;
+    const size_t shared = (size_t)kQBytes + 2 * kStages * kKVBytes + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t status = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        if (status != cudaSuccess) {
+            llm_set_error("attention_prefill_tcgen05: cannot get %zu bytes of shared memory: %s", shared, cudaGetErrorString(status));
+            return (int)status;
+        }
+        configured = true;
+    }
+    dim3 grid(total_tiles, n_kv_heads);
+    llm_launch(attention_prefill_tcgen05_kernel, grid, kThreads, shared, stream, map_q, map_k, map_v, p);
+    return llm_check_launch("attention_prefill_tcgen05");
+}

@@ -4,6 +4,8 @@
 uses the generic 32-bit-arithmetic kernel, which takes every size."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import gemm_bf16
@@ -12,6 +14,15 @@ from .library import call, check, library, stream_handle
 TILE = 64          # rows per block of the portions kernel, keys per tile of both kernels
 MIN_SPLIT = 256    # fewest keys one decode block walks
 TARGET_BLOCKS = 296   # one wave of two blocks per SM on 148 SMs
+
+
+PREFILL_KERNEL = os.environ.get("LLMSERVER_B200_PREFILL_ATTENTION", "tcgen05")   # or "mma"
+PREFILL_TILE = 128   # rows per block of the tcgen05 portions kernel
+
+
+def prefill_tcgen05_supported(head_dim: int, n_q_heads: int, n_kv_heads: int, page_size: int) -> bool:
+    return PREFILL_KERNEL == "tcgen05" and bool(
+        library().llm_attention_prefill_tcgen05_supports(head_dim, n_q_heads, n_kv_heads, page_size))
 
 
 def supported(head_dim: int, n_q_heads: int, n_kv_heads: int) -> bool:
@@ -59,9 +70,22 @@ def try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_head
                        torch.empty((batch.n_tokens, n_q_heads, max_splits, 2), dtype=torch.float32, device=qkv.device))
             batch.scratch[key] = scratch
         partial_out, partial_ml = scratch
+    page_size = k_pages.shape[2]
+    flag = gemm_bf16.error_flag(qkv.device).data_ptr()
+    if run_portions and prefill_tcgen05_supported(head_dim, n_q_heads, n_kv_heads, page_size):
+        # prompt portions on the tcgen05 kernel (128-row tiles); single tokens, if any, on the decode kernel
+        group = n_q_heads // n_kv_heads
+        big_tiles = sum(-(-length * group // PREFILL_TILE) for length in batch.q_lens if length > 1 or not run_decode)
+        call("llm_attention_prefill_tcgen05", qkv.data_ptr(), q_stride, batch.n_tokens, k_pages.data_ptr(), v_pages.data_ptr(),
+             block_tables.data_ptr(), block_tables.shape[-1], batch.q_start.data_ptr(), batch.context_len.data_ptr(),
+             out.data_ptr(), batch.n_seqs, n_q_heads, n_kv_heads, head_dim, page_size, float(scale), int(window),
+             int(run_decode), big_tiles, flag, stream_handle())
+        run_portions = False
+        if not run_decode:
+            return out
     call("llm_attention_mma", qkv.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(), block_tables.data_ptr(),
          block_tables.shape[-1], batch.q_start.data_ptr(), batch.context_len.data_ptr(), out.data_ptr(), batch.n_seqs,
-         n_q_heads, n_kv_heads, head_dim, k_pages.shape[2], float(scale), int(window), int(run_portions), tiles,
+         n_q_heads, n_kv_heads, head_dim, page_size, float(scale), int(window), int(run_portions), tiles,
          int(run_decode), split_len, max_splits, 0 if partial_out is None else partial_out.data_ptr(),
-         0 if partial_ml is None else partial_ml.data_ptr(), gemm_bf16.error_flag(qkv.device).data_ptr(), stream_handle())
+         0 if partial_ml is None else partial_ml.data_ptr(), flag, stream_handle())
     return out

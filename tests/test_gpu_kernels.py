@@ -412,3 +412,39 @@ def test_tensor_core_attention_finds_a_far_key_and_respects_the_window_edge():
             last = out[-1].float().cpu().view(heads, dim)[2]
             target = v.to(dtype).float()[hot, 0]
             assert torch.allclose(last, target, atol=3e-2) == found, f"q_len {q_len}, hot key {hot}, window {window}"
+
+
+@pytest.mark.parametrize("heads,kv_heads,page_size,window", [(32, 8, 16, None), (4, 4, 8, None), (16, 1, 32, 100),
+                                                             (8, 4, 64, None), (8, 1, 16, 300), (2, 1, 16, None)])
+def test_attention_prefill_tcgen05(heads, kv_heads, page_size, window):
+    """The tcgen05 / tensor-memory kernel for prompt portions (head_dim 128, groups of 1 to 16 heads, whole
+    pages per tile): portions that start in the middle of a page and of a tile, more than one row tile,
+    a whole prompt, a portion of two tokens, beside single tokens that go to the decode kernel."""
+    from llmserver_b200.ops import attention_bf16
+    dim, dtype = 128, torch.bfloat16
+    assert attention_bf16.prefill_tcgen05_supported(dim, heads, kv_heads, page_size)
+    contexts, q_lens = [1100, 333, 1, 77, 513, 700], [1, 70, 1, 77, 2, 300]
+    scale = dim ** -0.5
+    dense_k = [rand((c, kv_heads, dim), dtype, 220 + i).cpu() for i, c in enumerate(contexts)]
+    dense_v = [rand((c, kv_heads, dim), dtype, 230 + i).cpu() for i, c in enumerate(contexts)]
+    k_pages, v_pages, tables = paged(dense_k, dense_v, page_size, 9, dtype)
+    queries = [rand((n, heads, dim), dtype, 240 + i).cpu() for i, n in enumerate(q_lens)]
+    q_stride = (heads + 2 * kv_heads) * dim
+    packed = torch.zeros((sum(q_lens), q_stride), dtype=dtype)
+    packed[:, :heads * dim] = torch.cat(queries).reshape(-1, heads * dim)
+    want = torch.cat([plain_attention_rows(q.double(), k.double(), v.double(), scale, window, c - n)
+                      for q, k, v, c, n in zip(queries, dense_k, dense_v, contexts, q_lens)])
+    results = {}
+    for kernel in ("tcgen05", "mma"):
+        attention_bf16.PREFILL_KERNEL = kernel
+        try:
+            out = attention_bf16.try_attention(packed.to(DEVICE), q_stride, FakeBatch(contexts, q_lens), tables, k_pages, v_pages,
+                                               heads, kv_heads, dim, scale, window or 0)
+        finally:
+            attention_bf16.PREFILL_KERNEL = "tcgen05"
+        torch.cuda.synchronize()
+        from llmserver_b200.ops import gemm_bf16
+        gemm_bf16.check_errors()
+        close(out, want, dtype, f"prompt attention ({kernel})")
+        results[kernel] = out
+    close(results["tcgen05"], results["mma"].double().cpu(), dtype, "the two prompt kernels against each other")

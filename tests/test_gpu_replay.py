@@ -16,7 +16,7 @@ from tiny_configs import TINY
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-NAMES = ["a", "b", "c", "d"]
+NAMES = ["a", "b", "c", "d", "e"]
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 

@@ -26,5 +26,12 @@ TINY_D = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size
               hidden_act="silu", attention_bias=False, sliding_window=70,
               layer_types=["full_attention", "sliding_attention"])
 
+# head_dim 128 with groups of 4: the sizes from which prompts run the tcgen05 attention kernel
+TINY_E = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=333, hidden_size=192,
+              intermediate_size=320, num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+              rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096,
+              hidden_act="silu", attention_bias=False, sliding_window=150,
+              layer_types=["sliding_attention", "full_attention"])
+
 # name -> (config.json dict, weight seed)
-TINY = {"a": (TINY_A, 0), "b": (TINY_B, 1), "c": (TINY_C, 2), "d": (TINY_D, 3)}
+TINY = {"a": (TINY_A, 0), "b": (TINY_B, 1), "c": (TINY_C, 2), "d": (TINY_D, 3), "e": (TINY_E, 4)}
