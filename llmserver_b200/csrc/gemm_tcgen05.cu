@@ -26,7 +26,9 @@
 namespace {
 
 constexpr int kBlockRows = 128;     // rows of W per CTA (UMMA M)
-constexpr int kBlockK = 64;         // one 128-byte swizzle atom of bfloat16
+constexpr int kAtomK = 64;          // one 128-byte swizzle atom of bfloat16
+constexpr int kAtoms = 2;           // atoms per pipeline stage
+constexpr int kBlockK = kAtomK * kAtoms;
 constexpr int kThreads = 128;
 constexpr int kMaxStages = 12;
 constexpr int kMaxSplit = 8;
@@ -120,9 +122,11 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
     const uint32_t raw = smem_u32(shared_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* aligned = shared_raw + (base - raw);
-    const uint32_t a_bytes = kBlockRows * kBlockK * 2;               // 16 KiB
-    const uint32_t b_bytes = (uint32_t)p.token_pad * kBlockK * 2;     // 2..8 KiB
-    const uint32_t stage_bytes = a_bytes + ((b_bytes + 1023u) & ~1023u);
+    const uint32_t a_bytes = kBlockRows * kAtomK * 2;                 // 16 KiB per atom of W
+    const uint32_t b_bytes = (uint32_t)p.token_pad * kAtomK * 2;      // 2..8 KiB per atom of tokens
+    const uint32_t b_pitch = (b_bytes + 1023u) & ~1023u;
+    const uint32_t b_offset = kAtoms * a_bytes;                       // token atoms follow the W atoms of a stage
+    const uint32_t stage_bytes = b_offset + kAtoms * b_pitch;
 
     pdl_trigger();   // let the next kernel start launching
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -159,23 +163,31 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
         const int first = n_kb < p.stages ? n_kb : p.stages;
         for (int i = 0; i < first; ++i) {
             const uint32_t bar = smem_u32(&full_bar[i]);
-            mbar_expect_tx(bar, a_bytes + b_bytes);
-            tma_load_2d(base + i * stage_bytes, &map_w, bar, (kb_begin + i) * kBlockK, n0);
+            mbar_expect_tx(bar, kAtoms * (a_bytes + b_bytes));
+#pragma unroll
+            for (int atom = 0; atom < kAtoms; ++atom)
+                tma_load_2d(base + i * stage_bytes + atom * a_bytes, &map_w, bar, (kb_begin + i) * kBlockK + atom * kAtomK, n0);
         }
         pdl_wait();
         for (int i = 0; i < first; ++i)
-            tma_load_2d(base + i * stage_bytes + a_bytes, &map_x, smem_u32(&full_bar[i]), (kb_begin + i) * kBlockK, 0);
+#pragma unroll
+            for (int atom = 0; atom < kAtoms; ++atom)
+                tma_load_2d(base + i * stage_bytes + b_offset + atom * b_pitch, &map_x, smem_u32(&full_bar[i]),
+                            (kb_begin + i) * kBlockK + atom * kAtomK, 0);
         for (int i = first; i < n_kb; ++i) {
             const int s = i % p.stages;
             if (!mbar_wait(smem_u32(&empty_bar[s]), ((i / p.stages) - 1) & 1)) {
                 failed = 1;
                 break;
             }
-            const uint32_t a_dst = base + s * stage_bytes, b_dst = a_dst + a_bytes;
+            const uint32_t stage = base + s * stage_bytes;
             const uint32_t bar = smem_u32(&full_bar[s]);
-            mbar_expect_tx(bar, a_bytes + b_bytes);
-            tma_load_2d(a_dst, &map_w, bar, (kb_begin + i) * kBlockK, n0);
-            tma_load_2d(b_dst, &map_x, bar, (kb_begin + i) * kBlockK, 0);
+            mbar_expect_tx(bar, kAtoms * (a_bytes + b_bytes));
+#pragma unroll
+            for (int atom = 0; atom < kAtoms; ++atom) {
+                tma_load_2d(stage + atom * a_bytes, &map_w, bar, (kb_begin + i) * kBlockK + atom * kAtomK, n0);
+                tma_load_2d(stage + b_offset + atom * b_pitch, &map_x, bar, (kb_begin + i) * kBlockK + atom * kAtomK, 0);
+            }
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer
@@ -189,11 +201,15 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_src = base + s * stage_bytes, b_src = a_src + a_bytes;
-            const uint64_t desc_a = umma_descriptor(a_src), desc_b = umma_descriptor(b_src);
+            const uint32_t a_src = base + s * stage_bytes, b_src = a_src + b_offset;
 #pragma unroll
-            for (int k = 0; k < kBlockK / 16; ++k)   // 16 bfloat16 = 32 bytes further along the swizzled row
-                umma_bf16(tmem_base, desc_a + (uint64_t)(k * 2), desc_b + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+            for (int atom = 0; atom < kAtoms; ++atom) {
+                const uint64_t desc_a = umma_descriptor(a_src + atom * a_bytes), desc_b = umma_descriptor(b_src + atom * b_pitch);
+#pragma unroll
+                for (int k = 0; k < kAtomK / 16; ++k)   // 16 bfloat16 = 32 bytes further along the swizzled row
+                    umma_bf16(tmem_base, desc_a + (uint64_t)(k * 2), desc_b + (uint64_t)(k * 2), idesc,
+                              (i > 0 || atom > 0 || k > 0) ? 1u : 0u);
+            }
             umma_commit(smem_u32(&empty_bar[s]));     // the stage is free once these MMAs have read it
         }
         umma_commit(smem_u32(&accum_bar));            // the accumulator is complete once all MMAs are done
@@ -261,7 +277,7 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
 
 // Tensor map of a row-major [rows, k] bfloat16 matrix, box = [box_rows, 64] with 128-byte swizzle.
 bool make_map(CUtensorMap* map, const void* pointer, int rows, int k, int box_rows) {
-    return tma::make_map_bf16(map, pointer, (uint64_t)rows, (uint64_t)k, (uint32_t)box_rows);
+    return tma::make_map_bf16(map, pointer, (uint64_t)rows, (uint64_t)k, (uint32_t)box_rows);   // box of 64 columns
 }
 
 }  // namespace
@@ -292,13 +308,13 @@ LLM_EXPORT int llm_gemm_small_m(const void* x, const void* w, void* out, int m, 
     // K is split across a cluster so that the tiles fill the machine; each rank keeps >= 4 K blocks.  The
     // caller may name the split (it times a few once per shape); 0 asks for about one wave of 148 SMs.
     int split = requested_split > 0 ? requested_split : 148 / tiles;
-    if (split > total_kb / 4) split = total_kb / 4;
+    if (split > total_kb / 2) split = total_kb / 2;
     if (split > kMaxSplit) split = kMaxSplit;
     if (split < 1) split = 1;
     p.split = split;
-    const size_t a_bytes = (size_t)kBlockRows * kBlockK * 2;
-    const size_t b_bytes = ((size_t)p.token_pad * kBlockK * 2 + 1023) & ~(size_t)1023;
-    const size_t stage_bytes = a_bytes + b_bytes;
+    const size_t a_bytes = (size_t)kBlockRows * kAtomK * 2;
+    const size_t b_bytes = ((size_t)p.token_pad * kAtomK * 2 + 1023) & ~(size_t)1023;
+    const size_t stage_bytes = kAtoms * (a_bytes + b_bytes);
     // The ring of stages (about 100 KiB: two CTAs fit on an SM) lets a CTA that was launched early, while the kernels
     // before it still run, request that many bytes of weights before it has to wait for its input.
     static int ring_kib = -1;

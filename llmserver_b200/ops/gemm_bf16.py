@@ -104,9 +104,9 @@ def _plan_for(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> 
             out.copy_(torch.matmul(x, weight.t()))
 
     best_time, best = _time_once(library_product, x.device) * 0.98, 0
-    tiles, k_blocks = -(-cols // 128), -(-inner // 64)
+    tiles, k_blocks = -(-cols // 128), -(-inner // 128)
     for split in SPLITS:
-        if split > 1 and (tiles * split > 600 or k_blocks // split < 4):
+        if split > 1 and (tiles * split > 600 or k_blocks // split < 2):
             continue
         elapsed = _time_once(lambda: _small_m(x, weight, out, split), x.device)
         if elapsed < best_time:
