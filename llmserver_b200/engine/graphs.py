@@ -18,6 +18,7 @@ from typing import Dict, List, Sequence
 import torch
 
 from .. import ops
+from ..ops.library import wait_error_flag
 from .batch import BatchLayout, SequenceSlice, pack, views
 
 
@@ -37,7 +38,7 @@ class DecodeGraph:
         with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
             logits = self.model.step(self.batch)
             tokens = ops.sample(logits, self.batch.temperatures, self.batch.seeds, self.batch.sample_steps)
-            self.result = torch.cat([tokens, self.batch.error_flag])
+            self.result = torch.cat([tokens, self.batch.error_flag, wait_error_flag(device)])
 
     def run(self, slices: List[SequenceSlice], sampling: Sequence) -> List[int]:
         pack(slices, self.layout, self.host_view, self.vocab_size, sampling)

@@ -14,6 +14,7 @@ import torch
 
 from .. import ops
 from ..cache import CacheManager, KVCacheExhaustedError
+from ..ops.library import check_wait_errors, wait_error_flag
 from .batch import SequenceSlice, StepBatch, build_batch
 
 StepEntry = Tuple[object, Sequence[int], Sequence[int]]  # (request id, next tokens, wanted places)
@@ -126,16 +127,17 @@ class StepFunction:
                 self._advance(entries)
                 return []
             tokens = ops.sample(logits, batch.temperatures, batch.seeds, batch.sample_steps)
-            result = torch.cat([tokens, batch.error_flag]).tolist()
+            result = torch.cat([tokens, batch.error_flag, wait_error_flag(self.device)]).tolist()
         self._advance(entries)
-        if result[-1] != 0:
+        if result[-2] != 0:
             raise RuntimeError("a kernel met a block-table entry outside the page pool; the cache bookkeeping is corrupt")
-        return result[:-1]
+        if result[-1] != 0:
+            check_wait_errors()      # raises with the code and clears the flag
+        return result[:-2]
 
     def check_errors(self) -> None:
         """Reads the kernels' error flags of the steps run since the last check (synchronises)."""
-        from ..ops import gemm_bf16
-        gemm_bf16.check_errors()
+        check_wait_errors()
         flags, self.pending_flags = self.pending_flags, []
         if flags and int(torch.stack([flag.reshape(()) for flag in flags]).max().item()) != 0:
             raise RuntimeError("a kernel met a block-table entry outside the page pool; the cache bookkeeping is corrupt")

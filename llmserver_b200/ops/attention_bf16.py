@@ -8,8 +8,7 @@ import os
 
 import torch
 
-from . import gemm_bf16
-from .library import call, check, library, stream_handle
+from .library import call, check, library, stream_handle, wait_error_flag
 
 TILE = 64          # rows per block of the portions kernel, keys per tile of both kernels
 MIN_SPLIT = 256    # fewest keys one decode block walks
@@ -71,7 +70,7 @@ def try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_head
             batch.scratch[key] = scratch
         partial_out, partial_ml = scratch
     page_size = k_pages.shape[2]
-    flag = gemm_bf16.error_flag(qkv.device).data_ptr()
+    flag = wait_error_flag(qkv.device).data_ptr()
     if run_portions and prefill_tcgen05_supported(head_dim, n_q_heads, n_kv_heads, page_size):
         # prompt portions on the tcgen05 kernel (128-row tiles); single tokens, if any, on the decode kernel
         group = n_q_heads // n_kv_heads

@@ -15,26 +15,12 @@ from typing import Optional
 
 import torch
 
-from .library import KernelError, call, library, stream_handle
+from .library import KernelError, call, check_wait_errors, library, stream_handle, wait_error_flag
 
 SMALL_M = 64
-_error_flags = {}
 _use_small_m = os.environ.get("LLMSERVER_B200_SMALL_M_GEMM", "1") != "0"
-
-
-def error_flag(device) -> torch.Tensor:
-    """Device word the kernel sets when one of its bounded waits ran out (never expected)."""
-    device = torch.device(device)
-    if device not in _error_flags:
-        _error_flags[device] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _error_flags[device]
-
-
-def check_errors() -> None:
-    for flag in _error_flags.values():
-        if int(flag.item()) != 0:
-            flag.zero_()
-            raise KernelError("a kernel gave up waiting on one of its barriers (TMA or MMA completion); the step's result is invalid")
+error_flag = wait_error_flag        # the kernels of this package share one flag per device
+check_errors = check_wait_errors
 
 
 def small_m_supported(rows: int, cols: int, inner: int) -> bool:

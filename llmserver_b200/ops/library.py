@@ -128,3 +128,26 @@ def check(tensor: torch.Tensor, name: str, dtype=None, last_dim=None) -> torch.T
     if last_dim is not None and tensor.shape[-1] != last_dim:
         raise KernelError(f"{name}: last dimension {tensor.shape[-1]} != {last_dim}")
     return tensor
+
+
+_wait_error_flags = {}
+
+
+def wait_error_flag(device) -> torch.Tensor:
+    """Device word that a kernel sets when one of its bounded waits (on an mbarrier: a TMA copy or an MMA
+    that never reported completion) ran out.  Never expected; checked after steps by ``check_wait_errors``."""
+    device = torch.device(device)
+    if device.index is None and device.type == "cuda":
+        device = torch.device("cuda", torch.cuda.current_device())
+    if device not in _wait_error_flags:
+        _wait_error_flags[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _wait_error_flags[device]
+
+
+def check_wait_errors() -> None:
+    for flag in _wait_error_flags.values():
+        code = int(flag.item())
+        if code != 0:
+            flag.zero_()
+            raise KernelError(f"a kernel gave up waiting on one of its barriers (code {code}: 2 matrix product, "
+                              "3 decode attention, 4 prompt attention); the step's result is invalid")
