@@ -229,7 +229,9 @@ class Harness:
             self.step_function.release(request_id)
         prompt_len = max(1, MEAN_DECODE_CONTEXT - steps // 2 - warmup)
         # the engine shares the model and the cache that are already on the device
-        engine = Engine(self.model, max_new_tokens=warmup + steps + 2, max_batch_size=batch,
+        # requests that finish their prompt first decode while the others still prefill: leave room for that
+        prefill_steps = -(-batch * prompt_len // max(8192, batch)) + 2
+        engine = Engine(self.model, max_new_tokens=warmup + steps + prefill_steps + 8, max_batch_size=batch,
                         max_num_batched_tokens=max(8192, batch), ignore_eos=True, cache=self.cache,
                         step_function=self.step_function)
         requests = [engine.add_request(prompt_token_ids=self.tokens(prompt_len)) for _ in range(batch)]
@@ -238,11 +240,15 @@ class Harness:
         for _ in range(warmup):
             engine.step()
         torch.cuda.synchronize()
+        before = sum(len(request.generated_token_ids) for request in requests)
         started = time.perf_counter()
         for _ in range(steps):
             engine.step()
         torch.cuda.synchronize()
         elapsed = time.perf_counter() - started
+        generated = sum(len(request.generated_token_ids) for request in requests) - before
+        if generated != batch * steps:
+            raise RuntimeError(f"the timed steps produced {generated} tokens, not {batch} x {steps}")
         h2d = engine.step_function.last_batch_bytes
         for request in requests:
             engine.cancel_request(request.request_id)

@@ -123,7 +123,8 @@ class CacheManager:
                 raise TypeError(f"schedule entry {entry}: unknown cache need {need!r}")
         self.slots = StateSlots(num_slots)
         self.requests: Dict[object, int] = {}   # request -> tokens that have a slot in every group
-        only_full = all(group.window is None for group in self.groups) and not self.state_entries
+        self.has_windows = any(group.window is not None for group in self.groups)
+        only_full = not self.has_windows and not self.state_entries
         self.prefix_sharing = bool(prefix_sharing and only_full and len(self.groups) == 1)
         self.model_identity = model_identity
         self.device = None
@@ -186,6 +187,26 @@ class CacheManager:
             return [-(-total_tokens // self.page_size) for _ in self.groups]
         return [group.pages_for(request_id, total_tokens) for group in self.groups]
 
+    def reserve_null_pages(self) -> List[int]:
+        """Sets one page per group aside for good and returns their ids: rows that only pad a batch to a
+        fixed size point there, so what they write and read touches no request's pages."""
+        for group in self.groups:
+            if getattr(group, "null_page", None) is None:
+                group.null_page = group.pool.allocate()
+        return [group.null_page for group in self.groups]
+
+    def capacity(self) -> List[int]:
+        """Pages per group that requests can hold (the pool minus a page set aside for padding rows)."""
+        return [group.pool.num_pages - (1 if getattr(group, "null_page", None) is not None else 0) for group in self.groups]
+
+    def has_room(self, request_id, total_tokens: int) -> bool:
+        """True when positions < total_tokens already have a slot in every group (no page to allocate)."""
+        limit = total_tokens
+        for group in self.groups:
+            if len(group.tables[request_id]) * self.page_size < limit:
+                return False
+        return True
+
     def available(self) -> List[int]:
         return [group.pool.num_available for group in self.groups]
 
@@ -208,6 +229,8 @@ class CacheManager:
     def advance(self, request_id, num_computed: int) -> int:
         """Called after a step: gives back the pages of windowed groups that no later query of this
         request can read.  Returns how many pages were released."""
+        if not self.has_windows:
+            return 0
         released = 0
         for group in self.groups:
             upto = min(group.passed_pages(num_computed), len(group.tables[request_id]))
@@ -309,6 +332,8 @@ class CacheManager:
                 for page in table:
                     if page != RELEASED:
                         counts[page] = counts.get(page, 0) + 1
+            if getattr(group, "null_page", None) is not None:
+                counts[group.null_page] = counts.get(group.null_page, 0) + 1
             if counts != group.pool.references:
                 raise AssertionError(f"group {group.index}: block tables and reference counts disagree")
         held = set(self.slots.slot_of.values())

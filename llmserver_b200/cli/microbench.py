@@ -128,7 +128,11 @@ def bench_attention(args, prefill: bool) -> dict:
     layers = min(layers, 12)
     caches = [(torch.randn(pages, kv_heads, page, dim, device="cuda", dtype=torch.bfloat16),
                torch.randn(pages, kv_heads, page, dim, device="cuda", dtype=torch.bfloat16)) for _ in range(layers)]
-    tables = torch.arange(len(contexts) * blocks, device="cuda", dtype=torch.int32).view(len(contexts), blocks)
+    if args.shuffle_pages:      # pages of a request scattered over the pool, as after a long run of a server
+        order = torch.randperm(len(contexts) * blocks, generator=torch.Generator().manual_seed(0))
+        tables = order.to(torch.int32).view(len(contexts), blocks).cuda()
+    else:
+        tables = torch.arange(len(contexts) * blocks, device="cuda", dtype=torch.int32).view(len(contexts), blocks)
     stride = (heads + 2 * kv_heads) * dim
     qkv = torch.randn(batch.n_tokens, stride, device="cuda", dtype=torch.bfloat16)
 
@@ -198,6 +202,7 @@ def main(argv=None) -> int:
         p.add_argument("--kv-heads", type=int, default=8)
         p.add_argument("--head-dim", type=int, default=128)
         p.add_argument("--page-size", type=int, default=16)
+        p.add_argument("--shuffle-pages", action="store_true", help="scatter each request's pages over the pool")
 
     gemm = sub.add_parser("gemm")
     common(gemm)

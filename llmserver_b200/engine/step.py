@@ -52,7 +52,7 @@ class StepFunction:
     def enable_graphs(self, max_context: int, max_batch: int = 256) -> None:
         """Decode-only steps of up to ``max_context`` tokens per request run as CUDA graphs from now on."""
         from .graphs import DecodeGraphs
-        self.graphs = DecodeGraphs(self.model, len(self.cache.groups), self.cache.page_size, max_context, max_batch)
+        self.graphs = DecodeGraphs(self.model, self.cache, max_context, max_batch)
 
     def slices_for(self, entries: List[StepEntry]) -> List[SequenceSlice]:
         """Allocates the pages the step needs (all or nothing) and describes each request's share."""
@@ -63,14 +63,20 @@ class StepFunction:
             seen.add(request_id)
             if request_id not in self.computed:
                 raise KeyError(f"request {request_id!r} was not admitted")
-        # check the whole step against what is available before allocating anything
-        totals = [0] * len(self.cache.groups)
-        for request_id, tokens, _ in entries:
-            needed = self.cache.pages_needed(request_id, self.computed[request_id] + len(tokens))
-            totals = [a + b for a, b in zip(totals, needed)]
-        for group, (total, available) in enumerate(zip(totals, self.cache.available())):
-            if total > available:
-                raise KVCacheExhaustedError(f"the step needs {total} pages in cache group {group}, {available} are available")
+        # check the whole step against what is available before allocating anything (entries that stay inside
+        # their last page, as most decode tokens do, need nothing)
+        growing = [entry for entry in entries
+                   if not self.cache.has_room(entry[0], self.computed[entry[0]] + len(entry[1]))]
+        if growing:
+            totals = [0] * len(self.cache.groups)
+            for request_id, tokens, _ in growing:
+                needed = self.cache.pages_needed(request_id, self.computed[request_id] + len(tokens))
+                totals = [a + b for a, b in zip(totals, needed)]
+            for group, (total, available) in enumerate(zip(totals, self.cache.available())):
+                if total > available:
+                    raise KVCacheExhaustedError(f"the step needs {total} pages in cache group {group}, {available} are available")
+            for request_id, tokens, _ in growing:
+                self.cache.ensure(request_id, self.computed[request_id] + len(tokens))
         limit = self.model.spec.max_positions
         slices = []
         for request_id, tokens, want in entries:
@@ -78,7 +84,6 @@ class StepFunction:
             if limit is not None and start + len(tokens) > limit:
                 raise ValueError(f"request {request_id!r} would reach {start + len(tokens)} tokens; "
                                  f"the model's max_position_embeddings is {limit}")
-            self.cache.ensure(request_id, start + len(tokens))
             slices.append(SequenceSlice(request_id, tokens, start, want,
                                         [self.cache.table(request_id, group) for group in range(len(self.cache.groups))],
                                         self.cache.slot_of(request_id)))
@@ -91,9 +96,11 @@ class StepFunction:
         return batch
 
     def _advance(self, entries: List[StepEntry]) -> None:
+        windows = self.cache.has_windows
         for request_id, tokens, _ in entries:
             self.computed[request_id] += len(tokens)
-            self.cache.advance(request_id, self.computed[request_id])
+            if windows:
+                self.cache.advance(request_id, self.computed[request_id])
         self.steps_run += 1
 
     def run(self, entries: List[StepEntry]) -> torch.Tensor:
