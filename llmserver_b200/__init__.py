@@ -12,9 +12,9 @@ __version__ = "0.1.0"
 
 def __getattr__(name):
     # heavier pieces are imported on first use so that configuration tools start quickly
-    if name in ("Engine", "SamplingParams"):
-        from .engine.engine import Engine, SamplingParams
-        return {"Engine": Engine, "SamplingParams": SamplingParams}[name]
+    if name == "Engine":
+        from .engine.engine import Engine
+        return Engine
     if name in ("load_model", "random_model"):
         from . import models
         return getattr(models, name)

@@ -19,7 +19,6 @@ fit raises ``KVCacheExhaustedError``.
 from __future__ import annotations
 
 import itertools
-from dataclasses import dataclass
 from typing import Dict, Iterable, List, Optional, Sequence
 
 import torch
@@ -29,14 +28,6 @@ from ..sampling import Sampler, SamplingRow
 from .request import Request, RequestFinishReason, RequestStatus
 from .scheduler import PageBudget, Scheduler, SchedulerOutput
 from .step import StepFunction
-
-
-@dataclass
-class SamplingParams:
-    temperature: float = 0.0
-    seed: Optional[int] = None
-    max_new_tokens: Optional[int] = None
-    ignore_eos: Optional[bool] = None
 
 
 class Engine:

@@ -15,6 +15,7 @@ import torch
 from .. import ops
 from ..cache import CacheManager, KVCacheExhaustedError
 from ..ops.library import check_wait_errors, wait_error_flag
+from ..sampling import Sampler
 from .batch import SequenceSlice, StepBatch, build_batch
 
 StepEntry = Tuple[object, Sequence[int], Sequence[int]]  # (request id, next tokens, wanted places)
@@ -31,6 +32,7 @@ class StepFunction:
         self.last_batch_bytes = 0   # size of the last step's host-to-device copy
         self.graphs = None
         self.graph_steps = 0
+        self.sampler = Sampler(self.device)
 
     # ------------------------------------------------------------------ request lifetime
     def admit(self, request_id, prompt: Sequence[int] = None) -> int:
@@ -133,7 +135,7 @@ class StepFunction:
                 self.pending_flags.append(batch.error_flag)
                 self._advance(entries)
                 return []
-            tokens = ops.sample(logits, batch.temperatures, batch.seeds, batch.sample_steps)
+            tokens = (sampler or self.sampler).from_batch(logits, batch)
             result = torch.cat([tokens, batch.error_flag, wait_error_flag(self.device)]).tolist()
         self._advance(entries)
         if result[-2] != 0:

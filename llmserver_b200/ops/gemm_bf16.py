@@ -42,7 +42,7 @@ def _row_bucket(rows: int) -> int:
 _flush_buffer = {}
 
 
-def _time_once(run, device, repeats: int = 3) -> float:
+def _time_once(run, device, repeats: int = 5) -> float:
     """Fastest of a few runs, each from a cold L2: a buffer larger than the cache is overwritten before
     every run, so that the weights come from HBM as they do inside a model step."""
     if device not in _flush_buffer:

@@ -36,7 +36,8 @@ class Sampler:
         return self.sample_on_device(logits, rows).tolist()
 
     def from_batch(self, logits: torch.Tensor, batch) -> torch.Tensor:
-        """Samples with the per-row inputs that crossed to the device inside the step's batch."""
+        """Samples with the per-row inputs that crossed to the device inside the step's batch; the tokens
+        stay on the device (the step function reads them back together with its error flags)."""
         return ops.sample(logits, batch.temperatures, batch.seeds, batch.sample_steps)
 
     def sample_on_device(self, logits: torch.Tensor, rows: Sequence[SamplingRow]) -> torch.Tensor:

@@ -127,3 +127,41 @@ def test_schedule_with_a_repeated_layer_and_a_shared_cache(tiny_folders, dtype):
     config, weights = plain_folder(folder)
     want = plain_model.forward(config, weights, tokens, order=[(0, None), (1, None), (0, None), (1, 1)]).numpy()
     assert_close(got, want, dtype, "repeated layer + shared cache")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_pre_norm_block_alone(dtype):
+    """One block (norm, attention, norm, feed-forward around the 32-bit stream) against the plain decoder layer,
+    with the not-yet-added output of a previous block handed in and its own handed out."""
+    from llmserver_b200.parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, EntryCache
+    hidden, heads, kv_heads, dim, inter, eps, theta = 40, 5, 5, 16, 72, 2e-6, 20000.0
+    config = {"hidden_size": hidden, "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": dim,
+              "rms_norm_eps": eps}
+    run = runtime(dtype)
+    mixer_params = {"hidden": hidden, "heads": heads, "kv_heads": kv_heads, "head_dim": dim, "scale": dim ** -0.5,
+                    "qk_norm": True, "eps": eps, "window": None}
+    plain_weights, parts = {}, {}
+    for role, registry, kind, params, prefix in (
+            ("mixer", MIXERS, "gqa_attention", mixer_params, "self_attn."),
+            ("feed_forward", FEED_FORWARDS, "swiglu", {"hidden": hidden, "intermediate": inter}, "mlp."),
+            ("mixer_norm", NORMS, "rmsnorm", {"width": hidden, "eps": eps}, "input_layernorm."),
+            ("feed_forward_norm", NORMS, "rmsnorm", {"width": hidden, "eps": eps}, "post_attention_layernorm.")):
+        cls = registry.get(kind)
+        weights = {}
+        for index, (name, declaration) in enumerate(cls.declare_weights(params).items()):
+            values = rand(declaration.shape, 300 + 10 * len(plain_weights) + index, 0.2)
+            weights[name] = (values + 1 if declaration.kind == "norm" else values).to(dtype)
+            plain_weights[prefix + name] = weights[name].double()
+        parts[role] = cls(params, {k: v.to(DEVICE) for k, v in weights.items()}, run)
+    parts["mixer"].attach(POSITION_ENCODINGS.get("rotary")({"head_dim": dim, "theta": theta}, {}, run))
+    block = BLOCKS.get("pre_norm")({}, parts["mixer"], parts["feed_forward"], parts["mixer_norm"], parts["feed_forward_norm"])
+    tokens = 23
+    stream, pending = rand((tokens, hidden), 70), rand((tokens, hidden), 71).to(dtype)
+    pages = torch.zeros((2, 8, kv_heads, 4, dim), dtype=dtype, device=DEVICE)
+    cache = EntryCache(k_pages=pages[0], v_pages=pages[1], group=0, writes=True)
+    residual = stream.to(DEVICE)
+    residual, delta = block.forward(residual, pending.to(DEVICE), one_sequence_batch(0, tokens, 6), cache)
+    got = residual.double().cpu() + delta.double().cpu()
+    cosine, sine = plain_model.rope_tables(torch.arange(tokens), dim, theta, torch.float64)
+    want, _ = plain_model.decoder_layer(stream.double() + pending.double(), plain_weights, config, cosine, sine)
+    close(got, want, dtype, "pre-norm block")
