@@ -55,6 +55,11 @@ def main(argv=None) -> int:
     parser.add_argument("--block-size", type=int, default=16)
     parser.add_argument("--max-num-batched-tokens", type=int, default=16384)
     parser.add_argument("--no-cuda-graphs", action="store_true")
+    parser.add_argument("--mixed-requests", type=int, default=0,
+                        help="instead of the grid: this many requests with uniform-random prompt lengths, all queued at once "
+                             "and served by continuous batching (prompt portions and decode tokens share each step)")
+    parser.add_argument("--mixed-prompt-range", type=_int_list, default=[128, 2048], help="shortest,longest prompt of --mixed-requests")
+    parser.add_argument("--max-batch-size", type=int, default=0, help="request slots for --mixed-requests (default: all of them)")
     parser.add_argument("--json", action="store_true", help="print the results as JSON")
     parser.add_argument("--out-dir", help="also write results.json there")
     args = parser.parse_args(argv)
@@ -80,6 +85,34 @@ def main(argv=None) -> int:
     vocab = model.spec.vocab_size
     generator = torch.Generator().manual_seed(args.seed)
     results = []
+    if args.mixed_requests:
+        import random
+        rng = random.Random(args.seed)
+        low, high = args.mixed_prompt_range
+        lengths = [rng.randint(low, high) for _ in range(args.mixed_requests)]
+        slots = args.max_batch_size or args.mixed_requests
+        longest = high + args.output_tokens
+        engine = Engine(model, max_new_tokens=args.output_tokens, max_batch_size=slots,
+                        max_num_batched_tokens=args.max_num_batched_tokens,
+                        kv_cache_num_blocks=slots * -(-longest // args.block_size) + 8, kv_cache_block_size=args.block_size,
+                        ignore_eos=True, prefix_caching=False, cuda_graphs=not args.no_cuda_graphs, max_context=longest)
+        prompts = [torch.randint(0, vocab, (length,), generator=generator).tolist() for length in lengths]
+        run_once(engine, [prompt[:64] for prompt in prompts[:min(4, len(prompts))]], 4)      # warm-up
+        runs = []
+        for _ in range(args.repeats):
+            steps_before = engine.stats["steps"]
+            seconds = run_once(engine, prompts, args.output_tokens)
+            runs.append((seconds, engine.stats["steps"] - steps_before))
+        seconds, steps = sorted(runs)[len(runs) // 2]
+        row = {"mixed_requests": args.mixed_requests, "prompt_tokens_total": sum(lengths), "output_tokens": args.output_tokens,
+               "token_budget": args.max_num_batched_tokens, "seconds": round(seconds, 4), "steps": steps,
+               "output_tokens_per_s": round(args.mixed_requests * args.output_tokens / seconds, 1),
+               "all_tokens_per_s": round((sum(lengths) + args.mixed_requests * args.output_tokens) / seconds, 1),
+               "preemptions": engine.stats["preemptions"]}
+        results.append(row)
+        if not args.json:
+            print(row, flush=True)
+        args.prompt_tokens = []
     for prompt_tokens in args.prompt_tokens:
         for batch in args.batch_sizes:
             longest = prompt_tokens + args.output_tokens

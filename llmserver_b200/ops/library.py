@@ -102,7 +102,14 @@ def call(name: str, *args) -> None:
         raise KernelError(f"{name} failed ({status}): {library().llm_last_error().decode()}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_handle() -> int:
+    """The raw handle of PyTorch's current stream on the current device (asked for at every launch: it is
+    another stream while a CUDA graph is being captured)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
