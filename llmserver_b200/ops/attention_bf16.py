@@ -11,8 +11,8 @@ import torch
 from .library import call, check, library, stream_handle, wait_error_flag
 
 TILE = 64          # rows per block of the portions kernel, keys per tile of both kernels
-MIN_SPLIT = 256    # fewest keys one decode block walks
-TARGET_BLOCKS = 296   # one wave of two blocks per SM on 148 SMs
+MIN_SPLIT = 192    # fewest keys one decode block walks
+WAVE_BLOCKS = 296   # one wave of two blocks per SM on 148 SMs
 
 
 PREFILL_KERNEL = os.environ.get("LLMSERVER_B200_PREFILL_ATTENTION", "tcgen05")   # or "mma"
@@ -41,9 +41,15 @@ def plan(batch, group: int, n_kv_heads: int):
     split_len, max_splits = MIN_SPLIT, 1
     if run_decode:
         longest = max(context for context, length in zip(batch.context_lens, batch.q_lens) if length == 1)
-        # the longest splits that still fill the machine; never shorter than MIN_SPLIT keys
-        while split_len * 2 < longest and singles * n_kv_heads * -(-longest // (split_len * 2)) >= TARGET_BLOCKS:
-            split_len *= 2
+        # As many equal splits of the longest context as give about one wave of blocks (two per SM); with a
+        # wave's worth of (sequence, kv head) pairs already, no split at all.  Measured on the 8B head shape:
+        # equal splits beat ragged ones, and one wave beats one and a half.
+        pairs = singles * n_kv_heads
+        splits = max(1, min(WAVE_BLOCKS // pairs, -(-longest // MIN_SPLIT)))
+        split_len = max(MIN_SPLIT, -(-(-(-longest // splits)) // TILE) * TILE)
+        forced = os.environ.get("LLMSERVER_B200_DECODE_SPLIT")
+        if forced:
+            split_len = int(forced)
         max_splits = -(-longest // split_len) + 1     # + 1: a window may start inside a tile
     cached = (run_portions, tiles, run_decode, split_len, max_splits)
     batch.scratch[key] = cached
