@@ -158,23 +158,43 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
     const int group = p.n_q_heads / p.n_kv_heads;
     const int tokens_per_tile = kRows / group;
     const int kv_head = blockIdx.y;
-    int seq = 0, tile = blockIdx.x;
+    // Work of this CTA: one or two row tiles of one sequence.  Tile t of a causal prompt sees about t + 1 key
+    // tiles, so tile T - 1 - b is paired with tile b: every CTA of a sequence then has the same amount of work.
+    int seq = 0, pair = blockIdx.x, first_tile = 0, second_tile = 0;
     for (; seq < p.n_seqs; ++seq) {
         const int q_len = p.q_start[seq + 1] - p.q_start[seq];
         const int tiles = (q_len == 1 && p.skip_single) ? 0 : (q_len * group + kRows - 1) / kRows;
-        if (tile < tiles) {
-            tile = tiles - 1 - tile;     // later tiles see more keys: start the long ones first
+        const int pairs = (tiles + 1) / 2;
+        if (pair < pairs) {
+            first_tile = tiles - 1 - pair;
+            second_tile = pair;
             break;
         }
-        tile -= tiles;
+        pair -= pairs;
     }
     if (seq >= p.n_seqs) return;
+    const int passes = second_tile < first_tile ? 2 : 1;
     const int token0 = p.q_start[seq];
     const int q_len = p.q_start[seq + 1] - token0;
     const int context = p.context_len[seq];
     const int n_rows = q_len * group;
-    const int first_row = tile * kRows;
     const int base_position = context - q_len;
+    const int* table = p.block_tables + (size_t)seq * p.max_blocks;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) failed = 0;
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = tmem_slot;
+
+  for (int pass = 0; pass < passes; ++pass) {
+    const int tile = pass == 0 ? first_tile : second_tile;
+    const int first_row = tile * kRows;
     const int first_token = first_row / group;
     const int last_row = min(first_row + kRows, n_rows) - 1;
     const int high_key = base_position + last_row / group;
@@ -182,11 +202,9 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
     if (p.window > 0) low_key = max(0, base_position + first_token - p.window + 1);
     const int first_tile_key = (low_key / kKeys) * kKeys;
     const int n_tiles = (high_key - first_tile_key) / kKeys + 1;
-    const int* table = p.block_tables + (size_t)seq * p.max_blocks;
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // fresh barriers for every pass: at the end of a pass every copy has landed and every MMA has retired
     if (threadIdx.x == 0) {
-        failed = 0;
         mbar_init(smem_u32(&q_full), 1);
         for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&k_full[s]), 1);
@@ -200,14 +218,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
         mbar_init(smem_u32(&o_done), 1);
         tma::mbar_fence_init();
     }
-    if (warp == 5) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    fence_before();
     __syncthreads();
-    fence_after();
-    const uint32_t tmem = tmem_slot;
 
     if (warp == 4) {
         // ---------------------------------------------------------------- producer
@@ -369,7 +380,22 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
         }
     }
     fence_before();
-    __syncthreads();
+    __syncthreads();      // end of the pass: tensor memory, shared tiles and barriers are idle
+    fence_after();
+    if (pass + 1 < passes && threadIdx.x == 0) {
+        tma::mbar_inval(smem_u32(&q_full));
+        for (int s = 0; s < kStages; ++s) {
+            tma::mbar_inval(smem_u32(&k_full[s]));
+            tma::mbar_inval(smem_u32(&v_full[s]));
+            tma::mbar_inval(smem_u32(&kv_free[s]));
+        }
+        for (int b = 0; b < 2; ++b) {
+            tma::mbar_inval(smem_u32(&s_ready[b]));
+            tma::mbar_inval(smem_u32(&p_ready[b]));
+        }
+        tma::mbar_inval(smem_u32(&o_done));
+    }
+  }
     if (failed && threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 4);
     if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
 }
@@ -383,14 +409,14 @@ LLM_EXPORT int llm_attention_prefill_tcgen05_supports(int head_dim, int n_q_head
     return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64;
 }
 
-// total_tiles: sum over the sequences it handles of ceil(q_len * group / 128); sequences of one token are
-// skipped when skip_single is set (the decode kernel takes them).
+// total_pairs: sum over the sequences it handles of ceil(ceil(q_len * group / 128) / 2): each CTA takes a row
+// tile and its mirror; sequences of one token are skipped when skip_single is set (the decode kernel takes them).
 LLM_EXPORT int llm_attention_prefill_tcgen05(const void* q, int q_stride, int n_tokens, const void* k_pages, const void* v_pages,
                                              const int* block_tables, int max_blocks, const int* q_start,
                                              const int* context_len, void* out, int n_seqs, int n_q_heads, int n_kv_heads,
                                              int head_dim, int page_size, float scale, int window, int skip_single,
-                                             int total_tiles, int* error_flag, cudaStream_t stream) {
-    if (total_tiles <= 0) return LLM_OK;
+                                             int total_pairs, int* error_flag, cudaStream_t stream) {
+    if (total_pairs <= 0) return LLM_OK;
     if (!llm_attention_prefill_tcgen05_supports(head_dim, n_q_heads, n_kv_heads, page_size) || !aligned16(q) || q_stride % 8) {
         llm_set_error("attention_prefill_tcgen05: unsupported sizes (head_dim %d, %d/%d heads, page %d)", head_dim, n_q_heads,
                       n_kv_heads, page_size);
@@ -449,7 +475,7 @@ LLM_EXPORT int llm_attention_prefill_tcgen05(const void* q, int q_stride, int n_
         }
         configured = true;
     }
-    dim3 grid(total_tiles, n_kv_heads);
+    dim3 grid(total_pairs, n_kv_heads);
     llm_launch(attention_prefill_tcgen05_kernel, grid, kThreads, shared, stream, map_q, map_k, map_v, p);
     return llm_check_launch("attention_prefill_tcgen05");
 }

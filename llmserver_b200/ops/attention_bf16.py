@@ -80,7 +80,8 @@ def try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_head
     if run_portions and prefill_tcgen05_supported(head_dim, n_q_heads, n_kv_heads, page_size):
         # prompt portions on the tcgen05 kernel (128-row tiles); single tokens, if any, on the decode kernel
         group = n_q_heads // n_kv_heads
-        big_tiles = sum(-(-length * group // PREFILL_TILE) for length in batch.q_lens if length > 1 or not run_decode)
+        # a block takes a 128-row tile and its mirror image (the light one with the heavy one)
+        big_tiles = sum((-(-length * group // PREFILL_TILE) + 1) // 2 for length in batch.q_lens if length > 1 or not run_decode)
         call("llm_attention_prefill_tcgen05", qkv.data_ptr(), q_stride, batch.n_tokens, k_pages.data_ptr(), v_pages.data_ptr(),
              block_tables.data_ptr(), block_tables.shape[-1], batch.q_start.data_ptr(), batch.context_len.data_ptr(),
              out.data_ptr(), batch.n_seqs, n_q_heads, n_kv_heads, head_dim, page_size, float(scale), int(window),
