@@ -76,7 +76,7 @@ class Engine:
         self.cuda_graphs = (self.device.type == "cuda") if cuda_graphs is None else bool(cuda_graphs)
         if self.cuda_graphs and self.step_function.graphs is None:
             self.step_function.enable_graphs(min(max_context, self.num_blocks * self.block_size), max_batch_size)
-        self.stats = {"steps": 0, "preemptions": 0, "tokens": 0, "prefill_tokens": 0, "decode_tokens": 0}
+        self.stats = {"steps": 0, "preemptions": 0, "tokens": 0, "prefill_tokens": 0, "decode_tokens": 0, "prefix_tokens": 0}
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt=None, prompt_token_ids: Optional[Sequence[int]] = None,
@@ -155,6 +155,7 @@ class Engine:
                 for request in self.scheduler.commit(out):
                     covered = self.step_function.admit(request.request_id, request.prefill_token_ids)
                     request.num_computed_tokens = covered
+                    self.stats["prefix_tokens"] += covered
                 return out
             if len(self.scheduler.running) <= 1:
                 raise KVCacheExhaustedError(f"Required pages {out.pages_needed} exceed the pages available {self.cache.available()}")

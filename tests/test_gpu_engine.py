@@ -155,3 +155,45 @@ def test_cuda_graph_decode_gives_the_same_tokens(tiny_folders, dtype):
         assert outputs[True] == outputs[False]
     for prompt, tokens in zip(prompts, outputs[True]):
         assert_tokens_are_argmax_of_plain(folder, prompt, tokens, dtype)
+
+
+def test_random_serving_schedule_changes_no_token(tiny_folders):
+    """Thirty requests of random lengths arrive over time into a small cache (preemptions), with shared
+    beginnings (prefix pages), a small token budget (portions beside decode tokens), CUDA graphs of several
+    buckets, greedy and sampled: in 32-bit every request must produce exactly the tokens it produces alone."""
+    import random
+    from llmserver_b200 import Engine
+    folder = tiny_folders["b"]      # one cache group without a window: shared prefixes are on
+    rng = random.Random(3)
+    common = tokens_for(509, 48, 500)
+    jobs = []
+    for index in range(30):
+        prompt = tokens_for(509, rng.randint(1, 90), 600 + index)
+        if index % 3 == 0:
+            prompt = common[:rng.choice([16, 32, 48])] + prompt
+        jobs.append(dict(prompt=prompt, new=rng.randint(1, 40), temperature=rng.choice([0.0, 0.0, 0.7]), seed=900 + index,
+                         arrives=rng.randint(0, 60)))
+    engine = Engine(folder, max_new_tokens=64, max_batch_size=6, max_num_batched_tokens=48, prefill_chunk_size=20,
+                    kv_cache_num_blocks=22, kv_cache_block_size=16, ignore_eos=True, dtype="float32", max_context=256)
+    requests, step = {}, 0
+    while len(requests) < len(jobs) or engine.scheduler.waiting or engine.scheduler.running:
+        for index, job in enumerate(jobs):
+            if index not in requests and job["arrives"] <= step:
+                requests[index] = engine.add_request(prompt_token_ids=job["prompt"], max_new_tokens=job["new"],
+                                                     temperature=job["temperature"], seed=job["seed"])
+        engine.step()
+        step += 1
+        assert step < 5000
+    engine.cache.check_invariants()
+    assert engine.cache.available() == engine.cache.capacity()
+    assert engine.stats["preemptions"] > 0 and engine.step_function.graph_steps > 0
+    assert engine.stats["prefix_tokens"] > 0, "prefixes were meant to be shared"
+    alone = Engine(engine.model, max_new_tokens=64, max_batch_size=1, max_num_batched_tokens=256, kv_cache_num_blocks=24,
+                   kv_cache_block_size=16, ignore_eos=True, prefix_caching=False, cuda_graphs=False, max_context=256)
+    for index, job in enumerate(jobs):
+        request = alone.add_request(prompt_token_ids=job["prompt"], max_new_tokens=job["new"], temperature=job["temperature"],
+                                    seed=job["seed"])
+        while alone.step():
+            pass
+        assert requests[index].generated_token_ids == request.generated_token_ids, f"request {index} differs"
+        assert len(request.generated_token_ids) == job["new"]
