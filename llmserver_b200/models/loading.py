@@ -1,6 +1,9 @@
 """From a model folder, or from a configuration and a seed, to a model on the device."""
 from __future__ import annotations
 
+import json
+import os
+
 import torch
 
 from ..config.registry import ARCHITECTURES, read_config
@@ -28,9 +31,25 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda:0") -> DecoderMode
     config, architecture = read_config(model_dir)
     spec = architecture.build_spec(config)
     runtime = Runtime(as_dtype(dtype), torch.device(device))
+    eos = generation_eos_ids(model_dir)
+    if eos is not None:
+        spec.eos_token_ids = eos
     model = DecoderModel(spec, CheckpointSource(model_dir, spec, runtime.dtype, runtime.device), runtime)
     model.config = config
     return model
+
+
+def generation_eos_ids(model_dir: str):
+    """End-of-sequence ids of generation_config.json when the folder has one; they take precedence over
+    config.json's, as in the reference (utils/engine.py:107-117)."""
+    path = os.path.join(model_dir, "generation_config.json")
+    if not os.path.isfile(path):
+        return None
+    with open(path) as handle:
+        eos = json.load(handle).get("eos_token_id")
+    if eos is None:
+        return None
+    return (int(eos),) if isinstance(eos, int) else tuple(int(token) for token in eos)
 
 
 def random_model(config, seed: int, dtype="bfloat16", device="cuda:0", spec=None) -> DecoderModel:

@@ -95,3 +95,28 @@ def test_schedule_validation():
     spec.schedule = [ScheduleEntry(5)]
     with pytest.raises(ValueError):
         spec.validate()
+
+
+def test_a_published_qwen3_config_json_parses():
+    """The keys of a published Qwen3-8B config.json, nulls and unused keys included."""
+    raw = {"architectures": ["Qwen3ForCausalLM"], "attention_bias": False, "attention_dropout": 0.0, "bos_token_id": 151643,
+           "eos_token_id": 151645, "head_dim": 128, "hidden_act": "silu", "hidden_size": 4096, "initializer_range": 0.02,
+           "intermediate_size": 12288, "max_position_embeddings": 40960, "max_window_layers": 36, "model_type": "qwen3",
+           "num_attention_heads": 32, "num_hidden_layers": 36, "num_key_value_heads": 8, "rms_norm_eps": 1e-06,
+           "rope_scaling": None, "rope_theta": 1000000, "sliding_window": None, "tie_word_embeddings": False,
+           "torch_dtype": "bfloat16", "transformers_version": "4.51.0", "use_cache": True, "use_sliding_window": False,
+           "vocab_size": 151936}
+    config = Qwen3Config.from_dict(raw)
+    assert config.layer_types == ("full_attention",) * 36 and config.sliding_window is None
+    assert config.eos_token_id == (151645,) and config.rope_theta == 1e6 and config.head_dim == 128
+    spec = ARCHITECTURES["Qwen3ForCausalLM"].build_spec(config)
+    assert len(spec.layers) == 36 and spec.max_positions == 40960 and not spec.tie_head
+
+
+def test_generation_config_overrides_eos(tmp_path):
+    from llmserver_b200.models.loading import generation_eos_ids
+    assert generation_eos_ids(str(tmp_path)) is None
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [151645, 151643], "temperature": 0.6}))
+    assert generation_eos_ids(str(tmp_path)) == (151645, 151643)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 7}))
+    assert generation_eos_ids(str(tmp_path)) == (7,)
