@@ -152,6 +152,103 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const W* __res
     }
 }
 
+// The same operation for head sizes 64, 128 and 256 with aligned operands: LANES = head_dim / 16 lanes share a
+// head, each holding 8 elements of the low half and the 8 elements of the high half that rotate with them
+// (16-byte accesses), so a warp works on 32 / LANES heads at a time.
+template <typename T, typename W, int LANES>
+__global__ void qk_norm_rope_kv_write_wide_kernel(T* __restrict__ qkv, const W* __restrict__ q_weight,
+                                                  const W* __restrict__ k_weight, const float* __restrict__ inv_freq,
+                                                  const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                                  const int* __restrict__ block_tables, int max_blocks,
+                                                  T* __restrict__ k_pages, T* __restrict__ v_pages, int n_q_heads,
+                                                  int n_kv_heads, int page_size, int num_pages, float eps, int write_cache,
+                                                  int* __restrict__ error_flag, int heads_per_block) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int kHalf = LANES * 8, kDim = 2 * kHalf;
+    __shared__ float2 rotation[kHalf];
+    const int token = blockIdx.y;
+    const int total_heads = n_q_heads + 2 * n_kv_heads;
+    const int position = positions[token];
+    if (inv_freq) {
+        for (int i = threadIdx.x; i < kHalf; i += blockDim.x) {
+            const float angle = (float)position * inv_freq[i];
+            rotation[i] = make_float2(cosf(angle), sinf(angle));
+        }
+    }
+    __syncthreads();
+    const int groups_per_block = blockDim.x / LANES;
+    const int group = threadIdx.x / LANES, sub = threadIdx.x % LANES;
+    const int first_head = blockIdx.x * heads_per_block;
+    const int end_head = min(first_head + heads_per_block, total_heads);
+    const int rounds = (end_head - first_head + groups_per_block - 1) / groups_per_block;
+    for (int round = 0; round < rounds; ++round) {        // the same number of rounds for every lane of a warp
+        const int head = first_head + round * groups_per_block + group;
+        bool active = head < end_head;
+        const bool is_q = head < n_q_heads;
+        const bool is_k = !is_q && head < n_q_heads + n_kv_heads;
+        T* src = qkv + (size_t)token * total_heads * kDim + (size_t)(active ? head : first_head) * kDim;
+        T* dst = src;
+        if (active && !is_q) {
+            if (!write_cache) {
+                active = false;
+            } else {
+                const int kv_head = is_k ? head - n_q_heads : head - n_q_heads - n_kv_heads;
+                const int page = block_tables[(size_t)seq_of_token[token] * max_blocks + position / page_size];
+                if (page < 0 || page >= num_pages) {
+                    if (sub == 0) atomicExch(error_flag, 1 + token);
+                    active = false;
+                } else {
+                    T* pages = is_k ? k_pages : v_pages;
+                    dst = pages + (((size_t)page * n_kv_heads + kv_head) * page_size + position % page_size) * kDim;
+                }
+            }
+        }
+        float low[8], high[8];
+        if (active) {
+            load8<T>(src + sub * 8, low);
+            load8<T>(src + kHalf + sub * 8, high);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) low[j] = high[j] = 0.0f;
+        }
+        // every lane of the warp takes part in the shuffles, whatever kind of head its group holds
+        float sum_squares = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sum_squares += low[j] * low[j] + high[j] * high[j];
+#pragma unroll
+        for (int offset = LANES / 2; offset > 0; offset >>= 1) sum_squares += __shfl_xor_sync(0xffffffffu, sum_squares, offset);
+        const W* weight = is_q ? q_weight : (is_k ? k_weight : nullptr);
+        if (active && (is_q || is_k)) {
+            if (weight) {
+                const float inverse = rsqrtf(sum_squares / (float)kDim + eps);
+                float w_low[8], w_high[8];
+                load8<W>(weight + sub * 8, w_low);
+                load8<W>(weight + kHalf + sub * 8, w_high);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    low[j] = low[j] * inverse * w_low[j];
+                    high[j] = high[j] * inverse * w_high[j];
+                }
+            }
+            if (inv_freq) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float2 r = rotation[sub * 8 + j];      // (cos, sin)
+                    const float rotated_low = low[j] * r.x - high[j] * r.y;
+                    const float rotated_high = high[j] * r.x + low[j] * r.y;
+                    low[j] = rotated_low;
+                    high[j] = rotated_high;
+                }
+            }
+        }
+        if (active) {
+            store8<T>(dst + sub * 8, low);
+            store8<T>(dst + kHalf + sub * 8, high);
+        }
+    }
+}
+
 LLM_EXPORT int llm_qk_norm_rope_kv_write(void* qkv, const void* q_weight, const void* k_weight, const float* inv_freq,
                                          const int* positions, const int* seq_of_token, const int* block_tables,
                                          int max_blocks, void* k_pages, void* v_pages, int n_tokens, int n_q_heads,
@@ -178,6 +275,28 @@ LLM_EXPORT int llm_qk_norm_rope_kv_write(void* qkv, const void* q_weight, const 
                             aligned16(v_pages) && aligned16(q_weight) && aligned16(k_weight);
     dim3 grid((total_heads + heads_per_block - 1) / heads_per_block, n_tokens);
     const size_t shared = (size_t)(head_dim / 2) * sizeof(float2);
+    // head sizes 64 / 128 / 256 with aligned operands: the wide form
+    const bool wide = vector_form && (head_dim == 64 || head_dim == 128 || head_dim == 256) && aligned16(q_weight) && aligned16(k_weight);
+    if (wide) {
+        const int wide_threads = 256;
+        const int lanes = head_dim / 16;
+        const int wide_heads_per_block = n_tokens >= 256 ? total_heads : (wide_threads / lanes < total_heads ? wide_threads / lanes : total_heads);
+        dim3 wide_grid((total_heads + wide_heads_per_block - 1) / wide_heads_per_block, n_tokens);
+#define LLM_ROPE_WIDE(LANES)                                                                                          \
+        LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype, (llm_launch(qk_norm_rope_kv_write_wide_kernel<T, W, LANES>, wide_grid, wide_threads, 0, stream, \
+                                      (T*)qkv, (const W*)q_weight, (const W*)k_weight, inv_freq, positions, seq_of_token, \
+                                      block_tables, max_blocks, (T*)k_pages, (T*)v_pages, n_q_heads, n_kv_heads, \
+                                      page_size, num_pages, eps, write_cache, error_flag, wide_heads_per_block)));
+        if (lanes == 4) {
+            LLM_ROPE_WIDE(4)
+        } else if (lanes == 8) {
+            LLM_ROPE_WIDE(8)
+        } else {
+            LLM_ROPE_WIDE(16)
+        }
+#undef LLM_ROPE_WIDE
+        return llm_check_launch("qk_norm_rope_kv_write");
+    }
 #define LLM_ROPE_LAUNCH(HELD)                                                                                        \
         LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype, (llm_launch(qk_norm_rope_kv_write_kernel<T, W, HELD>, grid, warps * 32, shared, stream,  \
                                       (T*)qkv, (const W*)q_weight, (const W*)k_weight, inv_freq, positions, seq_of_token, \
