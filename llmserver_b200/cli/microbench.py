@@ -116,6 +116,9 @@ def bench_attention(args, prefill: bool) -> dict:
     from ..ops import attention_bf16
 
     heads, kv_heads, dim, page = args.heads, args.kv_heads, args.head_dim, args.page_size
+    if not attention_bf16.supported(dim, heads, kv_heads):
+        return {"workload": "attention-prefill" if prefill else "attention-decode", "heads": heads, "kv_heads": kv_heads, "head_dim": dim,
+                "unsupported": "the tensor-core kernels do not take these sizes; the engine runs the generic kernel for them"}
     if prefill:
         contexts, q_lens = [args.tokens], [args.tokens]
     else:

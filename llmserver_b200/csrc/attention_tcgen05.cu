@@ -7,7 +7,8 @@
 // of 64 (whole cache pages), from the first key in the tile's window to the last token's position:
 //
 //   producer warp   TMA: the Q tile once (a 4-D box: 64 columns x G heads x 1 kv head x 128/G tokens), then
-//                   per key tile the K pages and the V pages into a ring of two stages
+//                   per key tile the K pages and the V pages into rings of two stages each (a K stage is free again
+//                   once its S is computed, a V stage once its P V is)
 //   MMA warp        one thread: S_b = Q K_j^T (8 x UMMA 128x64x16) into S buffer b = j mod 2, and, one
 //                   tile behind, O += P_{j-1} V_{j-1} (4 x UMMA 128x128x16 with A = P read from tensor
 //                   memory, B = V as an MN-major operand)
@@ -135,6 +136,13 @@ __device__ __forceinline__ void tmem_store_32(uint32_t address, const uint32_t (
 }
 __device__ __forceinline__ void tmem_wait_store() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// 2^x on the special-function unit: one instruction; 2^-inf = 0, results below the normal range flush to zero.
+__device__ __forceinline__ float exp2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t pack2(float low, float high) {
     __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
     return *reinterpret_cast<uint32_t*>(&pair);
@@ -145,7 +153,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
                                                                              const __grid_constant__ CUtensorMap map_v,
                                                                              const PrefillParams p) {
     extern __shared__ __align__(16) unsigned char shared_raw[];
-    __shared__ __align__(8) uint64_t q_full, k_full[kStages], v_full[kStages], kv_free[kStages], s_ready[2], p_ready[2], o_done;
+    __shared__ __align__(8) uint64_t q_full, k_full[kStages], v_full[kStages], k_free[kStages], v_free[kStages], s_ready[2], p_ready[2], o_done, o_final;
     __shared__ uint32_t tmem_slot;
     __shared__ int failed;
     pdl_trigger();
@@ -209,13 +217,15 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
         for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&k_full[s]), 1);
             mbar_init(smem_u32(&v_full[s]), 1);
-            mbar_init(smem_u32(&kv_free[s]), 1);
+            mbar_init(smem_u32(&k_free[s]), 1);
+            mbar_init(smem_u32(&v_free[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&s_ready[b]), 1);
             mbar_init(smem_u32(&p_ready[b]), 4);      // one arrival per softmax warp
         }
         mbar_init(smem_u32(&o_done), 1);
+        mbar_init(smem_u32(&o_final), 1);
         tma::mbar_fence_init();
     }
     __syncthreads();
@@ -230,26 +240,45 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
         const int pages_per_tile = kKeys / p.page_size;
         const int copies = pages_per_tile * 2;               // two column halves per page
         const int my_page = lane >> 1, my_half = lane & 1;
-        for (int t = 0; t < n_tiles; ++t) {
-            const int s = t % kStages;
-            if (t >= kStages && !mbar_wait(smem_u32(&kv_free[s]), ((t / kStages) - 1) & 1)) {
+        // K of tile t goes out as soon as S of tile t - 2 has been computed, V of tile t once P V of tile t - 2
+        // has: the MMA warp issues S_0 S_1 PV_0 S_2 PV_1 ..., so the copies go K_0 K_1 V_0 K_2 V_1 ...
+        for (int step = 0; step <= n_tiles; ++step) {
+            bool ok = true;
+            if (step < n_tiles) {
+                const int t = step, s = t % kStages;
+                if (t >= kStages) ok = mbar_wait(smem_u32(&k_free[s]), ((t / kStages) - 1) & 1);
+                if (ok) {
+                    if (lane == 0) mbar_expect_tx(smem_u32(&k_full[s]), kKVBytes);
+                    __syncwarp();
+                    if (lane < copies) {
+                        // whole tiles always: pages past the sequence's end come from whatever the zero-padded
+                        // table names (an existing page with finite contents, masked out below)
+                        const int key = first_tile_key + t * kKeys + my_page * p.page_size;
+                        const int page = table[min(key / p.page_size, p.max_blocks - 1)];
+                        const int y = (page * p.n_kv_heads + kv_head) * p.page_size;
+                        const uint32_t offset = s * kKVBytes + my_half * (kKeys * 128u) + (uint32_t)(my_page * p.page_size) * 128u;
+                        tma::load_2d(k_smem + offset, &map_k, smem_u32(&k_full[s]), my_half * 64, y);
+                    }
+                }
+            }
+            if (ok && step > 0) {
+                const int t = step - 1, s = t % kStages;
+                if (t >= kStages) ok = mbar_wait(smem_u32(&v_free[s]), ((t / kStages) - 1) & 1);
+                if (ok) {
+                    if (lane == 0) mbar_expect_tx(smem_u32(&v_full[s]), kKVBytes);
+                    __syncwarp();
+                    if (lane < copies) {
+                        const int key = first_tile_key + t * kKeys + my_page * p.page_size;
+                        const int page = table[min(key / p.page_size, p.max_blocks - 1)];
+                        const int y = (page * p.n_kv_heads + kv_head) * p.page_size;
+                        const uint32_t offset = s * kKVBytes + my_half * (kKeys * 128u) + (uint32_t)(my_page * p.page_size) * 128u;
+                        tma::load_2d(v_smem + offset, &map_v, smem_u32(&v_full[s]), my_half * 64, y);
+                    }
+                }
+            }
+            if (!ok) {
                 failed = 1;
                 break;
-            }
-            if (lane == 0) {
-                mbar_expect_tx(smem_u32(&k_full[s]), kKVBytes);
-                mbar_expect_tx(smem_u32(&v_full[s]), kKVBytes);
-            }
-            __syncwarp();
-            if (lane < copies) {
-                // whole tiles always: pages past the sequence's end come from whatever the zero-padded table
-                // names (an existing page with finite contents, masked out below)
-                const int key = first_tile_key + t * kKeys + my_page * p.page_size;
-                const int page = table[min(key / p.page_size, p.max_blocks - 1)];
-                const int y = (page * p.n_kv_heads + kv_head) * p.page_size;
-                const uint32_t offset = s * kKVBytes + my_half * (kKeys * 128u) + (uint32_t)(my_page * p.page_size) * 128u;
-                tma::load_2d(k_smem + offset, &map_k, smem_u32(&k_full[s]), my_half * 64, y);
-                tma::load_2d(v_smem + offset, &map_v, smem_u32(&v_full[s]), my_half * 64, y);
             }
         }
     } else if (warp == 5) {
@@ -271,6 +300,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
                                desc_k_major(k_smem + s * kKVBytes + half * (kKeys * 128u) + within), idesc_s, ks > 0 ? 1u : 0u);
                     }
                     mma_commit(smem_u32(&s_ready[b]));
+                    mma_commit(smem_u32(&k_free[s]));
                 }
                 if (j > 0) {              // O += P_{j-1} V_{j-1}
                     const int t = j - 1, s = t % kStages, b = t & 1;
@@ -281,8 +311,9 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
                     for (int kk = 0; kk < kKeys / 16; ++kk)     // 16 keys = 8 packed columns of P, 2048 bytes of V rows
                         mma_ts(tmem + kColO, tmem + (b ? kColS1 : kColS0) + kk * 8,
                                desc_mn_major(v_smem + s * kKVBytes + kk * 2048u, kKeys * 128u), idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
-                    mma_commit(smem_u32(&kv_free[s]));
+                    mma_commit(smem_u32(&v_free[s]));
                     mma_commit(smem_u32(&o_done));
+                    if (t == n_tiles - 1) mma_commit(smem_u32(&o_final));
                 }
             }
             if (!ok) failed = 1;
@@ -307,21 +338,25 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
             tmem_load_32(s_address, raw_low);
             tmem_load_32(s_address + 32, raw_high);
             const int tile_key = first_tile_key + j * kKeys;
-            float tile_max = -INFINITY;
+            // only tiles that touch the diagonal, the window's edge or the end of the rows need the mask
+            if (tile_key + kKeys - 1 > position || tile_key < low) {
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                const int key_low = tile_key + c, key_high = tile_key + 32 + c;
-                float x = __uint_as_float(raw_low[c]) * p.scale_log2, y = __uint_as_float(raw_high[c]) * p.scale_log2;
-                x = (key_low >= low && key_low <= position) ? x : -INFINITY;
-                y = (key_high >= low && key_high <= position) ? y : -INFINITY;
-                raw_low[c] = __float_as_uint(x);
-                raw_high[c] = __float_as_uint(y);
-                tile_max = fmaxf(tile_max, fmaxf(x, y));
+                for (int c = 0; c < 32; ++c) {
+                    const int key_low = tile_key + c, key_high = tile_key + 32 + c;
+                    if (!(key_low >= low && key_low <= position)) raw_low[c] = 0xff800000u;      // -inf
+                    if (!(key_high >= low && key_high <= position)) raw_high[c] = 0xff800000u;
+                }
             }
+            // the maximum is taken over the raw scores (the scale is positive); the scale and the reference
+            // enter the exponent in one fused multiply-add
+            float raw_max = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) raw_max = fmaxf(raw_max, fmaxf(__uint_as_float(raw_low[c]), __uint_as_float(raw_high[c])));
+            const float tile_max = raw_max * p.scale_log2;
             // the reference moves only when the maximum has outgrown it by the threshold (or nothing was seen yet)
             float factor = 1.0f;
             if (tile_max > reference + kRescaleThreshold || (reference == -INFINITY && tile_max > -INFINITY)) {
-                factor = reference == -INFINITY ? 0.0f : exp2f(reference - tile_max);
+                factor = reference == -INFINITY ? 0.0f : exp2_approx(reference - tile_max);
                 reference = tile_max;
             }
             const float subtract = reference == -INFINITY ? 0.0f : reference;
@@ -329,8 +364,10 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
             uint32_t packed[32];
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
-                const float a0 = exp2f(__uint_as_float(raw_low[2 * c]) - subtract), a1 = exp2f(__uint_as_float(raw_low[2 * c + 1]) - subtract);
-                const float b0 = exp2f(__uint_as_float(raw_high[2 * c]) - subtract), b1 = exp2f(__uint_as_float(raw_high[2 * c + 1]) - subtract);
+                const float a0 = exp2_approx(fmaf(__uint_as_float(raw_low[2 * c]), p.scale_log2, -subtract));
+                const float a1 = exp2_approx(fmaf(__uint_as_float(raw_low[2 * c + 1]), p.scale_log2, -subtract));
+                const float b0 = exp2_approx(fmaf(__uint_as_float(raw_high[2 * c]), p.scale_log2, -subtract));
+                const float b1 = exp2_approx(fmaf(__uint_as_float(raw_high[2 * c + 1]), p.scale_log2, -subtract));
                 tile_sum += (a0 + a1) + (b0 + b1);
                 packed[c] = pack2(a0, a1);            // keys 2c, 2c + 1
                 packed[16 + c] = pack2(b0, b1);       // keys 32 + 2c, 32 + 2c + 1
@@ -355,8 +392,10 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&p_ready[b]));
         }
-        // the last P V, then O / sum
-        if (ok && !mbar_wait(smem_u32(&o_done), (n_tiles - 1) & 1)) ok = false;
+        // the last P V, then O / sum.  It has a barrier of its own: o_done may still be a phase behind here (the
+        // softmax of the last tile needs S only, not the P V before it), and a parity wait cannot tell a phase
+        // that is two behind from the one it waits for.
+        if (ok && !mbar_wait(smem_u32(&o_final), 0)) ok = false;
         fence_after();
         if (!ok) failed = 1;
         const float inverse = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
@@ -387,13 +426,15 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
         for (int s = 0; s < kStages; ++s) {
             tma::mbar_inval(smem_u32(&k_full[s]));
             tma::mbar_inval(smem_u32(&v_full[s]));
-            tma::mbar_inval(smem_u32(&kv_free[s]));
+            tma::mbar_inval(smem_u32(&k_free[s]));
+            tma::mbar_inval(smem_u32(&v_free[s]));
         }
         for (int b = 0; b < 2; ++b) {
             tma::mbar_inval(smem_u32(&s_ready[b]));
             tma::mbar_inval(smem_u32(&p_ready[b]));
         }
         tma::mbar_inval(smem_u32(&o_done));
+        tma::mbar_inval(smem_u32(&o_final));
     }
   }
     if (failed && threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 4);
@@ -417,7 +458,8 @@ LLM_EXPORT int llm_attention_prefill_tcgen05(const void* q, int q_stride, int n_
                                              int head_dim, int page_size, float scale, int window, int skip_single,
                                              int total_pairs, int* error_flag, cudaStream_t stream) {
     if (total_pairs <= 0) return LLM_OK;
-    if (!llm_attention_prefill_tcgen05_supports(head_dim, n_q_heads, n_kv_heads, page_size) || !aligned16(q) || q_stride % 8) {
+    if (!llm_attention_prefill_tcgen05_supports(head_dim, n_q_heads, n_kv_heads, page_size) || !aligned16(q) || q_stride % 8 ||
+        !(scale > 0.0f)) {
         llm_set_error("attention_prefill_tcgen05: unsupported sizes (head_dim %d, %d/%d heads, page %d)", head_dim, n_q_heads,
                       n_kv_heads, page_size);
         return LLM_REFUSED;
