@@ -124,6 +124,15 @@ __device__ __forceinline__ void tmem_load_32(uint32_t address, uint32_t (&r)[32]
         : "r"(address)
         : "memory");
 }
+__device__ __forceinline__ void tmem_load_64(uint32_t address, uint32_t (&r)[64]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(address)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_store_32(uint32_t address, const uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -334,24 +343,25 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
             if (ok && !mbar_wait(smem_u32(&s_ready[b]), (j >> 1) & 1)) ok = false;
             fence_after();
             const uint32_t s_address = lane_base + (b ? kColS1 : kColS0);
-            uint32_t raw_low[32], raw_high[32];
-            tmem_load_32(s_address, raw_low);
-            tmem_load_32(s_address + 32, raw_high);
+            uint32_t raw[64];
+            tmem_load_64(s_address, raw);
             const int tile_key = first_tile_key + j * kKeys;
             // only tiles that touch the diagonal, the window's edge or the end of the rows need the mask
             if (tile_key + kKeys - 1 > position || tile_key < low) {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    const int key_low = tile_key + c, key_high = tile_key + 32 + c;
-                    if (!(key_low >= low && key_low <= position)) raw_low[c] = 0xff800000u;      // -inf
-                    if (!(key_high >= low && key_high <= position)) raw_high[c] = 0xff800000u;
-                }
+                for (int c = 0; c < 64; ++c)
+                    if (!(tile_key + c >= low && tile_key + c <= position)) raw[c] = 0xff800000u;      // -inf
             }
-            // the maximum is taken over the raw scores (the scale is positive); the scale and the reference
-            // enter the exponent in one fused multiply-add
-            float raw_max = -INFINITY;
+            // The maximum is taken over the raw scores (the scale is positive); the scale and the reference enter
+            // the exponent in one fused multiply-add.  Eight running maxima and four running sums keep the
+            // dependent chains short: with two softmax warps per scheduler, latency is what this loop is bound by.
+            float running[8];
 #pragma unroll
-            for (int c = 0; c < 32; ++c) raw_max = fmaxf(raw_max, fmaxf(__uint_as_float(raw_low[c]), __uint_as_float(raw_high[c])));
+            for (int c = 0; c < 8; ++c) running[c] = __uint_as_float(raw[c]);
+#pragma unroll
+            for (int c = 8; c < 64; ++c) running[c & 7] = fmaxf(running[c & 7], __uint_as_float(raw[c]));
+            const float raw_max = fmaxf(fmaxf(fmaxf(running[0], running[1]), fmaxf(running[2], running[3])),
+                                        fmaxf(fmaxf(running[4], running[5]), fmaxf(running[6], running[7])));
             const float tile_max = raw_max * p.scale_log2;
             // the reference moves only when the maximum has outgrown it by the threshold (or nothing was seen yet)
             float factor = 1.0f;
@@ -360,18 +370,18 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
                 reference = tile_max;
             }
             const float subtract = reference == -INFINITY ? 0.0f : reference;
-            float tile_sum = 0.0f;
+            float weight[64];
+#pragma unroll
+            for (int c = 0; c < 64; ++c) weight[c] = fmaf(__uint_as_float(raw[c]), p.scale_log2, -subtract);
+#pragma unroll
+            for (int c = 0; c < 64; ++c) weight[c] = exp2_approx(weight[c]);
+            float partial[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int c = 0; c < 64; ++c) partial[c & 3] += weight[c];
+            const float tile_sum = (partial[0] + partial[1]) + (partial[2] + partial[3]);
             uint32_t packed[32];
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                const float a0 = exp2_approx(fmaf(__uint_as_float(raw_low[2 * c]), p.scale_log2, -subtract));
-                const float a1 = exp2_approx(fmaf(__uint_as_float(raw_low[2 * c + 1]), p.scale_log2, -subtract));
-                const float b0 = exp2_approx(fmaf(__uint_as_float(raw_high[2 * c]), p.scale_log2, -subtract));
-                const float b1 = exp2_approx(fmaf(__uint_as_float(raw_high[2 * c + 1]), p.scale_log2, -subtract));
-                tile_sum += (a0 + a1) + (b0 + b1);
-                packed[c] = pack2(a0, a1);            // keys 2c, 2c + 1
-                packed[16 + c] = pack2(b0, b1);       // keys 32 + 2c, 32 + 2c + 1
-            }
+            for (int c = 0; c < 32; ++c) packed[c] = pack2(weight[2 * c], weight[2 * c + 1]);      // keys 2c, 2c + 1
             row_sum = row_sum * factor + tile_sum;
             // O is rescaled (by the whole warp, rows that need nothing use 1) once the previous P V is done
             if (j > 0 && __any_sync(0xffffffffu, factor != 1.0f)) {
