@@ -7,7 +7,7 @@
 // of 64 (whole cache pages), from the first key in the tile's window to the last token's position:
 //
 //   producer warp   TMA: the Q tile once (a 4-D box: 64 columns x G heads x 1 kv head x 128/G tokens), then
-//                   per key tile the K pages and the V pages into rings of two stages each (a K stage is free again
+//                   per key tile the K pages and the V pages (one 5-D box per page) into rings of three and two stages (a K stage is free again
 //                   once its S is computed, a V stage once its P V is)
 //   MMA warp        one thread: S_b = Q K_j^T (8 x UMMA 128x64x16) into S buffer b = j mod 2, and, one
 //                   tile behind, O += P_{j-1} V_{j-1} (4 x UMMA 128x128x16 with A = P read from tensor
@@ -19,7 +19,7 @@
 //                   final division by the sum undoes it); at the end O / sum is stored as bfloat16
 //
 // Formulas as in attention_mma.cu (utils/attention.py:186-198, utils/attention.py:75-96).  Tensor memory:
-// S0 | S1 | O = 64 + 64 + 128 columns; two CTAs fit on an SM (512 columns, 2 x 97 KiB shared memory), so one
+// S0 | S1 | O = 64 + 64 + 128 columns; two CTAs fit on an SM (512 columns, 2 x 114 KiB shared memory), so one
 // CTA's softmax overlaps the other's MMAs as well as its own next S tile.
 // Every mbarrier wait is bounded; a wait that runs out sets the error flag, and the CTA still releases its
 // tensor memory.  Takes head_dim 128, groups of 1, 2, 4, 8 or 16 heads, pages of 8, 16, 32 or 64 tokens;
@@ -32,7 +32,8 @@ namespace {
 constexpr int kRows = 128;        // rows per CTA (UMMA M)
 constexpr int kKeys = 64;         // keys per tile (UMMA N of S, K of P V)
 constexpr int kDim = 128;         // head_dim
-constexpr int kStages = 2;        // K/V ring
+constexpr int kKStages = 3;       // K ring: a copy needs more than one tile's time to arrive, so two tiles are in flight
+constexpr int kVStages = 2;       // V ring
 constexpr int kThreads = 192;     // 4 softmax warps + producer warp + MMA warp
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
@@ -40,6 +41,18 @@ constexpr float kRescaleThreshold = 8.0f;   // log2 units
 constexpr uint32_t kQBytes = kRows * kDim * 2;        // 32 KiB
 constexpr uint32_t kKVBytes = kKeys * kDim * 2;       // 16 KiB per K or V tile
 constexpr uint32_t kColS0 = 0, kColS1 = 64, kColO = 128, kTmemCols = 256;
+
+constexpr uint32_t kTileBytes = kQBytes + (kKStages + kVStages) * kKVBytes;   // 112 KiB
+constexpr uint32_t kControlBytes = 256;
+constexpr uint32_t kSharedBytes = 113 * 1024;
+
+struct Control {      // barriers and flags, at the end of the dynamic shared memory
+    uint64_t q_full, k_full[kKStages], v_full[kVStages], k_free[kKStages], v_free[kVStages], s_ready[2], p_ready[2], o_done, o_final;
+    uint32_t tmem_slot;
+    int failed;
+};
+static_assert(sizeof(Control) <= kControlBytes, "control block");
+static_assert(kTileBytes + kControlBytes <= kSharedBytes, "shared memory layout");
 
 struct PrefillParams {
     const int* block_tables;
@@ -67,23 +80,30 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
-// K-major operand with 128-byte swizzle (rows of 128 bytes, 8-row groups 1024 bytes apart).
-__device__ __forceinline__ uint64_t desc_k_major(uint32_t address) {
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+
+// K-major operand with 128-byte swizzle (rows of 128 bytes, 8-row groups `group_stride` bytes apart).
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t address, uint32_t group_stride) {
     uint64_t d = 0;
     d |= (uint64_t)((address & 0x3FFFF) >> 4);
     d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)(group_stride >> 4) << 32;
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)2 << 61;
     return d;
 }
 // MN-major operand with 128-byte swizzle: 64 MN-elements (128 bytes) contiguous, 8 K-rows per 1024-byte
-// atom; atoms along MN `leading` bytes apart, atoms along K 1024 bytes apart.
-__device__ __forceinline__ uint64_t desc_mn_major(uint32_t address, uint32_t leading) {
+// atom; atoms along MN `leading` bytes apart, atoms along K `group_stride` bytes apart.
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t address, uint32_t leading, uint32_t group_stride) {
     uint64_t d = 0;
     d |= (uint64_t)((address & 0x3FFFF) >> 4);
     d |= (uint64_t)((leading >> 4) & 0x3FFF) << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)(group_stride >> 4) << 32;
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)2 << 61;
     return d;
@@ -161,16 +181,31 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
                                                                              const __grid_constant__ CUtensorMap map_k,
                                                                              const __grid_constant__ CUtensorMap map_v,
                                                                              const PrefillParams p) {
+    // All shared memory is dynamic: tiles (1024-byte aligned for the 128-byte swizzle) and, in the last 256 bytes,
+    // the barriers.  113 KiB + 1 KiB the system reserves per CTA = 114 KiB, and two CTAs fill the SM's 228 KiB exactly.
     extern __shared__ __align__(16) unsigned char shared_raw[];
-    __shared__ __align__(8) uint64_t q_full, k_full[kStages], v_full[kStages], k_free[kStages], v_free[kStages], s_ready[2], p_ready[2], o_done, o_final;
-    __shared__ uint32_t tmem_slot;
-    __shared__ int failed;
     pdl_trigger();
     pdl_wait();
 
     const uint32_t raw = smem_u32(shared_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
-    const uint32_t q_smem = base, k_smem = base + kQBytes, v_smem = k_smem + kStages * kKVBytes;
+    if (base - raw > kSharedBytes - kTileBytes - kControlBytes) {      // the tiles would not fit behind the padding
+        if (threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 5);
+        return;
+    }
+    const uint32_t q_smem = base, k_smem = base + kQBytes, v_smem = k_smem + kKStages * kKVBytes;
+    Control& control = *reinterpret_cast<Control*>(shared_raw + (kSharedBytes - kControlBytes));
+    uint64_t& q_full = control.q_full;
+    uint64_t (&k_full)[kKStages] = control.k_full;
+    uint64_t (&v_full)[kVStages] = control.v_full;
+    uint64_t (&k_free)[kKStages] = control.k_free;
+    uint64_t (&v_free)[kVStages] = control.v_free;
+    uint64_t (&s_ready)[2] = control.s_ready;
+    uint64_t (&p_ready)[2] = control.p_ready;
+    uint64_t& o_done = control.o_done;
+    uint64_t& o_final = control.o_final;
+    uint32_t& tmem_slot = control.tmem_slot;
+    int& failed = control.failed;
 
     const int group = p.n_q_heads / p.n_kv_heads;
     const int tokens_per_tile = kRows / group;
@@ -223,10 +258,12 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
     // fresh barriers for every pass: at the end of a pass every copy has landed and every MMA has retired
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&q_full), 1);
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < kKStages; ++s) {
             mbar_init(smem_u32(&k_full[s]), 1);
-            mbar_init(smem_u32(&v_full[s]), 1);
             mbar_init(smem_u32(&k_free[s]), 1);
+        }
+        for (int s = 0; s < kVStages; ++s) {
+            mbar_init(smem_u32(&v_full[s]), 1);
             mbar_init(smem_u32(&v_free[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -246,16 +283,16 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
             tma_load_4d(q_smem, &map_q, smem_u32(&q_full), 0, 0, kv_head, token0 + tile * tokens_per_tile);
             tma_load_4d(q_smem + kRows * 128u, &map_q, smem_u32(&q_full), 64, 0, kv_head, token0 + tile * tokens_per_tile);
         }
-        const int pages_per_tile = kKeys / p.page_size;
-        const int copies = pages_per_tile * 2;               // two column halves per page
-        const int my_page = lane >> 1, my_half = lane & 1;
-        // K of tile t goes out as soon as S of tile t - 2 has been computed, V of tile t once P V of tile t - 2
-        // has: the MMA warp issues S_0 S_1 PV_0 S_2 PV_1 ..., so the copies go K_0 K_1 V_0 K_2 V_1 ...
-        for (int step = 0; step <= n_tiles; ++step) {
+        // one copy per page: 8-key groups of [low 64 columns | high 64 columns], 1024 bytes each (a 5-D box)
+        const int copies = kKeys / p.page_size;
+        const int my_page = lane;
+        // K of tile t goes out as soon as S of tile t - 3 has been computed, V of tile t once P V of tile t - 2
+        // has: the MMA warp issues S_0 S_1 PV_0 S_2 PV_1 S_3 PV_2 ..., so the copies go K_0 K_1 K_2 V_0 K_3 V_1 ...
+        for (int step = 0; step < n_tiles + 2; ++step) {
             bool ok = true;
             if (step < n_tiles) {
-                const int t = step, s = t % kStages;
-                if (t >= kStages) ok = mbar_wait(smem_u32(&k_free[s]), ((t / kStages) - 1) & 1);
+                const int t = step, s = t % kKStages;
+                if (t >= kKStages) ok = mbar_wait(smem_u32(&k_free[s]), ((t / kKStages) - 1) & 1);
                 if (ok) {
                     if (lane == 0) mbar_expect_tx(smem_u32(&k_full[s]), kKVBytes);
                     __syncwarp();
@@ -264,24 +301,22 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
                         // table names (an existing page with finite contents, masked out below)
                         const int key = first_tile_key + t * kKeys + my_page * p.page_size;
                         const int page = table[min(key / p.page_size, p.max_blocks - 1)];
-                        const int y = (page * p.n_kv_heads + kv_head) * p.page_size;
-                        const uint32_t offset = s * kKVBytes + my_half * (kKeys * 128u) + (uint32_t)(my_page * p.page_size) * 128u;
-                        tma::load_2d(k_smem + offset, &map_k, smem_u32(&k_full[s]), my_half * 64, y);
+                        const uint32_t offset = s * kKVBytes + (uint32_t)(my_page * p.page_size) * 256u;
+                        tma_load_5d(k_smem + offset, &map_k, smem_u32(&k_full[s]), 0, 0, 0, 0, page * p.n_kv_heads + kv_head);
                     }
                 }
             }
-            if (ok && step > 0) {
-                const int t = step - 1, s = t % kStages;
-                if (t >= kStages) ok = mbar_wait(smem_u32(&v_free[s]), ((t / kStages) - 1) & 1);
+            if (ok && step >= 2) {
+                const int t = step - 2, s = t % kVStages;
+                if (t >= kVStages) ok = mbar_wait(smem_u32(&v_free[s]), ((t / kVStages) - 1) & 1);
                 if (ok) {
                     if (lane == 0) mbar_expect_tx(smem_u32(&v_full[s]), kKVBytes);
                     __syncwarp();
                     if (lane < copies) {
                         const int key = first_tile_key + t * kKeys + my_page * p.page_size;
                         const int page = table[min(key / p.page_size, p.max_blocks - 1)];
-                        const int y = (page * p.n_kv_heads + kv_head) * p.page_size;
-                        const uint32_t offset = s * kKVBytes + my_half * (kKeys * 128u) + (uint32_t)(my_page * p.page_size) * 128u;
-                        tma::load_2d(v_smem + offset, &map_v, smem_u32(&v_full[s]), my_half * 64, y);
+                        const uint32_t offset = s * kKVBytes + (uint32_t)(my_page * p.page_size) * 256u;
+                        tma_load_5d(v_smem + offset, &map_v, smem_u32(&v_full[s]), 0, 0, 0, 0, page * p.n_kv_heads + kv_head);
                     }
                 }
             }
@@ -298,28 +333,28 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
             bool ok = mbar_wait(smem_u32(&q_full), 0);
             for (int j = 0; j <= n_tiles && ok; ++j) {
                 if (j < n_tiles) {        // S_b = Q K_j^T
-                    const int s = j % kStages, b = j & 1;
-                    ok = mbar_wait(smem_u32(&k_full[s]), (j / kStages) & 1);
+                    const int s = j % kKStages, b = j & 1;
+                    ok = mbar_wait(smem_u32(&k_full[s]), (j / kKStages) & 1);
                     if (!ok) break;
                     fence_after();
 #pragma unroll
                     for (int ks = 0; ks < kDim / 16; ++ks) {
                         const uint32_t half = ks >> 2, within = (ks & 3) * 32;
-                        mma_ss(tmem + (b ? kColS1 : kColS0), desc_k_major(q_smem + half * (kRows * 128u) + within),
-                               desc_k_major(k_smem + s * kKVBytes + half * (kKeys * 128u) + within), idesc_s, ks > 0 ? 1u : 0u);
+                        mma_ss(tmem + (b ? kColS1 : kColS0), desc_k_major(q_smem + half * (kRows * 128u) + within, 1024u),
+                               desc_k_major(k_smem + s * kKVBytes + half * 1024u + within, 2048u), idesc_s, ks > 0 ? 1u : 0u);
                     }
                     mma_commit(smem_u32(&s_ready[b]));
                     mma_commit(smem_u32(&k_free[s]));
                 }
                 if (j > 0) {              // O += P_{j-1} V_{j-1}
-                    const int t = j - 1, s = t % kStages, b = t & 1;
-                    ok = mbar_wait(smem_u32(&p_ready[b]), (t >> 1) & 1) && mbar_wait(smem_u32(&v_full[s]), (t / kStages) & 1);
+                    const int t = j - 1, s = t % kVStages, b = t & 1;
+                    ok = mbar_wait(smem_u32(&p_ready[b]), (t >> 1) & 1) && mbar_wait(smem_u32(&v_full[s]), (t / kVStages) & 1);
                     if (!ok) break;
                     fence_after();
 #pragma unroll
-                    for (int kk = 0; kk < kKeys / 16; ++kk)     // 16 keys = 8 packed columns of P, 2048 bytes of V rows
+                    for (int kk = 0; kk < kKeys / 16; ++kk)     // 16 keys = 8 packed columns of P, two 8-key groups of V
                         mma_ts(tmem + kColO, tmem + (b ? kColS1 : kColS0) + kk * 8,
-                               desc_mn_major(v_smem + s * kKVBytes + kk * 2048u, kKeys * 128u), idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+                               desc_mn_major(v_smem + s * kKVBytes + kk * 4096u, 1024u, 2048u), idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
                     mma_commit(smem_u32(&v_free[s]));
                     mma_commit(smem_u32(&o_done));
                     if (t == n_tiles - 1) mma_commit(smem_u32(&o_final));
@@ -433,10 +468,12 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
     fence_after();
     if (pass + 1 < passes && threadIdx.x == 0) {
         tma::mbar_inval(smem_u32(&q_full));
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < kKStages; ++s) {
             tma::mbar_inval(smem_u32(&k_full[s]));
-            tma::mbar_inval(smem_u32(&v_full[s]));
             tma::mbar_inval(smem_u32(&k_free[s]));
+        }
+        for (int s = 0; s < kVStages; ++s) {
+            tma::mbar_inval(smem_u32(&v_full[s]));
             tma::mbar_inval(smem_u32(&v_free[s]));
         }
         for (int b = 0; b < 2; ++b) {
@@ -498,10 +535,20 @@ LLM_EXPORT int llm_attention_prefill_tcgen05(const void* q, int q_stride, int n_
             return LLM_REFUSED;
         }
     }
-    if (!tma::make_map_bf16(&map_k, k_pages, (uint64_t)1 << 30, head_dim, (uint32_t)page_size) ||
-        !tma::make_map_bf16(&map_v, v_pages, (uint64_t)1 << 30, head_dim, (uint32_t)page_size)) {
-        llm_set_error("attention_prefill_tcgen05: cannot describe the pages to TMA");
-        return LLM_REFUSED;
+    // A page of one kv head, [page_size keys][128 columns], as (64 columns, 8 keys, 2 column halves, page_size / 8 key
+    // groups, page x kv head): one box brings the whole page as 8-key groups of [low half | high half], each half a
+    // 1024-byte swizzle atom, which is the operand layout both MMAs read.
+    for (int which = 0; which < 2; ++which) {
+        const cuuint64_t dims[5] = {64u, 8u, 2u, (cuuint64_t)(page_size / 8), (cuuint64_t)1 << 30};
+        const cuuint64_t strides[4] = {(cuuint64_t)kDim * 2, 128u, (cuuint64_t)8 * kDim * 2, (cuuint64_t)page_size * kDim * 2};
+        const cuuint32_t box[5] = {64u, 8u, 2u, (cuuint32_t)(page_size / 8), 1u};
+        const cuuint32_t ones[5] = {1, 1, 1, 1, 1};
+        if (encode(which ? &map_v : &map_k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(which ? v_pages : k_pages), dims,
+                   strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+            llm_set_error("attention_prefill_tcgen05: cannot describe the pages to TMA");
+            return LLM_REFUSED;
+        }
     }
     PrefillParams p;
     p.block_tables = block_tables;
@@ -517,7 +564,7 @@ LLM_EXPORT int llm_attention_prefill_tcgen05(const void* q, int q_stride, int n_
     p.window = window;
     p.skip_single = skip_single;
     p.error_flag = error_flag;
-    const size_t shared = (size_t)kQBytes + 2 * kStages * kKVBytes + 1024;
+    const size_t shared = kSharedBytes;
     static bool configured = false;
     if (!configured) {
         cudaError_t status = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
@@ -525,6 +572,7 @@ LLM_EXPORT int llm_attention_prefill_tcgen05(const void* q, int q_stride, int n_
             llm_set_error("attention_prefill_tcgen05: cannot get %zu bytes of shared memory: %s", shared, cudaGetErrorString(status));
             return (int)status;
         }
+        cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         configured = true;
     }
     dim3 grid(total_pairs, n_kv_heads);
