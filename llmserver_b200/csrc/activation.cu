@@ -4,6 +4,14 @@
 // (utils/fused_ops.py:80-88).  16-byte accesses when the intermediate size allows, else element-wise.
 #include "common.cuh"
 
+// silu(x) * y in 32-bit.  For 16-bit activations the exponential and the reciprocal are the hardware
+// approximations (a few units in the last place of a 32-bit float, far below the rounding of the result).
+template <typename T>
+__device__ __forceinline__ float silu_times(float gate, float up) {
+    if (sizeof(T) == 2) return __fdividef(gate, 1.0f + __expf(-gate)) * up;
+    return gate / (1.0f + expf(-gate)) * up;
+}
+
 template <typename T>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int intermediate,
                                     size_t total_vectors) {
@@ -11,16 +19,29 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict
     pdl_wait();      // everything before this kernel in the stream is complete and visible
     constexpr int kCount = Vec16<T>::kCount;
     const int vectors_per_row = intermediate / kCount;
-    for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < total_vectors; v += (size_t)gridDim.x * blockDim.x) {
-        const size_t row = v / vectors_per_row;
-        const int column = (int)(v % vectors_per_row) * kCount;
-        const T* src = gate_up + row * 2 * (size_t)intermediate + column;
-        float gate[kCount], up[kCount], result[kCount];
-        Vec16<T>::load(src, gate);
-        Vec16<T>::load(src + intermediate, up);
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    // two vectors per thread and turn: four 16-byte loads are in flight before the first result is needed
+    for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < total_vectors; v += 2 * stride) {
+        const size_t w = v + stride;
+        const bool second = w < total_vectors;
+        const size_t row_v = v / vectors_per_row, row_w = second ? w / vectors_per_row : row_v;
+        const int column_v = (int)(v - row_v * vectors_per_row) * kCount;
+        const int column_w = second ? (int)(w - row_w * vectors_per_row) * kCount : column_v;
+        const T* src_v = gate_up + row_v * 2 * (size_t)intermediate + column_v;
+        const T* src_w = gate_up + row_w * 2 * (size_t)intermediate + column_w;
+        float gate_v[kCount], up_v[kCount], gate_w[kCount], up_w[kCount], result[kCount];
+        Vec16<T>::load(src_v, gate_v);
+        Vec16<T>::load(src_v + intermediate, up_v);
+        Vec16<T>::load(src_w, gate_w);
+        Vec16<T>::load(src_w + intermediate, up_w);
 #pragma unroll
-        for (int i = 0; i < kCount; ++i) result[i] = gate[i] / (1.0f + expf(-gate[i])) * up[i];
-        Vec16<T>::store(out + row * (size_t)intermediate + column, result);
+        for (int i = 0; i < kCount; ++i) result[i] = silu_times<T>(gate_v[i], up_v[i]);
+        Vec16<T>::store(out + row_v * (size_t)intermediate + column_v, result);
+        if (second) {
+#pragma unroll
+            for (int i = 0; i < kCount; ++i) result[i] = silu_times<T>(gate_w[i], up_w[i]);
+            Vec16<T>::store(out + row_w * (size_t)intermediate + column_w, result);
+        }
     }
 }
 
@@ -46,6 +67,7 @@ LLM_EXPORT int llm_silu_mul(const void* gate_up, void* out, int n_rows, int inte
     const bool vector_form = intermediate % per_vector == 0 && aligned16(gate_up) && aligned16(out);
     const size_t work = vector_form ? (size_t)n_rows * (intermediate / per_vector) : (size_t)n_rows * intermediate;
     size_t blocks = (work + threads - 1) / threads;
+    if (vector_form) blocks = (blocks + 1) / 2;      // two vectors per thread and turn
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (vector_form) {
         LLM_DISPATCH_DTYPE(dtype, (llm_launch(silu_mul_vec_kernel<T>, (unsigned)blocks, threads, 0, stream, 
