@@ -15,13 +15,29 @@ MIN_SPLIT = 192    # fewest keys one decode block walks
 WAVE_BLOCKS = 296   # one wave of two blocks per SM on 148 SMs
 
 
-PREFILL_KERNEL = os.environ.get("LLMSERVER_B200_PREFILL_ATTENTION", "tcgen05")   # or "mma"
+# "tcgen05": the 256-row kernel for long portions and the 128-row kernel otherwise; "tcgen05-128" / "tcgen05-256":
+# always that kernel; "mma": the mma.sync kernel
+PREFILL_KERNEL = os.environ.get("LLMSERVER_B200_PREFILL_ATTENTION", "tcgen05")
 PREFILL_TILE = 128   # rows per block of the tcgen05 portions kernel
+WIDE_TILE = 256      # rows per block of the 256-row kernel
+WIDE_MIN_ROWS = int(os.environ.get("LLMSERVER_B200_PREFILL_WIDE_ROWS", "4096"))   # longest portion (rows) from which it is used
 
 
 def prefill_tcgen05_supported(head_dim: int, n_q_heads: int, n_kv_heads: int, page_size: int) -> bool:
-    return PREFILL_KERNEL == "tcgen05" and bool(
+    return PREFILL_KERNEL.startswith("tcgen05") and bool(
         library().llm_attention_prefill_tcgen05_supports(head_dim, n_q_heads, n_kv_heads, page_size))
+
+
+def prefill_wide_wanted(batch, group: int, head_dim: int, n_q_heads: int, n_kv_heads: int, page_size: int) -> bool:
+    """Whether the prompt portions of this batch go to the 256-row kernel: when the longest of them has enough
+    rows that 256-row tiles fill the GPU, or when asked for."""
+    if PREFILL_KERNEL == "tcgen05-128":
+        return False
+    if not library().llm_attention_prefill_wide_supports(head_dim, n_q_heads, n_kv_heads, page_size):
+        return False
+    if PREFILL_KERNEL == "tcgen05-256":
+        return True
+    return max(batch.q_lens) * group >= WIDE_MIN_ROWS
 
 
 def supported(head_dim: int, n_q_heads: int, n_kv_heads: int) -> bool:
@@ -80,9 +96,11 @@ def try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_head
     if run_portions and prefill_tcgen05_supported(head_dim, n_q_heads, n_kv_heads, page_size):
         # prompt portions on the tcgen05 kernel (128-row tiles); single tokens, if any, on the decode kernel
         group = n_q_heads // n_kv_heads
-        # a block takes a 128-row tile and its mirror image (the light one with the heavy one)
-        big_tiles = sum((-(-length * group // PREFILL_TILE) + 1) // 2 for length in batch.q_lens if length > 1 or not run_decode)
-        call("llm_attention_prefill_tcgen05", qkv.data_ptr(), q_stride, batch.n_tokens, k_pages.data_ptr(), v_pages.data_ptr(),
+        wide = prefill_wide_wanted(batch, group, head_dim, n_q_heads, n_kv_heads, page_size)
+        rows_per_tile = WIDE_TILE if wide else PREFILL_TILE
+        # a block takes a row tile and its mirror image (the light one with the heavy one)
+        big_tiles = sum((-(-length * group // rows_per_tile) + 1) // 2 for length in batch.q_lens if length > 1 or not run_decode)
+        call("llm_attention_prefill_wide" if wide else "llm_attention_prefill_tcgen05", qkv.data_ptr(), q_stride, batch.n_tokens, k_pages.data_ptr(), v_pages.data_ptr(),
              block_tables.data_ptr(), block_tables.shape[-1], batch.q_start.data_ptr(), batch.context_len.data_ptr(),
              out.data_ptr(), batch.n_seqs, n_q_heads, n_kv_heads, head_dim, page_size, float(scale), int(window),
              int(run_decode), big_tiles, flag, stream_handle())

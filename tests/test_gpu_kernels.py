@@ -417,9 +417,9 @@ def test_tensor_core_attention_finds_a_far_key_and_respects_the_window_edge():
 @pytest.mark.parametrize("heads,kv_heads,page_size,window", [(32, 8, 16, None), (4, 4, 8, None), (16, 1, 32, 100),
                                                              (8, 4, 64, None), (8, 1, 16, 300), (2, 1, 16, None)])
 def test_attention_prefill_tcgen05(heads, kv_heads, page_size, window):
-    """The tcgen05 / tensor-memory kernel for prompt portions (head_dim 128, groups of 1 to 16 heads, whole
-    pages per tile): portions that start in the middle of a page and of a tile, more than one row tile,
-    a whole prompt, a portion of two tokens, beside single tokens that go to the decode kernel."""
+    """The two tcgen05 / tensor-memory kernels for prompt portions (128 and 256 rows per block; head_dim 128, groups
+    of 1 to 16 heads, whole pages per tile): portions that start in the middle of a page and of a tile, more than
+    one row tile, a whole prompt, a portion of two tokens, beside single tokens that go to the decode kernel."""
     from llmserver_b200.ops import attention_bf16
     dim, dtype = 128, torch.bfloat16
     assert attention_bf16.prefill_tcgen05_supported(dim, heads, kv_heads, page_size)
@@ -435,7 +435,7 @@ def test_attention_prefill_tcgen05(heads, kv_heads, page_size, window):
     want = torch.cat([plain_attention_rows(q.double(), k.double(), v.double(), scale, window, c - n)
                       for q, k, v, c, n in zip(queries, dense_k, dense_v, contexts, q_lens)])
     results = {}
-    for kernel in ("tcgen05", "mma"):
+    for kernel in ("tcgen05-128", "tcgen05-256", "mma"):
         attention_bf16.PREFILL_KERNEL = kernel
         try:
             out = attention_bf16.try_attention(packed.to(DEVICE), q_stride, FakeBatch(contexts, q_lens), tables, k_pages, v_pages,
@@ -447,4 +447,5 @@ def test_attention_prefill_tcgen05(heads, kv_heads, page_size, window):
         gemm_bf16.check_errors()
         close(out, want, dtype, f"prompt attention ({kernel})")
         results[kernel] = out
-    close(results["tcgen05"], results["mma"].double().cpu(), dtype, "the two prompt kernels against each other")
+    close(results["tcgen05-128"], results["mma"].double().cpu(), dtype, "the 128-row kernel against the mma.sync kernel")
+    close(results["tcgen05-256"], results["mma"].double().cpu(), dtype, "the 256-row kernel against the mma.sync kernel")
