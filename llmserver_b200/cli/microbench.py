@@ -5,7 +5,7 @@ workloads are what ``ncu`` is pointed at for the summaries under ``profiles/``.
 
     python -m llmserver_b200.cli.microbench gemm --rows 8 --out-features 4096 --in-features 4096
     python -m llmserver_b200.cli.microbench attention-decode --batch 64 --context 3072
-    python -m llmserver_b200.cli.microbench attention-prefill --tokens 2048
+    python -m llmserver_b200.cli.microbench attention-prefill --tokens 2048 [--context 32768]
     python -m llmserver_b200.cli.microbench decode-step --batch 8 --layers 4 [--eager]
     python -m llmserver_b200.cli.microbench prefill-step --tokens 2048 --layers 4
 
@@ -120,7 +120,7 @@ def bench_attention(args, prefill: bool) -> dict:
         return {"workload": "attention-prefill" if prefill else "attention-decode", "heads": heads, "kv_heads": kv_heads, "head_dim": dim,
                 "unsupported": "the tensor-core kernels do not take these sizes; the engine runs the generic kernel for them"}
     if prefill:
-        contexts, q_lens = [args.tokens], [args.tokens]
+        contexts, q_lens = [max(args.context or 0, args.tokens)], [args.tokens]
     else:
         contexts, q_lens = [args.context] * args.batch, [1] * args.batch
     batch = _Batch(contexts, q_lens)
@@ -152,8 +152,9 @@ def bench_attention(args, prefill: bool) -> dict:
         return result
     micro = _graph_time(run, layers)
     if prefill:
-        flops = 4.0 * heads * dim * args.tokens * (args.tokens + 1) / 2
-        result.update(tokens=args.tokens, us=round(micro, 1), causal_TFLOPs=round(flops / micro / 1e6, 1))
+        before = contexts[0] - args.tokens          # keys every row of the portion sees, plus the causal triangle
+        flops = 4.0 * heads * dim * (args.tokens * before + args.tokens * (args.tokens + 1) / 2)
+        result.update(tokens=args.tokens, context=contexts[0], us=round(micro, 1), causal_TFLOPs=round(flops / micro / 1e6, 1))
     else:
         result.update(batch=args.batch, context=args.context, us=round(micro, 1), kv_MB=round(kv_bytes / 1e6, 1),
                       TBps=round(kv_bytes / micro / 1e6, 3))
@@ -220,6 +221,7 @@ def main(argv=None) -> int:
     prefill = sub.add_parser("attention-prefill")
     common(prefill)
     prefill.add_argument("--tokens", type=int, default=2048)
+    prefill.add_argument("--context", type=int, default=0, help="tokens the request holds after the portion (default: the portion is the whole prompt)")
     step = sub.add_parser("decode-step")
     common(step)
     step.add_argument("--batch", type=int, default=8)

@@ -65,6 +65,7 @@ struct PrefillParams {
     float scale_log2;
     int window;
     int skip_single;
+    int pairing;
     int* error_flag;
 };
 
@@ -115,10 +116,10 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
     for (; seq < p.n_seqs; ++seq) {
         const int q_len = p.q_start[seq + 1] - p.q_start[seq];
         const int tiles = (q_len == 1 && p.skip_single) ? 0 : (q_len * group + kRows - 1) / kRows;
-        const int pairs = (tiles + 1) / 2;
+        const int pairs = p.pairing ? (tiles + 1) / 2 : tiles;
         if (pair < pairs) {
-            first_tile = tiles - 1 - pair;
-            second_tile = pair;
+            first_tile = tiles - 1 - pair;      // heavy tiles first
+            second_tile = p.pairing ? pair : first_tile;
             break;
         }
         pair -= pairs;
@@ -396,12 +397,12 @@ LLM_EXPORT int llm_attention_prefill_tcgen05_supports(int head_dim, int n_q_head
     return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64;
 }
 
-// total_pairs: sum over the sequences it handles of ceil(ceil(q_len * group / 128) / 2): each CTA takes a row
-// tile and its mirror; sequences of one token are skipped when skip_single is set (the decode kernel takes them).
+// total_pairs: the number of CTAs: with pairing, the sum over the sequences it handles of ceil(ceil(q_len * group / 128) / 2)
+// (each CTA takes a row tile and its mirror, which evens out the work of a causal prompt); without, one CTA per tile; sequences of one token are skipped when skip_single is set (the decode kernel takes them).
 LLM_EXPORT int llm_attention_prefill_tcgen05(const void* q, int q_stride, int n_tokens, const void* k_pages, const void* v_pages,
                                              const int* block_tables, int max_blocks, const int* q_start,
                                              const int* context_len, void* out, int n_seqs, int n_q_heads, int n_kv_heads,
-                                             int head_dim, int page_size, float scale, int window, int skip_single,
+                                             int head_dim, int page_size, float scale, int window, int skip_single, int pairing,
                                              int total_pairs, int* error_flag, cudaStream_t stream) {
     if (total_pairs <= 0) return LLM_OK;
     if (!llm_attention_prefill_tcgen05_supports(head_dim, n_q_heads, n_kv_heads, page_size) || !aligned16(q) || q_stride % 8 ||
@@ -462,6 +463,7 @@ LLM_EXPORT int llm_attention_prefill_tcgen05(const void* q, int q_stride, int n_
     p.scale_log2 = scale * kLog2e;
     p.window = window;
     p.skip_single = skip_single;
+    p.pairing = pairing;
     p.error_flag = error_flag;
     const size_t shared = kSharedBytes;
     static bool configured = false;

@@ -70,6 +70,7 @@ struct WideParams {
     float scale_log2;
     int window;
     int skip_single;
+    int pairing;
     int* error_flag;
 };
 
@@ -96,10 +97,10 @@ __global__ void __launch_bounds__(kThreads, 1) attention_prefill_wide_kernel(con
     for (; seq < p.n_seqs; ++seq) {
         const int q_len = p.q_start[seq + 1] - p.q_start[seq];
         const int tiles = (q_len == 1 && p.skip_single) ? 0 : (q_len * group + kRows - 1) / kRows;
-        const int pairs = (tiles + 1) / 2;
+        const int pairs = p.pairing ? (tiles + 1) / 2 : tiles;
         if (pair < pairs) {
-            first_tile = tiles - 1 - pair;
-            second_tile = pair;
+            first_tile = tiles - 1 - pair;      // heavy tiles first
+            second_tile = p.pairing ? pair : first_tile;
             break;
         }
         pair -= pairs;
@@ -294,79 +295,67 @@ __global__ void __launch_bounds__(kThreads, 1) attention_prefill_wide_kernel(con
             const int tile_key = first_tile_key + j * kKeys;
             // only tiles that touch the diagonal, the window's edge or the end of the rows need the mask
             const bool edge = tile_key + kKeys - 1 > position || tile_key < low;
-            float running[8];
-            uint32_t upper[64];
-            {
-                uint32_t lower[64];
-                tmem_load_64(s_address, lower);
+            // The exponentials are taken against the reference as it stands, so they do not wait for this tile's
+            // maximum; only when the maximum has outgrown the reference by the threshold (or nothing was seen yet) does
+            // the reference move, and the tile is done again: S stays readable until P is stored over columns 64..127.
+            // Maximum, exponential, sum and packing go element by element, so that the special-function unit and the
+            // arithmetic pipes of the one softmax warp a scheduler has at a time work side by side.
+            uint32_t packed_upper[32], packed_lower[32];
+            float sums[4], running[4];
+            auto half = [&](uint32_t (&packed)[32], int first_column, float subtract) {
+                uint32_t values[64];
+                tmem_load_64(s_address + first_column, values);
                 if (edge) {
 #pragma unroll
                     for (int c = 0; c < 64; ++c)
-                        if (!(tile_key + c >= low && tile_key + c <= position)) lower[c] = 0xff800000u;      // -inf
+                        if (!(tile_key + first_column + c >= low && tile_key + first_column + c <= position)) values[c] = 0xff800000u;   // -inf
                 }
 #pragma unroll
-                for (int c = 0; c < 8; ++c) running[c] = __uint_as_float(lower[c]);
+                for (int c = 0; c < 64; c += 2) {
+                    const float x0 = __uint_as_float(values[c]), x1 = __uint_as_float(values[c + 1]);
+                    // the scale and the reference enter the exponent in one fused multiply-add
+                    const float e0 = exp2_approx(fmaf(x0, p.scale_log2, -subtract));
+                    const float e1 = exp2_approx(fmaf(x1, p.scale_log2, -subtract));
+                    running[(c >> 1) & 3] = fmaxf(running[(c >> 1) & 3], fmaxf(x0, x1));
+                    sums[(c >> 1) & 3] += e0 + e1;
+                    packed[c >> 1] = pack2(e0, e1);
+                }
+            };
+            auto whole_tile = [&]() -> float {
+                const float subtract = reference == -INFINITY ? 0.0f : reference;
 #pragma unroll
-                for (int c = 8; c < 64; ++c) running[c & 7] = fmaxf(running[c & 7], __uint_as_float(lower[c]));
-            }
-            tmem_load_64(s_address + 64, upper);
-            if (edge) {
-#pragma unroll
-                for (int c = 0; c < 64; ++c)
-                    if (!(tile_key + 64 + c >= low && tile_key + 64 + c <= position)) upper[c] = 0xff800000u;
-            }
-#pragma unroll
-            for (int c = 0; c < 64; ++c) running[c & 7] = fmaxf(running[c & 7], __uint_as_float(upper[c]));
-            const float raw_max = fmaxf(fmaxf(fmaxf(running[0], running[1]), fmaxf(running[2], running[3])),
-                                        fmaxf(fmaxf(running[4], running[5]), fmaxf(running[6], running[7])));
-            // the maximum is taken over the raw scores (the scale is positive); the scale and the reference enter
-            // the exponent in one fused multiply-add
-            const float tile_max = raw_max * p.scale_log2;
-            // the reference moves only when the maximum has outgrown it by the threshold (or nothing was seen yet)
+                for (int c = 0; c < 4; ++c) {
+                    sums[c] = 0.0f;
+                    running[c] = -INFINITY;
+                }
+                half(packed_upper, 64, subtract);
+                half(packed_lower, 0, subtract);
+                // the maximum is taken over the raw scores (the scale is positive)
+                return fmaxf(fmaxf(running[0], running[1]), fmaxf(running[2], running[3])) * p.scale_log2;
+            };
+            const float tile_max = whole_tile();
             float factor = 1.0f;
-            if (tile_max > reference + kRescaleThreshold || (reference == -INFINITY && tile_max > -INFINITY)) {
-                factor = reference == -INFINITY ? 0.0f : exp2_approx(reference - tile_max);
-                reference = tile_max;
-            }
-            const float subtract = reference == -INFINITY ? 0.0f : reference;
-            // O is rescaled (by the whole warp, rows that need nothing use 1): P V of the tile before is done, since
-            // this tile's S was computed behind it
-            if (j > 0 && __any_sync(0xffffffffu, factor != 1.0f)) {
+            const bool moved = tile_max > reference + kRescaleThreshold || (reference == -INFINITY && tile_max > -INFINITY);
+            if (__any_sync(0xffffffffu, moved)) {
+                if (moved) {
+                    factor = reference == -INFINITY ? 0.0f : exp2_approx(reference - tile_max);
+                    reference = tile_max;
+                }
+                whole_tile();
+                // O is rescaled (by the whole warp, rows that need nothing use 1): P V of the tile before is done,
+                // since this tile's S was computed behind it
+                if (j > 0) {
 #pragma unroll
-                for (int chunk = 0; chunk < kDim / 32; ++chunk) {
-                    uint32_t o_raw[32];
-                    tmem_load_32(o_address + chunk * 32, o_raw);
+                    for (int chunk = 0; chunk < kDim / 32; ++chunk) {
+                        uint32_t o_raw[32];
+                        tmem_load_32(o_address + chunk * 32, o_raw);
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) o_raw[c] = __float_as_uint(__uint_as_float(o_raw[c]) * factor);
-                    tmem_store_32(o_address + chunk * 32, o_raw);
+                        for (int c = 0; c < 32; ++c) o_raw[c] = __float_as_uint(__uint_as_float(o_raw[c]) * factor);
+                        tmem_store_32(o_address + chunk * 32, o_raw);
+                    }
                 }
             }
-            float partial[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            uint32_t packed_upper[32];
-#pragma unroll
-            for (int c = 0; c < 64; ++c) upper[c] = __float_as_uint(exp2_approx(fmaf(__uint_as_float(upper[c]), p.scale_log2, -subtract)));
-#pragma unroll
-            for (int c = 0; c < 64; ++c) partial[c & 3] += __uint_as_float(upper[c]);
-#pragma unroll
-            for (int c = 0; c < 32; ++c) packed_upper[c] = pack2(__uint_as_float(upper[2 * c]), __uint_as_float(upper[2 * c + 1]));
-            // the lower 64 scores again (their columns are untouched: P goes over columns 64..127)
-            uint32_t packed_lower[32];
-            {
-                uint32_t lower[64];
-                tmem_load_64(s_address, lower);
-                if (edge) {
-#pragma unroll
-                    for (int c = 0; c < 64; ++c)
-                        if (!(tile_key + c >= low && tile_key + c <= position)) lower[c] = 0xff800000u;
-                }
-#pragma unroll
-                for (int c = 0; c < 64; ++c) lower[c] = __float_as_uint(exp2_approx(fmaf(__uint_as_float(lower[c]), p.scale_log2, -subtract)));
-#pragma unroll
-                for (int c = 0; c < 64; ++c) partial[c & 3] += __uint_as_float(lower[c]);
-#pragma unroll
-                for (int c = 0; c < 32; ++c) packed_lower[c] = pack2(__uint_as_float(lower[2 * c]), __uint_as_float(lower[2 * c + 1]));
-            }
-            row_sum = row_sum * factor + ((partial[0] + partial[1]) + (partial[2] + partial[3]));
+            row_sum = row_sum * factor + ((sums[0] + sums[1]) + (sums[2] + sums[3]));
             tmem_store_32(s_address + kColP, packed_lower);          // keys 0..63 of the tile
             tmem_store_32(s_address + kColP + 32, packed_upper);     // keys 64..127
             tmem_wait_store();
@@ -431,12 +420,12 @@ LLM_EXPORT int llm_attention_prefill_wide_supports(int head_dim, int n_q_heads, 
     return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
 }
 
-// total_pairs: sum over the sequences it handles of ceil(ceil(q_len * group / 256) / 2): each CTA takes a 256-row
-// tile and its mirror; sequences of one token are skipped when skip_single is set (the decode kernel takes them).
+// total_pairs: the number of CTAs: with pairing, the sum over the sequences it handles of ceil(ceil(q_len * group / 256) / 2)
+// (each CTA takes a 256-row tile and its mirror, which evens out the work of a causal prompt); without, one CTA per tile; sequences of one token are skipped when skip_single is set (the decode kernel takes them).
 LLM_EXPORT int llm_attention_prefill_wide(const void* q, int q_stride, int n_tokens, const void* k_pages, const void* v_pages,
                                           const int* block_tables, int max_blocks, const int* q_start, const int* context_len,
                                           void* out, int n_seqs, int n_q_heads, int n_kv_heads, int head_dim, int page_size,
-                                          float scale, int window, int skip_single, int total_pairs, int* error_flag,
+                                          float scale, int window, int skip_single, int pairing, int total_pairs, int* error_flag,
                                           cudaStream_t stream) {
     if (total_pairs <= 0) return LLM_OK;
     if (!llm_attention_prefill_wide_supports(head_dim, n_q_heads, n_kv_heads, page_size) || !aligned16(q) || q_stride % 8 ||
@@ -496,6 +485,7 @@ LLM_EXPORT int llm_attention_prefill_wide(const void* q, int q_stride, int n_tok
     p.scale_log2 = scale * kLog2e;
     p.window = window;
     p.skip_single = skip_single;
+    p.pairing = pairing;
     p.error_flag = error_flag;
     static bool configured = false;
     if (!configured) {

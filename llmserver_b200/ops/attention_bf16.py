@@ -20,7 +20,10 @@ WAVE_BLOCKS = 296   # one wave of two blocks per SM on 148 SMs
 PREFILL_KERNEL = os.environ.get("LLMSERVER_B200_PREFILL_ATTENTION", "tcgen05")
 PREFILL_TILE = 128   # rows per block of the tcgen05 portions kernel
 WIDE_TILE = 256      # rows per block of the 256-row kernel
-WIDE_MIN_ROWS = int(os.environ.get("LLMSERVER_B200_PREFILL_WIDE_ROWS", "4096"))   # longest portion (rows) from which it is used
+# the 256-row kernel is used when the longest portion has this many rows (tokens x heads of a group) and its request
+# holds this many tokens: measured on the 8B head shape, it wins from about there (long key loops, enough row tiles)
+WIDE_MIN_ROWS = int(os.environ.get("LLMSERVER_B200_PREFILL_WIDE_ROWS", "8192"))
+WIDE_MIN_CONTEXT = int(os.environ.get("LLMSERVER_B200_PREFILL_WIDE_CONTEXT", "8192"))
 
 
 def prefill_tcgen05_supported(head_dim: int, n_q_heads: int, n_kv_heads: int, page_size: int) -> bool:
@@ -28,16 +31,29 @@ def prefill_tcgen05_supported(head_dim: int, n_q_heads: int, n_kv_heads: int, pa
         library().llm_attention_prefill_tcgen05_supports(head_dim, n_q_heads, n_kv_heads, page_size))
 
 
+FORCE_PAIRING = None     # True / False: tests set it to run both ways of handing out row tiles
+_SM_COUNT = {}
+
+
+def _block_slots(device, wide: bool) -> int:
+    """Blocks of a prompt kernel the GPU holds at a time (one per SM for the 256-row kernel, two for the 128-row one)."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _SM_COUNT:
+        _SM_COUNT[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _SM_COUNT[index] * (1 if wide else 2)
+
+
 def prefill_wide_wanted(batch, group: int, head_dim: int, n_q_heads: int, n_kv_heads: int, page_size: int) -> bool:
     """Whether the prompt portions of this batch go to the 256-row kernel: when the longest of them has enough
-    rows that 256-row tiles fill the GPU, or when asked for."""
+    rows and keys, or when asked for."""
     if PREFILL_KERNEL == "tcgen05-128":
         return False
     if not library().llm_attention_prefill_wide_supports(head_dim, n_q_heads, n_kv_heads, page_size):
         return False
     if PREFILL_KERNEL == "tcgen05-256":
         return True
-    return max(batch.q_lens) * group >= WIDE_MIN_ROWS
+    length, context = max(zip(batch.q_lens, batch.context_lens))
+    return length * group >= WIDE_MIN_ROWS and context >= WIDE_MIN_CONTEXT
 
 
 def supported(head_dim: int, n_q_heads: int, n_kv_heads: int) -> bool:
@@ -98,12 +114,16 @@ def try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_head
         group = n_q_heads // n_kv_heads
         wide = prefill_wide_wanted(batch, group, head_dim, n_q_heads, n_kv_heads, page_size)
         rows_per_tile = WIDE_TILE if wide else PREFILL_TILE
-        # a block takes a row tile and its mirror image (the light one with the heavy one)
-        big_tiles = sum((-(-length * group // rows_per_tile) + 1) // 2 for length in batch.q_lens if length > 1 or not run_decode)
-        call("llm_attention_prefill_wide" if wide else "llm_attention_prefill_tcgen05", qkv.data_ptr(), q_stride, batch.n_tokens, k_pages.data_ptr(), v_pages.data_ptr(),
+        tile_counts = [-(-length * group // rows_per_tile) for length in batch.q_lens if length > 1 or not run_decode]
+        # A block takes a row tile and its mirror image (the light one with the heavy one), which evens out the work of
+        # a causal prompt, unless that leaves SMs without a block: portions over a long context have few, even tiles.
+        paired = sum((count + 1) // 2 for count in tile_counts)
+        pairing = paired * n_kv_heads >= (3 * _block_slots(qkv.device, wide)) // 4 if FORCE_PAIRING is None else FORCE_PAIRING
+        call("llm_attention_prefill_wide" if wide else "llm_attention_prefill_tcgen05", qkv.data_ptr(), q_stride, batch.n_tokens,
+             k_pages.data_ptr(), v_pages.data_ptr(),
              block_tables.data_ptr(), block_tables.shape[-1], batch.q_start.data_ptr(), batch.context_len.data_ptr(),
              out.data_ptr(), batch.n_seqs, n_q_heads, n_kv_heads, head_dim, page_size, float(scale), int(window),
-             int(run_decode), big_tiles, flag, stream_handle())
+             int(run_decode), int(pairing), paired if pairing else sum(tile_counts), flag, stream_handle())
         run_portions = False
         if not run_decode:
             return out

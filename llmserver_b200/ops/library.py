@@ -27,9 +27,9 @@ SIGNATURES = {
     "llm_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _S],
     "llm_attention_mma_supports": [_I, _I, _I],
     "llm_attention_prefill_tcgen05_supports": [_I, _I, _I, _I],
-    "llm_attention_prefill_tcgen05": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _S],
+    "llm_attention_prefill_tcgen05": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _S],
     "llm_attention_prefill_wide_supports": [_I, _I, _I, _I],
-    "llm_attention_prefill_wide": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _S],
+    "llm_attention_prefill_wide": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _S],
     "llm_gemm_small_m_supports": [_I, _I, _I],
     "llm_gemm_small_m": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _S],
     "llm_attention_mma": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _I, _I, _P, _P, _P, _S],

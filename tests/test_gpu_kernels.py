@@ -435,17 +435,18 @@ def test_attention_prefill_tcgen05(heads, kv_heads, page_size, window):
     want = torch.cat([plain_attention_rows(q.double(), k.double(), v.double(), scale, window, c - n)
                       for q, k, v, c, n in zip(queries, dense_k, dense_v, contexts, q_lens)])
     results = {}
-    for kernel in ("tcgen05-128", "tcgen05-256", "mma"):
-        attention_bf16.PREFILL_KERNEL = kernel
+    for kernel, pairing in (("tcgen05-128", False), ("tcgen05-128", True), ("tcgen05-256", False), ("tcgen05-256", True), ("mma", None)):
+        attention_bf16.PREFILL_KERNEL, attention_bf16.FORCE_PAIRING = kernel, pairing
         try:
             out = attention_bf16.try_attention(packed.to(DEVICE), q_stride, FakeBatch(contexts, q_lens), tables, k_pages, v_pages,
                                                heads, kv_heads, dim, scale, window or 0)
         finally:
-            attention_bf16.PREFILL_KERNEL = "tcgen05"
+            attention_bf16.PREFILL_KERNEL, attention_bf16.FORCE_PAIRING = "tcgen05", None
         torch.cuda.synchronize()
         from llmserver_b200.ops import gemm_bf16
         gemm_bf16.check_errors()
-        close(out, want, dtype, f"prompt attention ({kernel})")
-        results[kernel] = out
+        close(out, want, dtype, f"prompt attention ({kernel}, tiles {'paired' if pairing else 'one by one'})")
+        if pairing is not False:
+            results[kernel] = out
     close(results["tcgen05-128"], results["mma"].double().cpu(), dtype, "the 128-row kernel against the mma.sync kernel")
     close(results["tcgen05-256"], results["mma"].double().cpu(), dtype, "the 256-row kernel against the mma.sync kernel")

@@ -89,6 +89,28 @@ def test_mixed_requests_reuse_pages(tiny_folders, name, dtype):
     assert pool.allocations > pool.num_pages, "the trace was meant to reuse pages"
 
 
+@pytest.mark.parametrize("kernel,pairing", [("tcgen05-128", True), ("tcgen05-256", False), ("tcgen05-256", True)])
+def test_prompt_kernels_through_replay(tiny_folders, kernel, pairing):
+    """The other ways prompt portions can run (the 256-row kernel, which serving uses from 8192 rows on; row tiles
+    handed out in mirror pairs, which it does when there are enough of them), driven through the same traces."""
+    from llmserver_b200.ops import attention_bf16
+    name, dtype = "e", "bfloat16"
+    vocab = TINY[name][0]["vocab_size"]
+    attention_bf16.PREFILL_KERNEL, attention_bf16.FORCE_PAIRING = kernel, pairing
+    try:
+        tokens = tokens_for(vocab, 300, 11)
+        records = traces.portions("r", tokens, [7, 2, 70, 3, 130, 16, 33])
+        got, _ = run_in_process(tiny_folders[name], dtype, records, traces.rounded(len(tokens)), page_size=8)
+        compare(got, records, {"r": tokens}, tiny_folders[name], dtype, f"portions ({kernel})")
+        lengths = {"r0": 150, "r1": 97, "r2": 40, "r3": 211, "r4": 64}
+        requests = {key: tokens_for(vocab, length, 31 + index) for index, (key, length) in enumerate(lengths.items())}
+        records, peak = traces.mixed(requests, seed=5)
+        got, _ = run_in_process(tiny_folders[name], dtype, records, peak)
+        compare(got, records, requests, tiny_folders[name], dtype, f"mixed ({kernel})")
+    finally:
+        attention_bf16.PREFILL_KERNEL, attention_bf16.FORCE_PAIRING = "tcgen05", None
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_long_decoding(tiny_folders, dtype):
     vocab = TINY["c"][0]["vocab_size"]
