@@ -78,6 +78,21 @@ def plan(batch, group: int, n_kv_heads: int):
         # equal splits beat ragged ones, and one wave beats one and a half.
         pairs = singles * n_kv_heads
         splits = max(1, min(WAVE_BLOCKS // pairs, -(-longest // MIN_SPLIT)))
+        if pairs > WAVE_BLOCKS:
+            # More than a wave of whole contexts: when the last wave would leave most SMs idle (40 sequences x 8 kv
+            # heads = 1.08 waves take as long as 2), the contexts are split after all.  Measured on the 8B head shape at
+            # context 3072: unsplit wins while the waves are three quarters full, else the fewest splits that fill
+            # them to 0.85 (batch 40: 119 -> 100 us, batch 48: 123 -> 105, batch 80: 182 -> 170).
+            def filled(count):
+                blocks = pairs * count
+                return blocks / (-(-blocks // WAVE_BLOCKS) * WAVE_BLOCKS)
+            if filled(1) < 0.75:
+                candidates = [count for count in (2, 3, 4) if longest // count >= 4 * TILE]
+                good = [count for count in candidates if filled(count) >= 0.85]
+                if good:
+                    splits = good[0]
+                elif candidates:
+                    splits = max(candidates, key=filled)
         split_len = max(MIN_SPLIT, -(-(-(-longest // splits)) // TILE) * TILE)
         forced = os.environ.get("LLMSERVER_B200_DECODE_SPLIT")
         if forced:
