@@ -25,10 +25,10 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, int q_stride, 
     pdl_trigger();   // let the next kernel start launching
     pdl_wait();      // everything before this kernel in the stream is complete and visible
     extern __shared__ float q_shared[];  // [warps][head_dim]
-    const int token = blockIdx.y;
+    const int token = blockIdx.x;
     const int warps_per_block = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int head = blockIdx.x * warps_per_block + warp;
+    const int head = blockIdx.y * warps_per_block + warp;
     if (head >= n_q_heads) return;
     const int kv_head = head / (n_q_heads / n_kv_heads);
     const int position = positions[token];
@@ -101,12 +101,8 @@ LLM_EXPORT int llm_attention_generic(const void* q, int q_stride, const void* k_
         llm_set_error("attention_generic: %d query heads are no multiple of %d kv heads", n_q_heads, n_kv_heads);
         return LLM_REFUSED;
     }
-    if (n_tokens > 65535) {
-        llm_set_error("attention_generic: at most 65535 tokens per launch, got %d", n_tokens);
-        return LLM_REFUSED;
-    }
     const int warps = 4;
-    dim3 grid((n_q_heads + warps - 1) / warps, n_tokens);
+    dim3 grid(n_tokens, (n_q_heads + warps - 1) / warps);
     const size_t shared = (size_t)warps * head_dim * sizeof(float);
     LLM_DISPATCH_DTYPE(dtype, (llm_launch(attention_generic_kernel<T>, grid, warps * 32, shared, stream, 
                                   (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_tables,

@@ -18,7 +18,7 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__
     pdl_wait();      // everything before this kernel in the stream is complete and visible
     __shared__ float a_tile[BK][BM + 4];
     __shared__ float w_tile[BK][BN + 4];
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
     const int thread = threadIdx.x;
     const int row_group = thread / 16, col_group = thread % 16;  // outputs (row_group*4.., col_group*4..)
     float acc[TM][TN];
@@ -68,11 +68,11 @@ LLM_EXPORT int llm_gemm_f32(const float* a, const float* w, float* c, int m, int
                             cudaStream_t stream) {
     if (m == 0 || n == 0) return LLM_OK;
     const int blocks_m = (m + BM - 1) / BM;
-    if (blocks_m > 65535) {
-        llm_set_error("gemm_f32: at most %d rows per launch, got %d", 65535 * BM, m);
+    if ((n + BN - 1) / BN > 65535) {
+        llm_set_error("gemm_f32: at most %d output columns per launch, got %d", 65535 * BN, n);
         return LLM_REFUSED;
     }
-    dim3 grid((n + BN - 1) / BN, blocks_m);
+    dim3 grid(blocks_m, (n + BN - 1) / BN);
     llm_launch(gemm_f32_kernel, grid, 256, 0, stream, a, w, c, m, n, k, lda, ldw, ldc);
     return llm_check_launch("gemm_f32");
 }

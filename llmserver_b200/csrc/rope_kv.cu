@@ -35,7 +35,7 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const W* __res
     pdl_trigger();   // let the next kernel start launching
     pdl_wait();      // everything before this kernel in the stream is complete and visible
     extern __shared__ float2 rotation[];   // (cos, sin) of angle = position * inv_freq[i], i < head_dim / 2
-    const int token = blockIdx.y;
+    const int token = blockIdx.x;
     const int warps_per_block = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     const int total_heads = n_q_heads + 2 * n_kv_heads;
@@ -49,7 +49,7 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const W* __res
         }
     }
     __syncthreads();
-    const int first_head = blockIdx.x * heads_per_block;
+    const int first_head = blockIdx.y * heads_per_block;
     const int end_head = min(first_head + heads_per_block, total_heads);
     for (int head = first_head + (threadIdx.x >> 5); head < end_head; head += warps_per_block) {
         T* src = qkv + (size_t)token * total_heads * head_dim + (size_t)head * head_dim;
@@ -167,7 +167,7 @@ __global__ void qk_norm_rope_kv_write_wide_kernel(T* __restrict__ qkv, const W* 
     pdl_wait();
     constexpr int kHalf = LANES * 8, kDim = 2 * kHalf;
     __shared__ float2 rotation[kHalf];
-    const int token = blockIdx.y;
+    const int token = blockIdx.x;
     const int total_heads = n_q_heads + 2 * n_kv_heads;
     const int position = positions[token];
     if (inv_freq) {
@@ -179,7 +179,7 @@ __global__ void qk_norm_rope_kv_write_wide_kernel(T* __restrict__ qkv, const W* 
     __syncthreads();
     const int groups_per_block = blockDim.x / LANES;
     const int group = threadIdx.x / LANES, sub = threadIdx.x % LANES;
-    const int first_head = blockIdx.x * heads_per_block;
+    const int first_head = blockIdx.y * heads_per_block;
     const int end_head = min(first_head + heads_per_block, total_heads);
     const int rounds = (end_head - first_head + groups_per_block - 1) / groups_per_block;
     for (int round = 0; round < rounds; ++round) {        // the same number of rounds for every lane of a warp
@@ -260,10 +260,6 @@ LLM_EXPORT int llm_qk_norm_rope_kv_write(void* qkv, const void* q_weight, const 
         llm_set_error("qk_norm_rope_kv_write: head_dim must be even, got %d", head_dim);
         return LLM_REFUSED;
     }
-    if (n_tokens > 65535) {
-        llm_set_error("qk_norm_rope_kv_write: at most 65535 tokens per launch, got %d", n_tokens);
-        return LLM_REFUSED;
-    }
     const int total_heads = n_q_heads + 2 * n_kv_heads;
     // many tokens (prompts): one block of 8 warps per token takes all heads and computes the token's angles
     // once; few tokens (decode): four heads per block of four warps, for more blocks in flight
@@ -273,7 +269,7 @@ LLM_EXPORT int llm_qk_norm_rope_kv_write(void* qkv, const void* q_weight, const 
     const int per_vector = dtype == LLM_F32 ? 4 : 8;
     const int vector_form = head_dim % per_vector == 0 && head_dim % 4 == 0 && head_dim <= 512 && aligned16(qkv) && aligned16(k_pages) &&
                             aligned16(v_pages) && aligned16(q_weight) && aligned16(k_weight);
-    dim3 grid((total_heads + heads_per_block - 1) / heads_per_block, n_tokens);
+    dim3 grid(n_tokens, (total_heads + heads_per_block - 1) / heads_per_block);
     const size_t shared = (size_t)(head_dim / 2) * sizeof(float2);
     // head sizes 64 / 128 / 256 with aligned operands: the wide form
     const bool wide = vector_form && (head_dim == 64 || head_dim == 128 || head_dim == 256) && aligned16(q_weight) && aligned16(k_weight);
@@ -281,7 +277,7 @@ LLM_EXPORT int llm_qk_norm_rope_kv_write(void* qkv, const void* q_weight, const 
         const int wide_threads = 256;
         const int lanes = head_dim / 16;
         const int wide_heads_per_block = n_tokens >= 256 ? total_heads : (wide_threads / lanes < total_heads ? wide_threads / lanes : total_heads);
-        dim3 wide_grid((total_heads + wide_heads_per_block - 1) / wide_heads_per_block, n_tokens);
+        dim3 wide_grid(n_tokens, (total_heads + wide_heads_per_block - 1) / wide_heads_per_block);
 #define LLM_ROPE_WIDE(LANES)                                                                                          \
         LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype, (llm_launch(qk_norm_rope_kv_write_wide_kernel<T, W, LANES>, wide_grid, wide_threads, 0, stream, \
                                       (T*)qkv, (const W*)q_weight, (const W*)k_weight, inv_freq, positions, seq_of_token, \
