@@ -142,3 +142,120 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
     step.release("y")
     step.release("z")
     cache.check_invariants()
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# A feed-forward with routing and another position encoding, defined here as well: the model below uses them in
+# one layer and the framework's SwiGLU and rotary encoding in the other, through the same registries.
+
+N_EXPERTS = 3
+
+
+def register_toy_feed_forward_and_position():
+    from llmserver_b200.parts import FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, PositionEncoding
+    from llmserver_b200.weights.declare import WeightDecl
+
+    @FEED_FORWARDS.register("toy_top1_experts")
+    class Top1Experts(FeedForward):
+        """probabilities = softmax(x R^T) in 32-bit; out = p[e] * (x W_e^T) for the likeliest expert e of each token."""
+
+        @classmethod
+        def declare_weights(cls, params):
+            decls = {"router.weight": WeightDecl((params["experts"], params["hidden"]))}
+            for e in range(params["experts"]):
+                decls[f"experts.{e}.weight"] = WeightDecl((params["hidden"], params["hidden"]))
+            return decls
+
+        def __init__(self, params, weights, runtime):
+            super().__init__(params, weights, runtime)
+            self.router = weights["router.weight"].float()
+            self.experts = [weights[f"experts.{e}.weight"].float() for e in range(params["experts"])]
+
+        def forward(self, x):
+            probabilities = torch.softmax(x.float() @ self.router.T, dim=-1)
+            weight, chosen = probabilities.max(dim=-1)
+            out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+            for e, expert in enumerate(self.experts):
+                rows = (chosen == e).nonzero().flatten()
+                if rows.numel():
+                    out[rows] = (x[rows].float() @ expert.T) * weight[rows, None]
+            return out.to(x.dtype)
+
+    @POSITION_ENCODINGS.register("toy_harmonic_rotary")
+    class HarmonicRotary(PositionEncoding):
+        """Rotation by position / (1 + i) for pair i: another set of frequencies for the same rotating kernel."""
+
+        def __init__(self, params, weights, runtime):
+            super().__init__(params, weights, runtime)
+            self.head_dim = int(params["head_dim"])
+            self.inv_freq = (1.0 / (1.0 + torch.arange(self.head_dim // 2, dtype=torch.float32))).to(runtime.device)
+
+    return Top1Experts, HarmonicRotary
+
+
+def routed_spec(hidden=40, vocab=90):
+    from llmserver_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    norm = PartSpec.of("rmsnorm", width=hidden, eps=1e-6)
+    block = PartSpec.of("pre_norm", mixer_prefix="mixer.", feed_forward_prefix="ffn.", mixer_norm_prefix="norm1.",
+                        feed_forward_norm_prefix="norm2.")
+    attention = PartSpec.of("gqa_attention", hidden=hidden, heads=2, kv_heads=2, head_dim=16, scale=0.25, qk_norm=True,
+                            eps=1e-6, window=None)
+    layers = [LayerSpec("toy.layers.0.", block, attention, PartSpec.of("toy_top1_experts", hidden=hidden, experts=N_EXPERTS),
+                        norm, norm, "harmonic"),
+              LayerSpec("toy.layers.1.", block, attention, PartSpec.of("swiglu", hidden=hidden, intermediate=56), norm, norm, "rotary")]
+    return ModelSpec(architecture="ToyRoutedForTests", vocab_size=vocab, hidden_size=hidden, layers=layers,
+                     schedule=[ScheduleEntry(0), ScheduleEntry(1)],
+                     positions={"rotary": PartSpec.of("rotary", head_dim=16, theta=10000.0),
+                                "harmonic": PartSpec.of("toy_harmonic_rotary", head_dim=16)},
+                     final_norm=norm, embedding_name="toy.embed.weight", final_norm_prefix="toy.norm.", head_name="toy.head.weight")
+
+
+def plain_routed_forward(weights, tokens):
+    w = {name: tensor.double() for name, tensor in weights.items()}
+    h = w["toy.embed.weight"][torch.tensor(tokens)]
+    positions = torch.arange(len(tokens), dtype=torch.float64)
+    harmonic = positions[:, None] * (1.0 / (1.0 + torch.arange(8, dtype=torch.float32))).double()[None, :]
+    tables = [(torch.cos(torch.cat([harmonic, harmonic], dim=-1)), torch.sin(torch.cat([harmonic, harmonic], dim=-1))),
+              plain_model.rope_tables(torch.arange(len(tokens)), 16, 10000.0, torch.float64)]
+    for index in range(2):
+        p = f"toy.layers.{index}."
+        normed = plain_model.rms_norm(h, w[p + "norm1.weight"], 1e-6)
+        layer = {"self_attn." + k[len(p + "mixer."):]: v for k, v in w.items() if k.startswith(p + "mixer.")}
+        q, k, v = plain_model.project_qkv(normed, layer, 2, 2, 16, 1e-6, *tables[index])
+        h = h + plain_model.causal_attention(q, k, v, 0.25) @ layer["self_attn.o_proj.weight"].T
+        normed = plain_model.rms_norm(h, w[p + "norm2.weight"], 1e-6)
+        if index == 0:
+            probabilities = torch.softmax(normed @ w[p + "ffn.router.weight"].T, dim=-1)
+            weight, chosen = probabilities.max(dim=-1)
+            h = h + torch.stack([(row @ w[p + f"ffn.experts.{int(e)}.weight"].T) * g for row, e, g in zip(normed, chosen, weight)])
+        else:
+            h = h + plain_model.swiglu_mlp(normed, {"mlp." + k[len(p + "ffn."):]: v for k, v in w.items() if k.startswith(p + "ffn.")})
+    return (plain_model.rms_norm(h, w["toy.norm.weight"], 1e-6) @ w["toy.head.weight"].T).numpy()
+
+
+def test_toy_routed_feed_forward_and_position_encoding():
+    """A feed-forward that routes each token to one of three experts and a position encoding with other frequencies
+    are registered from here, built by the generic decoder beside the framework's own parts, and stepped in pieces."""
+    from llmserver_b200.cache import CacheManager
+    from llmserver_b200.engine.step import StepFunction
+    from llmserver_b200.models import DecoderModel
+    from llmserver_b200.parts import Runtime
+
+    register_toy_feed_forward_and_position()
+    dtype = torch.float32
+    spec = routed_spec()
+    source = MovedSource(spec, 9, dtype)
+    model = DecoderModel(spec, source, Runtime(dtype, DEVICE))
+    cache = CacheManager(model.cache_needs(), 8, 24, num_slots=2)
+    cache.materialize(DEVICE, dtype)
+    step = StepFunction(model, cache)
+    tokens = tokens_for(90, 41, 4)
+    want = plain_routed_forward(source.seen, tokens)
+    step.admit("r")
+    got = [step.run([("r", tokens[:17], list(range(17)))]), step.run([("r", tokens[17:19], [0, 1])])]
+    got += [step.run([("r", [token], [0])]) for token in tokens[19:30]]
+    got.append(step.run([("r", tokens[30:], list(range(11)))]))
+    assert_close(torch.cat(got).cpu().numpy(), want, "float32", "toy routed model")
+    step.check_errors()
+    step.release("r")
+    cache.check_invariants()
