@@ -43,12 +43,23 @@ struct AttnParams {
     float scale_log2;
     int window;
     int skip_single;         // portions kernel: leave sequences with one token to the decode kernel
-    int split_len;           // decode kernel: keys per split (multiple of 64)
+    int split_len;           // decode kernel: keys per split (multiple of 64); negative: -split_len equal parts per sequence
     int max_splits;
     float* partial_out;      // [N, Hq, max_splits, D]
     float* partial_ml;       // [N, Hq, max_splits, 2]
     int* error_flag;         // set when a bounded wait of the TMA decode kernel runs out (may be null)
 };
+
+// Keys per split of a sequence that sees `span` keys: the fixed length, or (split_len < 0) the span divided into
+// -split_len equal parts, in whole tiles and no shorter than three tiles.  With equal parts every sequence of a
+// batch gets the same number of blocks, all about equally long, whatever its length: the launch shape of a captured
+// graph (sized for the longest context it may meet) then fits shorter contexts as well.
+__device__ __forceinline__ int split_length(const AttnParams& p, int span) {
+    if (p.split_len > 0) return p.split_len;
+    const int parts = -p.split_len;
+    const int length = ((span + parts - 1) / parts + kTileKeys - 1) / kTileKeys * kTileKeys;
+    return length < 3 * kTileKeys ? 3 * kTileKeys : length;
+}
 
 __device__ __forceinline__ uint32_t smem_address(const void* pointer) {
     return (uint32_t)__cvta_generic_to_shared(pointer);
@@ -371,10 +382,11 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnPa
     const int position = context - 1;
     const int low_key = p.window > 0 ? max(0, position - p.window + 1) : 0;
     const int first_key = (low_key / kTileKeys) * kTileKeys;
-    const int n_splits = (context - first_key + p.split_len - 1) / p.split_len;
+    const int split_len = split_length(p, context - first_key);
+    const int n_splits = (context - first_key + split_len - 1) / split_len;
     if (split >= n_splits) return;
-    const int split_begin = first_key + split * p.split_len;
-    const int split_end = min(split_begin + p.split_len, context);
+    const int split_begin = first_key + split * split_len;
+    const int split_end = min(split_begin + split_len, context);
     const int n_tiles = (split_end - split_begin + kTileKeys - 1) / kTileKeys;
     const int* table = p.block_tables + (size_t)seq * p.max_blocks;
 
@@ -521,10 +533,11 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
     const int position = context - 1;
     const int low_key = p.window > 0 ? max(0, position - p.window + 1) : 0;
     const int first_key = (low_key / kTileKeys) * kTileKeys;
-    const int n_splits = (context - first_key + p.split_len - 1) / p.split_len;
+    const int split_len = split_length(p, context - first_key);
+    const int n_splits = (context - first_key + split_len - 1) / split_len;
     if (split >= n_splits) return;
-    const int split_begin = first_key + split * p.split_len;
-    const int split_end = min(split_begin + p.split_len, context);
+    const int split_begin = first_key + split * split_len;
+    const int split_end = min(split_begin + split_len, context);
     const int n_tiles = (split_end - split_begin + kTileKeys - 1) / kTileKeys;
     const int* table = p.block_tables + (size_t)seq * p.max_blocks;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -680,7 +693,8 @@ __global__ void attention_decode_merge_kernel(const AttnParams p) {
     const int context = p.context_len[seq];
     const int low_key = p.window > 0 ? max(0, context - p.window) : 0;
     const int first_key = (low_key / kTileKeys) * kTileKeys;
-    const int n_splits = (context - first_key + p.split_len - 1) / p.split_len;
+    const int split_len = split_length(p, context - first_key);
+    const int n_splits = (context - first_key + split_len - 1) / split_len;
     if (n_splits <= 1) return;
     const size_t slot0 = ((size_t)token * p.n_q_heads + head) * p.max_splits;
     float best = -INFINITY;
@@ -790,8 +804,8 @@ LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, const void* k_page
                       head_dim, n_q_heads, n_kv_heads);
         return LLM_REFUSED;
     }
-    if (run_decode && (split_len <= 0 || split_len % kTileKeys || max_splits <= 0)) {
-        llm_set_error("attention_mma: split_len %d must be a positive multiple of %d", split_len, kTileKeys);
+    if (run_decode && (split_len == 0 || (split_len > 0 && split_len % kTileKeys) || max_splits <= 0 || -split_len > max_splits)) {
+        llm_set_error("attention_mma: split_len %d must be a positive multiple of %d, or minus a number of parts up to max_splits", split_len, kTileKeys);
         return LLM_REFUSED;
     }
     if (n_seqs > 65535 || n_kv_heads > 65535) {
@@ -854,8 +868,8 @@ LLM_EXPORT int llm_attention_decode_noalloc(const void* q, int q_stride, const v
                       head_dim, n_q_heads, n_kv_heads);
         return LLM_REFUSED;
     }
-    if (split_len <= 0 || split_len % kTileKeys || max_splits <= 0) {
-        llm_set_error("attention_decode_noalloc: split_len %d must be a positive multiple of %d and max_splits %d positive",
+    if (split_len == 0 || (split_len > 0 && split_len % kTileKeys) || max_splits <= 0 || -split_len > max_splits) {
+        llm_set_error("attention_decode_noalloc: split_len %d must be a positive multiple of %d, or minus a number of parts up to max_splits %d",
                       split_len, kTileKeys, max_splits);
         return LLM_REFUSED;
     }

@@ -27,7 +27,8 @@
 // q[s * q_stride + h * head_dim] (bfloat16); pages are [page, kv_head, slot, head_dim]; block_tables is
 // int32 [n_seqs, max_blocks]; q_start is int32 [n_seqs + 1] = 0, 1, 2, ... and context_len int32 [n_seqs],
 // both on the device; `out` is bfloat16 [n_seqs, n_q_heads * head_dim].  split_len is a positive multiple
-// of 64; max_splits must be at least ceil(longest context / split_len) + 1.  Returns 0 on success.
+// of 64, with max_splits at least ceil(longest context / split_len) + 1; or minus the number of equal parts every
+// context is divided into, with max_splits at least that number.  Returns 0 on success.
 #pragma once
 
 #include <cuda_runtime.h>

@@ -93,11 +93,13 @@ def plan(batch, group: int, n_kv_heads: int):
                     splits = good[0]
                 elif candidates:
                     splits = max(candidates, key=filled)
-        split_len = max(MIN_SPLIT, -(-(-(-longest // splits)) // TILE) * TILE)
+        # every sequence is divided into this many equal parts (a negative split length says so to the kernel): the
+        # longest gets the planned splits, shorter ones the same number of shorter blocks
+        split_len, max_splits = -splits, splits
         forced = os.environ.get("LLMSERVER_B200_DECODE_SPLIT")
         if forced:
             split_len = int(forced)
-        max_splits = -(-longest // split_len) + 1     # + 1: a window may start inside a tile
+            max_splits = -(-longest // split_len) + 1     # + 1: a window may start inside a tile
     cached = (run_portions, tiles, run_decode, split_len, max_splits)
     batch.scratch[key] = cached
     return cached
