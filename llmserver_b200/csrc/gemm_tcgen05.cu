@@ -259,13 +259,30 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
     if (p.split > 1) {
         cluster_sync();          // every CTA's partial tile is in its shared memory
         const uint32_t reduce_address = smem_u32(reduce);
-        for (int m = (int)rank; m < p.m; m += p.split) {      // token rows are dealt round-robin to the ranks
-            float total = 0.0f;
-            for (uint32_t peer = 0; peer < (uint32_t)p.split; ++peer)
-                total += load_peer(reduce_address + (uint32_t)(m * kBlockRows + row) * 4u, peer);
-            if (n < p.n) {
-                if (p.out_is_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldc + n] = total;
-                else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(total);
+        // Token rows are dealt round-robin to the ranks.  The peers' parts of up to four rows are all requested
+        // before the first is used (a load from a peer's shared memory takes some hundred cycles; one at a time
+        // they were most of the epilogue), then summed in the order of the ranks.
+        constexpr int kRowsAtOnce = 4;
+        for (int m0 = (int)rank; m0 < p.m; m0 += kRowsAtOnce * p.split) {
+            float parts[kRowsAtOnce][kMaxSplit];
+#pragma unroll
+            for (int j = 0; j < kRowsAtOnce; ++j) {
+                const int m = m0 + j * p.split;
+#pragma unroll
+                for (int peer = 0; peer < kMaxSplit; ++peer)
+                    parts[j][peer] = (m < p.m && peer < p.split)
+                                         ? load_peer(reduce_address + (uint32_t)(m * kBlockRows + row) * 4u, (uint32_t)peer) : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < kRowsAtOnce; ++j) {
+                const int m = m0 + j * p.split;
+                float total = parts[j][0];
+#pragma unroll
+                for (int peer = 1; peer < kMaxSplit; ++peer) total += parts[j][peer];      // absent peers add 0
+                if (m < p.m && n < p.n) {
+                    if (p.out_is_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldc + n] = total;
+                    else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(total);
+                }
             }
         }
         cluster_sync();          // nobody leaves while a peer may still read its shared memory
