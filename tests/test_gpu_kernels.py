@@ -388,30 +388,39 @@ def test_attention_tensor_core_kernels(heads, kv_heads, dim, page_size, window, 
     close(generic, want, dtype, "generic attention on the same batch")
 
 
-def test_tensor_core_attention_finds_a_far_key_and_respects_the_window_edge():
+@pytest.mark.parametrize("kernel,pairing", [("tcgen05", None), ("tcgen05-128", True), ("tcgen05-256", False), ("tcgen05-256", True), ("mma", None)])
+def test_tensor_core_attention_finds_a_far_key_and_respects_the_window_edge(kernel, pairing):
+    """One key among 1300 is made to stand out for the last query (score 1600 against about 0): every kernel that
+    can run a decode token or a portion of 40 has to return that key's value, wherever the key lies (first tile, a
+    tile's edge, just inside or just outside the window).  The jump of the maximum also sends the kernels through
+    their rescaling paths."""
     from llmserver_b200.ops import attention_bf16
     heads, kv_heads, dim, page_size, context = 4, 1, 128, 16, 1300
     dtype = torch.bfloat16
     direction = torch.zeros(dim)
     direction[9] = 1.0
-    for q_len in (1, 40):
-        for hot, window, found in ((3, 0, True), (255, 0, True), (256, 0, True), (1299 - 40, 0, True),
-                                   (context - 200, 200, True), (context - 201, 200, False)):
-            k = torch.randn((context, kv_heads, dim), generator=torch.Generator().manual_seed(1)) * 0.1
-            v = torch.randn((context, kv_heads, dim), generator=torch.Generator().manual_seed(2))
-            k[hot, 0] = direction * 40.0
-            q = torch.zeros((q_len, heads, dim))
-            q[-1] = direction * 40.0       # the last query looks for the hot key
-            k_pages, v_pages, tables = paged([k.to(dtype)], [v.to(dtype)], page_size, 3, dtype)
-            q_stride = (heads + 2 * kv_heads) * dim
-            packed = torch.zeros((q_len, q_stride), dtype=dtype)
-            packed[:, :heads * dim] = q.reshape(q_len, -1).to(dtype)
-            batch = FakeBatch([context], [q_len])
-            out = attention_bf16.try_attention(packed.to(DEVICE), q_stride, batch, tables, k_pages, v_pages, heads,
-                                               kv_heads, dim, 1.0, window)
-            last = out[-1].float().cpu().view(heads, dim)[2]
-            target = v.to(dtype).float()[hot, 0]
-            assert torch.allclose(last, target, atol=3e-2) == found, f"q_len {q_len}, hot key {hot}, window {window}"
+    attention_bf16.PREFILL_KERNEL, attention_bf16.FORCE_PAIRING = kernel, pairing
+    try:
+        for q_len in (1, 40) if kernel == "tcgen05" else (40,):
+            for hot, window, found in ((3, 0, True), (255, 0, True), (256, 0, True), (1299 - 40, 0, True),
+                                       (context - 200, 200, True), (context - 201, 200, False)):
+                k = torch.randn((context, kv_heads, dim), generator=torch.Generator().manual_seed(1)) * 0.1
+                v = torch.randn((context, kv_heads, dim), generator=torch.Generator().manual_seed(2))
+                k[hot, 0] = direction * 40.0
+                q = torch.zeros((q_len, heads, dim))
+                q[-1] = direction * 40.0       # the last query looks for the hot key
+                k_pages, v_pages, tables = paged([k.to(dtype)], [v.to(dtype)], page_size, 3, dtype)
+                q_stride = (heads + 2 * kv_heads) * dim
+                packed = torch.zeros((q_len, q_stride), dtype=dtype)
+                packed[:, :heads * dim] = q.reshape(q_len, -1).to(dtype)
+                batch = FakeBatch([context], [q_len])
+                out = attention_bf16.try_attention(packed.to(DEVICE), q_stride, batch, tables, k_pages, v_pages, heads,
+                                                   kv_heads, dim, 1.0, window)
+                last = out[-1].float().cpu().view(heads, dim)[2]
+                target = v.to(dtype).float()[hot, 0]
+                assert torch.allclose(last, target, atol=3e-2) == found, f"q_len {q_len}, hot key {hot}, window {window}"
+    finally:
+        attention_bf16.PREFILL_KERNEL, attention_bf16.FORCE_PAIRING = "tcgen05", None
 
 
 @pytest.mark.parametrize("heads,kv_heads,page_size,window", [(32, 8, 16, None), (4, 4, 8, None), (16, 1, 32, 100),
