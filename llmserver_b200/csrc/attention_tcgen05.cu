@@ -2,7 +2,7 @@
 // S = Q K^T and O += P V are tcgen05.mma instructions whose accumulators live in tensor memory; Q, K and
 // V tiles arrive by TMA (128-byte swizzle); the softmax runs on 128 threads that each own one row.
 //
-// One CTA takes 128 rows of one (sequence, kv head): rows are (token, head of the group) pairs, so the
+// One CTA takes 128 rows (floor(128 / G) tokens x G heads) of one (sequence, kv head): rows are (token, head of the group) pairs, so the
 // G query heads that share a kv head share every K/V tile.  It walks the keys the rows can see in tiles
 // of 64 (whole cache pages), from the first key in the tile's window to the last token's position:
 //
@@ -22,7 +22,7 @@
 // S0 | S1 | O = 64 + 64 + 128 columns; two CTAs fit on an SM (512 columns, 2 x 114 KiB shared memory), so one
 // CTA's softmax overlaps the other's MMAs as well as its own next S tile.
 // Every mbarrier wait is bounded; a wait that runs out sets the error flag, and the CTA still releases its
-// tensor memory.  Takes head_dim 128, groups of 1, 2, 4, 8 or 16 heads, pages of 8, 16, 32 or 64 tokens;
+// tensor memory.  Takes head_dim 128, groups of 1 to 16 heads, pages of 8, 16, 32 or 64 tokens;
 // other sizes use the mma.sync kernel.
 #include "common.cuh"
 #include "tma.cuh"
@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
     int seq = 0, pair = blockIdx.x, first_tile = 0, second_tile = 0;
     for (; seq < p.n_seqs; ++seq) {
         const int q_len = p.q_start[seq + 1] - p.q_start[seq];
-        const int tiles = (q_len == 1 && p.skip_single) ? 0 : (q_len * group + kRows - 1) / kRows;
+        const int tiles = (q_len == 1 && p.skip_single) ? 0 : (q_len + tokens_per_tile - 1) / tokens_per_tile;
         const int pairs = p.pairing ? (tiles + 1) / 2 : tiles;
         if (pair < pairs) {
             first_tile = tiles - 1 - pair;      // heavy tiles first
@@ -129,7 +129,6 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
     const int token0 = p.q_start[seq];
     const int q_len = p.q_start[seq + 1] - token0;
     const int context = p.context_len[seq];
-    const int n_rows = q_len * group;
     const int base_position = context - q_len;
     const int* table = p.block_tables + (size_t)seq * p.max_blocks;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -146,10 +145,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
 
   for (int pass = 0; pass < passes; ++pass) {
     const int tile = pass == 0 ? first_tile : second_tile;
-    const int first_row = tile * kRows;
-    const int first_token = first_row / group;
-    const int last_row = min(first_row + kRows, n_rows) - 1;
-    const int high_key = base_position + last_row / group;
+    const int first_token = tile * tokens_per_tile;
+    const int high_key = base_position + min(first_token + tokens_per_tile, q_len) - 1;
     int low_key = 0;
     if (p.window > 0) low_key = max(0, base_position + first_token - p.window + 1);
     const int first_tile_key = (low_key / kKeys) * kKeys;
@@ -179,7 +176,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
     if (warp == 4) {
         // ---------------------------------------------------------------- producer
         if (lane == 0) {
-            mbar_expect_tx(smem_u32(&q_full), kQBytes);
+            mbar_expect_tx(smem_u32(&q_full), (uint32_t)(tokens_per_tile * group) * (uint32_t)kDim * 2u);
             tma_load_4d(q_smem, &map_q, smem_u32(&q_full), 0, 0, kv_head, token0 + tile * tokens_per_tile);
             tma_load_4d(q_smem + kRows * 128u, &map_q, smem_u32(&q_full), 64, 0, kv_head, token0 + tile * tokens_per_tile);
         }
@@ -265,9 +262,10 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
     } else {
         // ---------------------------------------------------------------- softmax: thread = row
         const int row = warp * 32 + lane;
-        const int r = first_row + row;
-        const bool exists = r < n_rows;
-        const int position = exists ? base_position + r / group : -1;
+        // rows are (token, head of the group) pairs; with a group that does not divide 128 the last rows of a tile are idle
+        const int token = first_token + row / group, head = kv_head * group + row % group;
+        const bool exists = row < tokens_per_tile * group && token < q_len;
+        const int position = exists ? base_position + token : -1;
         const int low = (exists && p.window > 0) ? max(0, position - p.window + 1) : 0;
         const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
         float reference = -INFINITY;     // what is subtracted in the exponent (a stale maximum)
@@ -344,7 +342,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
         fence_after();
         if (!ok) failed = 1;
         const float inverse = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
-        __nv_bfloat16* dst = exists ? p.out + (size_t)(token0 + r / group) * p.n_q_heads * kDim + (size_t)(kv_head * group + r % group) * kDim
+        __nv_bfloat16* dst = exists ? p.out + (size_t)(token0 + token) * p.n_q_heads * kDim + (size_t)head * kDim
                                     : nullptr;
 #pragma unroll
         for (int chunk = 0; chunk < kDim / 32; ++chunk) {
@@ -393,7 +391,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
 LLM_EXPORT int llm_attention_prefill_tcgen05_supports(int head_dim, int n_q_heads, int n_kv_heads, int page_size) {
     if (head_dim != kDim || n_kv_heads <= 0 || n_q_heads % n_kv_heads) return 0;
     const int group = n_q_heads / n_kv_heads;
-    if (group > 16 || (group & (group - 1))) return 0;
+    if (group > 16) return 0;
     return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64;
 }
 

@@ -19,7 +19,7 @@
 // Tensor memory (all 512 columns): S_A | S_B | O_A | O_B, 128 columns each.  S_h(j+1) is issued behind PV_h(j) and the
 // tensor core works in order, so "S_h(j+1) is ready" also says that PV_h(j) has finished with O_h and P_h.
 // Every mbarrier wait is bounded; a wait that runs out sets the error flag, and the CTA still releases its
-// tensor memory.  Takes head_dim 128, groups of 1, 2, 4, 8 or 16 heads, pages of 8 to 128 tokens.
+// tensor memory.  Takes head_dim 128, groups of 1 to 16 heads (floor(128 / G) tokens x G heads per half), pages of 8 to 128 tokens.
 #include "common.cuh"
 #include "tma.cuh"
 #include "tcgen05.cuh"
@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_prefill_wide_kernel(con
     int seq = 0, pair = blockIdx.x, first_tile = 0, second_tile = 0;
     for (; seq < p.n_seqs; ++seq) {
         const int q_len = p.q_start[seq + 1] - p.q_start[seq];
-        const int tiles = (q_len == 1 && p.skip_single) ? 0 : (q_len * group + kRows - 1) / kRows;
+        const int tiles = (q_len == 1 && p.skip_single) ? 0 : (q_len + 2 * tokens_per_half - 1) / (2 * tokens_per_half);
         const int pairs = p.pairing ? (tiles + 1) / 2 : tiles;
         if (pair < pairs) {
             first_tile = tiles - 1 - pair;      // heavy tiles first
@@ -110,7 +110,6 @@ __global__ void __launch_bounds__(kThreads, 1) attention_prefill_wide_kernel(con
     const int token0 = p.q_start[seq];
     const int q_len = p.q_start[seq + 1] - token0;
     const int context = p.context_len[seq];
-    const int n_rows = q_len * group;
     const int base_position = context - q_len;
     const int* table = p.block_tables + (size_t)seq * p.max_blocks;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -127,11 +126,10 @@ __global__ void __launch_bounds__(kThreads, 1) attention_prefill_wide_kernel(con
 
   for (int pass = 0; pass < passes; ++pass) {
     const int tile = pass == 0 ? first_tile : second_tile;
-    const int first_row = tile * kRows;
-    const int first_token = first_row / group;
-    const int rows_here = min(kRows, n_rows - first_row);
-    const bool has_b = rows_here > kHalfRows;
-    const int high_key = base_position + (first_row + rows_here - 1) / group;
+    const int first_token = tile * 2 * tokens_per_half;
+    const int tokens_here = min(2 * tokens_per_half, q_len - first_token);
+    const bool has_b = tokens_here > tokens_per_half;
+    const int high_key = base_position + first_token + tokens_here - 1;
     int low_key = 0;
     if (p.window > 0) low_key = max(0, base_position + first_token - p.window + 1);
     const int first_tile_key = (low_key / kKeys) * kKeys;
@@ -161,7 +159,8 @@ __global__ void __launch_bounds__(kThreads, 1) attention_prefill_wide_kernel(con
         // ---------------------------------------------------------------- producer
         if (lane == 0) {
             const uint32_t bar = smem_u32(&control.q_full);
-            mbar_expect_tx(bar, has_b ? 2 * kQHalfBytes : kQHalfBytes);
+            const uint32_t half_bytes = (uint32_t)(tokens_per_half * group) * (uint32_t)kDim * 2u;
+            mbar_expect_tx(bar, has_b ? 2 * half_bytes : half_bytes);
             for (int h = 0; h < (has_b ? 2 : 1); ++h) {
                 const int token = token0 + first_token + h * tokens_per_half;
                 tma_load_4d(q_smem + h * kQHalfBytes, &map_q, bar, 0, 0, kv_head, token);
@@ -279,9 +278,10 @@ __global__ void __launch_bounds__(kThreads, 1) attention_prefill_wide_kernel(con
         // ---------------------------------------------------------------- softmax: thread = row of its half
         const int h = warp >> 2;
         const int row = (warp & 3) * 32 + lane;
-        const int r = first_row + h * kHalfRows + row;
-        const bool exists = r < n_rows;
-        const int position = exists ? base_position + r / group : -1;
+        // rows are (token, head of the group) pairs; with a group that does not divide 128 the last rows of a half are idle
+        const int token = first_token + h * tokens_per_half + row / group, head = kv_head * group + row % group;
+        const bool exists = row < tokens_per_half * group && token < q_len;
+        const int position = exists ? base_position + token : -1;
         const int low = (exists && p.window > 0) ? max(0, position - p.window + 1) : 0;
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t s_address = lane_base + col_s(h), o_address = lane_base + col_o(h);
@@ -368,7 +368,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_prefill_wide_kernel(con
         fence_after();
         if (!ok) failed = 1;
         const float inverse = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
-        __nv_bfloat16* dst = exists ? p.out + (size_t)(token0 + r / group) * p.n_q_heads * kDim + (size_t)(kv_head * group + r % group) * kDim
+        __nv_bfloat16* dst = exists ? p.out + (size_t)(token0 + token) * p.n_q_heads * kDim + (size_t)head * kDim
                                     : nullptr;
 #pragma unroll
         for (int chunk = 0; chunk < kDim / 32; ++chunk) {
@@ -416,7 +416,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_prefill_wide_kernel(con
 LLM_EXPORT int llm_attention_prefill_wide_supports(int head_dim, int n_q_heads, int n_kv_heads, int page_size) {
     if (head_dim != kDim || n_kv_heads <= 0 || n_q_heads % n_kv_heads) return 0;
     const int group = n_q_heads / n_kv_heads;
-    if (group > 16 || (group & (group - 1))) return 0;
+    if (group > 16) return 0;
     return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
 }
 

@@ -20,10 +20,11 @@ WAVE_BLOCKS = 296   # one wave of two blocks per SM on 148 SMs
 PREFILL_KERNEL = os.environ.get("LLMSERVER_B200_PREFILL_ATTENTION", "tcgen05")
 PREFILL_TILE = 128   # rows per block of the tcgen05 portions kernel
 WIDE_TILE = 256      # rows per block of the 256-row kernel
-# the 256-row kernel is used when the longest portion has this many rows (tokens x heads of a group) and its request
-# holds this many tokens: measured on the 8B head shape, it wins from about there (long key loops, enough row tiles)
+# the 256-row kernel is used when the longest portion has this many rows (tokens x heads of a group), its request
+# holds this many tokens and the group divides 128: measured on the 8B, 14B and 32B head shapes, it wins from about
+# there (long key loops, enough row tiles; 8 % at 16384 tokens, 25 % at 32768), and not with groups of 5
 WIDE_MIN_ROWS = int(os.environ.get("LLMSERVER_B200_PREFILL_WIDE_ROWS", "8192"))
-WIDE_MIN_CONTEXT = int(os.environ.get("LLMSERVER_B200_PREFILL_WIDE_CONTEXT", "8192"))
+WIDE_MIN_CONTEXT = int(os.environ.get("LLMSERVER_B200_PREFILL_WIDE_CONTEXT", "16384"))
 
 
 def prefill_tcgen05_supported(head_dim: int, n_q_heads: int, n_kv_heads: int, page_size: int) -> bool:
@@ -53,7 +54,7 @@ def prefill_wide_wanted(batch, group: int, head_dim: int, n_q_heads: int, n_kv_h
     if PREFILL_KERNEL == "tcgen05-256":
         return True
     length, context = max(zip(batch.q_lens, batch.context_lens))
-    return length * group >= WIDE_MIN_ROWS and context >= WIDE_MIN_CONTEXT
+    return length * group >= WIDE_MIN_ROWS and context >= WIDE_MIN_CONTEXT and PREFILL_TILE % group == 0
 
 
 def supported(head_dim: int, n_q_heads: int, n_kv_heads: int) -> bool:
@@ -130,12 +131,17 @@ def try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_head
         # prompt portions on the tcgen05 kernel (128-row tiles); single tokens, if any, on the decode kernel
         group = n_q_heads // n_kv_heads
         wide = prefill_wide_wanted(batch, group, head_dim, n_q_heads, n_kv_heads, page_size)
-        rows_per_tile = WIDE_TILE if wide else PREFILL_TILE
-        tile_counts = [-(-length * group // rows_per_tile) for length in batch.q_lens if length > 1 or not run_decode]
-        # A block takes a row tile and its mirror image (the light one with the heavy one), which evens out the work of
-        # a causal prompt, unless that leaves SMs without a block: portions over a long context have few, even tiles.
+        # a tile holds whole tokens: floor(128 / group) of them per 128 rows (the 256-row kernel has two such halves)
+        tokens_per_tile = (PREFILL_TILE // group) * (2 if wide else 1)
+        tile_counts = [-(-length // tokens_per_tile) for length in batch.q_lens if length > 1 or not run_decode]
+        # A block takes a row tile and its mirror image (the light one with the heavy one), which gives every block of a
+        # causal prompt the same work, or tiles go out one by one, heaviest first.  Pairs cost whole waves of double
+        # blocks; single tiles fill the GPU more finely but end raggedly (about 1.3 x their mean, measured).
         paired = sum((count + 1) // 2 for count in tile_counts)
-        pairing = paired * n_kv_heads >= (3 * _block_slots(qkv.device, wide)) // 4 if FORCE_PAIRING is None else FORCE_PAIRING
+        slots = _block_slots(qkv.device, wide)
+        cost_paired = 2.0 * -(-paired * n_kv_heads // slots)
+        cost_single = 1.3 * max(sum(tile_counts) * n_kv_heads / slots, 1.0)
+        pairing = cost_paired < cost_single if FORCE_PAIRING is None else FORCE_PAIRING
         call("llm_attention_prefill_wide" if wide else "llm_attention_prefill_tcgen05", qkv.data_ptr(), q_stride, batch.n_tokens,
              k_pages.data_ptr(), v_pages.data_ptr(),
              block_tables.data_ptr(), block_tables.shape[-1], batch.q_start.data_ptr(), batch.context_len.data_ptr(),

@@ -424,11 +424,13 @@ def test_tensor_core_attention_finds_a_far_key_and_respects_the_window_edge(kern
 
 
 @pytest.mark.parametrize("heads,kv_heads,page_size,window", [(32, 8, 16, None), (4, 4, 8, None), (16, 1, 32, 100),
-                                                             (8, 4, 64, None), (8, 1, 16, 300), (2, 1, 16, None)])
+                                                             (8, 4, 64, None), (8, 1, 16, 300), (2, 1, 16, None),
+                                                             (40, 8, 16, None), (3, 1, 16, 100), (12, 2, 32, None), (7, 1, 8, None)])
 def test_attention_prefill_tcgen05(heads, kv_heads, page_size, window):
     """The two tcgen05 / tensor-memory kernels for prompt portions (128 and 256 rows per block; head_dim 128, groups
     of 1 to 16 heads, whole pages per tile): portions that start in the middle of a page and of a tile, more than
-    one row tile, a whole prompt, a portion of two tokens, beside single tokens that go to the decode kernel."""
+    one row tile, a whole prompt, a portion of two tokens, beside single tokens that go to the decode kernel; groups
+    of 5, 3, 6 and 7 heads, which leave the last rows of a tile idle."""
     from llmserver_b200.ops import attention_bf16
     dim, dtype = 128, torch.bfloat16
     assert attention_bf16.prefill_tcgen05_supported(dim, heads, kv_heads, page_size)
