@@ -46,9 +46,10 @@ _ROUNDS = 4
 _empty_round = {}
 # Between two small kernels the candidates often lie within a few percent of each other, and whole steps decide
 # differently from that measurement at the two ends: up to 16 rows a step is faster with this package's kernel
-# wherever the two are close (its weight stream starts before its predecessor ends), from 32 rows on with the
-# library's.  So a candidate of the other kind has to win by this much.
-_CLOSE = 0.05
+# wherever the two are close (its weight stream starts before its predecessor ends, and it lets its successor launch
+# early), from 32 rows on with the library's.  So a candidate of the other kind has to win by this much.
+_CLOSE_FEW_ROWS = 0.10
+_CLOSE_MANY_ROWS = 0.05
 
 
 def _time_in_step(run, device, repeats: int = 3) -> float:
@@ -123,7 +124,8 @@ def _plan_for(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> 
             out.copy_(torch.matmul(x, weight.t()))
 
     favour_library = key[0] > 16
-    best_time, best = _time_in_step(library_product, x.device) * ((1.0 - _CLOSE) if favour_library else (1.0 + _CLOSE)), 0
+    best_time = _time_in_step(library_product, x.device) * ((1.0 - _CLOSE_MANY_ROWS) if favour_library else (1.0 + _CLOSE_FEW_ROWS))
+    best = 0
     tiles, k_blocks = -(-cols // 128), -(-inner // 128)
     for split in SPLITS:
         if split > 1 and (tiles * split > 600 or k_blocks // split < 2):
