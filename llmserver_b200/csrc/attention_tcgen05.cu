@@ -288,13 +288,15 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
             // The maximum is taken over the raw scores (the scale is positive); the scale and the reference enter
             // the exponent in one fused multiply-add.  Eight running maxima and four running sums keep the
             // dependent chains short: with two softmax warps per scheduler, latency is what this loop is bound by.
-            float running[8];
+            // Four running maxima fed two scores at a time, the scale and the reference applied to two scores per
+            // instruction, two pairs of running sums: the softmax warps are bound by instruction issue, so every
+            // halved instruction count shows.
+            float running[4];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) running[c] = __uint_as_float(raw[c]);
+            for (int c = 0; c < 4; ++c) running[c] = fmaxf(__uint_as_float(raw[2 * c]), __uint_as_float(raw[2 * c + 1]));
 #pragma unroll
-            for (int c = 8; c < 64; ++c) running[c & 7] = fmaxf(running[c & 7], __uint_as_float(raw[c]));
-            const float raw_max = fmaxf(fmaxf(fmaxf(running[0], running[1]), fmaxf(running[2], running[3])),
-                                        fmaxf(fmaxf(running[4], running[5]), fmaxf(running[6], running[7])));
+            for (int c = 4; c < 32; ++c) running[c & 3] = max3(running[c & 3], __uint_as_float(raw[2 * c]), __uint_as_float(raw[2 * c + 1]));
+            const float raw_max = fmaxf(fmaxf(running[0], running[1]), fmaxf(running[2], running[3]));
             const float tile_max = raw_max * p.scale_log2;
             // the reference moves only when the maximum has outgrown it by the threshold (or nothing was seen yet)
             float factor = 1.0f;
@@ -303,15 +305,20 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
                 reference = tile_max;
             }
             const float subtract = reference == -INFINITY ? 0.0f : reference;
+            const uint64_t scale_pair = pair_of(p.scale_log2, p.scale_log2), minus_pair = pair_of(-subtract, -subtract);
             float weight[64];
 #pragma unroll
-            for (int c = 0; c < 64; ++c) weight[c] = fmaf(__uint_as_float(raw[c]), p.scale_log2, -subtract);
+            for (int c = 0; c < 32; ++c)
+                halves_of(fma_pair(pair_of(__uint_as_float(raw[2 * c]), __uint_as_float(raw[2 * c + 1])), scale_pair, minus_pair),
+                          weight[2 * c], weight[2 * c + 1]);
 #pragma unroll
             for (int c = 0; c < 64; ++c) weight[c] = exp2_approx(weight[c]);
-            float partial[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            uint64_t sums[2] = {pair_of(0.0f, 0.0f), pair_of(0.0f, 0.0f)};
 #pragma unroll
-            for (int c = 0; c < 64; ++c) partial[c & 3] += weight[c];
-            const float tile_sum = (partial[0] + partial[1]) + (partial[2] + partial[3]);
+            for (int c = 0; c < 32; ++c) sums[c & 1] = add_pair(sums[c & 1], pair_of(weight[2 * c], weight[2 * c + 1]));
+            float sum_low, sum_high;
+            halves_of(add_pair(sums[0], sums[1]), sum_low, sum_high);
+            const float tile_sum = sum_low + sum_high;
             uint32_t packed[32];
 #pragma unroll
             for (int c = 0; c < 32; ++c) packed[c] = pack2(weight[2 * c], weight[2 * c + 1]);      // keys 2c, 2c + 1

@@ -106,6 +106,32 @@ __device__ __forceinline__ float exp2_approx(float x) {
     return y;
 }
 
+// Two-wide 32-bit arithmetic and the three-input maximum of sm_100: half the instructions for the softmax's
+// scaling, sums and maxima (its warps are bound by instruction issue).
+__device__ __forceinline__ uint64_t pair_of(float low, float high) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(low), "f"(high));
+    return r;
+}
+__device__ __forceinline__ void halves_of(uint64_t pair, float& low, float& high) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(low), "=f"(high) : "l"(pair));
+}
+__device__ __forceinline__ uint64_t fma_pair(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add_pair(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 __device__ __forceinline__ uint32_t pack2(float low, float high) {
     __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
     return *reinterpret_cast<uint32_t*>(&pair);
