@@ -445,32 +445,10 @@ LLM_EXPORT int llm_attention_prefill_wide(const void* q, int q_stride, int n_tok
         return LLM_REFUSED;
     }
     CUtensorMap map_q, map_k, map_v;
-    {   // Q as a 4-D tensor (column, head of the group, kv head, token) over the packed projection
-        const cuuint64_t dims[4] = {(cuuint64_t)head_dim, (cuuint64_t)group, (cuuint64_t)n_kv_heads, (cuuint64_t)n_tokens};
-        const cuuint64_t strides[3] = {(cuuint64_t)head_dim * 2, (cuuint64_t)group * head_dim * 2, (cuuint64_t)q_stride * 2};
-        const cuuint32_t box[4] = {64u, (cuuint32_t)group, 1u, (cuuint32_t)(kHalfRows / group)};
-        const cuuint32_t ones[4] = {1, 1, 1, 1};
-        if (encode(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(q), dims, strides, box, ones,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
-            llm_set_error("attention_prefill_wide: cannot describe Q to TMA");
-            return LLM_REFUSED;
-        }
-    }
-    // A page of one kv head, [page_size keys][128 columns], as (64 columns, 8 keys, 2 column halves, page_size / 8 key
-    // groups, page x kv head): one box brings the whole page as 8-key groups of [low half | high half], each half a
-    // 1024-byte swizzle atom, which is the operand layout both MMAs read.
-    for (int which = 0; which < 2; ++which) {
-        const cuuint64_t dims[5] = {64u, 8u, 2u, (cuuint64_t)(page_size / 8), (cuuint64_t)1 << 30};
-        const cuuint64_t strides[4] = {(cuuint64_t)kDim * 2, 128u, (cuuint64_t)8 * kDim * 2, (cuuint64_t)page_size * kDim * 2};
-        const cuuint32_t box[5] = {64u, 8u, 2u, (cuuint32_t)(page_size / 8), 1u};
-        const cuuint32_t ones[5] = {1, 1, 1, 1, 1};
-        if (encode(which ? &map_v : &map_k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(which ? v_pages : k_pages), dims,
-                   strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
-            llm_set_error("attention_prefill_wide: cannot describe the pages to TMA");
-            return LLM_REFUSED;
-        }
+    if (!make_query_map(&map_q, encode, q, q_stride, n_tokens, head_dim, group, n_kv_heads, kHalfRows / group) ||
+        !make_page_map(&map_k, encode, k_pages, page_size) || !make_page_map(&map_v, encode, v_pages, page_size)) {
+        llm_set_error("attention_prefill_wide: cannot describe Q or the cache pages to TMA");
+        return LLM_REFUSED;
     }
     WideParams p;
     p.block_tables = block_tables;

@@ -5,6 +5,8 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 
+#include "tma.cuh"
+
 namespace tc5 {
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
@@ -135,6 +137,35 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 __device__ __forceinline__ uint32_t pack2(float low, float high) {
     __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
     return *reinterpret_cast<uint32_t*>(&pair);
+}
+
+
+// ---- host side: tensor maps of the attention kernels' operands (128-byte swizzle, head_dim 128) --------------------
+
+// Q of the packed projection as a 4-D tensor (column, head of the group, kv head, token); a box is 64 columns of all
+// `group` heads of one kv head for `tokens_per_box` tokens, i.e. tokens_per_box x group rows of 128 bytes.
+inline bool make_query_map(CUtensorMap* map, tma::EncodeTiled encode, const void* q, int q_stride, int n_tokens, int head_dim,
+                           int group, int n_kv_heads, int tokens_per_box) {
+    const cuuint64_t dims[4] = {(cuuint64_t)head_dim, (cuuint64_t)group, (cuuint64_t)n_kv_heads, (cuuint64_t)n_tokens};
+    const cuuint64_t strides[3] = {(cuuint64_t)head_dim * 2, (cuuint64_t)group * head_dim * 2, (cuuint64_t)q_stride * 2};
+    const cuuint32_t box[4] = {64u, (cuuint32_t)group, 1u, (cuuint32_t)tokens_per_box};
+    const cuuint32_t ones[4] = {1, 1, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(q), dims, strides, box, ones,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// A cache page of one kv head, [page_size keys][128 columns], as (64 columns, 8 keys, 2 column halves, page_size / 8 key
+// groups, page x kv head): one box brings the whole page as 8-key groups of [low half | high half], each half a
+// 1024-byte swizzle atom, which is the operand layout both MMAs read.
+inline bool make_page_map(CUtensorMap* map, tma::EncodeTiled encode, const void* pages, int page_size) {
+    const cuuint64_t dims[5] = {64u, 8u, 2u, (cuuint64_t)(page_size / 8), (cuuint64_t)1 << 30};
+    const cuuint64_t strides[4] = {(cuuint64_t)128 * 2, 128u, (cuuint64_t)8 * 128 * 2, (cuuint64_t)page_size * 128 * 2};
+    const cuuint32_t box[5] = {64u, 8u, 2u, (cuuint32_t)(page_size / 8), 1u};
+    const cuuint32_t ones[5] = {1, 1, 1, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(pages), dims, strides, box, ones,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace tc5
