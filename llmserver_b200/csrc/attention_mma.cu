@@ -21,6 +21,8 @@
 // is summed in 32-bit from the unrounded values.
 #include "common.cuh"
 #include "tma.cuh"
+#include "tcgen05.cuh"
+#include <type_traits>
 
 namespace {
 
@@ -114,6 +116,14 @@ template <int D, int ROWS>
 struct TmaLayout {
     static __device__ __forceinline__ int at(int row, int chunk) {
         return (chunk >> 3) * (ROWS * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
+    }
+};
+// PageLayout (head_dim 128): what one 5-D TMA box per cache page writes: groups of 8 keys, each group holding its low
+// 64 columns and then its high 64 columns as 1024-byte swizzle atoms (half as many, twice as large copies as two
+// boxes per page).
+struct PageLayout {
+    static __device__ __forceinline__ int at(int row, int chunk) {
+        return (row >> 3) * 1024 + (chunk >> 3) * 512 + (row & 7) * 64 + (((chunk & 7) ^ (row & 7)) << 3);
     }
 };
 
@@ -515,7 +525,7 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
     __shared__ __align__(8) uint64_t full_bar[kDecodeStages];
     __shared__ __align__(8) uint64_t empty_bar[kDecodeStages];
     __shared__ int failed;
-    using Layout = TmaLayout<D, kTileKeys>;
+    using Layout = typename std::conditional<D == 128, PageLayout, TmaLayout<D, kTileKeys>>::type;
     constexpr int kHalves = D / 64;
     constexpr uint32_t kTileBytes = kTileKeys * D * 2;          // one of K or V
     constexpr uint32_t kStageBytes = 2 * kTileBytes;
@@ -557,9 +567,11 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
         // page_size x 128 bytes; each lane issues one of them.  Every tile is copied whole: pages past the
         // end of the sequence come from whatever the (zero-padded) block table names there, an existing
         // page whose finite contents are masked out, so no row of a stage holds bits that were not loaded.
+        // (head_dim 128: one 5-D box per page and operand instead of one per column half)
+        constexpr int kBoxesPerPage = D == 128 ? 1 : kHalves;
         const int pages_per_tile = kTileKeys / p.page_size;
-        const int copies = pages_per_tile * kHalves * 2;
-        const int my_page = lane / (kHalves * 2), my_half = (lane / 2) % kHalves, my_v = lane & 1;
+        const int copies = pages_per_tile * kBoxesPerPage * 2;
+        const int my_page = lane / (kBoxesPerPage * 2), my_half = (lane / 2) % kBoxesPerPage, my_v = lane & 1;
         for (int t = 0; t < n_tiles; ++t) {
             const int s = t % kDecodeStages;
             bool ok = true;
@@ -575,9 +587,14 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
                 const int key = split_begin + t * kTileKeys + my_page * p.page_size;
                 const int page = table[min(key / p.page_size, p.max_blocks - 1)];
                 const int y = (page * p.n_kv_heads + kv_head) * p.page_size;
-                const uint32_t dst = base + s * kStageBytes + (my_v ? kTileBytes : 0u) + my_half * (kTileKeys * 128u) +
-                                     (uint32_t)(my_page * p.page_size) * 128u;
-                tma::load_2d(dst, my_v ? &map_v : &map_k, bar, my_half * 64, y);
+                if (D == 128) {
+                    const uint32_t dst = base + s * kStageBytes + (my_v ? kTileBytes : 0u) + (uint32_t)(my_page * p.page_size) * 256u;
+                    tc5::tma_load_5d(dst, my_v ? &map_v : &map_k, bar, 0, 0, 0, 0, page * p.n_kv_heads + kv_head);
+                } else {
+                    const uint32_t dst = base + s * kStageBytes + (my_v ? kTileBytes : 0u) + my_half * (kTileKeys * 128u) +
+                                         (uint32_t)(my_page * p.page_size) * 128u;
+                    tma::load_2d(dst, my_v ? &map_v : &map_k, bar, my_half * 64, y);
+                }
             }
         }
         return;
@@ -752,9 +769,16 @@ int launch_decode_tma(const AttnParams& p, cudaStream_t stream) {
     // address generation, so a generous one is fine when the number of pages is not known
     const uint64_t rows = (uint64_t)1 << 30;
     CUtensorMap map_k, map_v;
-    if (!tma::make_map_bf16(&map_k, p.k_pages, rows, D, (uint32_t)p.page_size) ||
-        !tma::make_map_bf16(&map_v, p.v_pages, rows, D, (uint32_t)p.page_size))
-        return launch_decode_cp_async<D>(p, stream);
+    bool described;
+    if (D == 128) {
+        tma::EncodeTiled encode = tma::encode_tiled();
+        described = encode != nullptr && tc5::make_page_map(&map_k, encode, p.k_pages, p.page_size) &&
+                    tc5::make_page_map(&map_v, encode, p.v_pages, p.page_size);
+    } else {
+        described = tma::make_map_bf16(&map_k, p.k_pages, rows, D, (uint32_t)p.page_size) &&
+                    tma::make_map_bf16(&map_v, p.v_pages, rows, D, (uint32_t)p.page_size);
+    }
+    if (!described) return launch_decode_cp_async<D>(p, stream);
     const size_t shared = (size_t)kDecodeStages * 2 * kTileKeys * D * 2 + (size_t)16 * D * 2 + 1024;
     static bool configured = false;
     if (!configured) {
