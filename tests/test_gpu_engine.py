@@ -197,3 +197,35 @@ def test_random_serving_schedule_changes_no_token(tiny_folders):
             pass
         assert requests[index].generated_token_ids == request.generated_token_ids, f"request {index} differs"
         assert len(request.generated_token_ids) == job["new"]
+
+
+def test_random_serving_schedule_in_bfloat16_at_head_dim_128(tiny_folders):
+    """The serving path's own kernels (tcgen05 prompt attention, TMA decode attention, the tcgen05 product for few rows)
+    under a random schedule: requests of random lengths arrive over time into a small cache of two groups (one layer
+    has a window of 150), portions run beside decode tokens, decode steps replay graphs of several buckets, requests
+    are preempted.  Every token must be the plain implementation's choice for its own prefix, within the logit
+    tolerance, greedy and sampled."""
+    import random
+    from llmserver_b200 import Engine
+    folder, vocab = tiny_folders["e"], 333
+    rng = random.Random(11)
+    jobs = [dict(prompt=tokens_for(vocab, rng.randint(1, 260), 700 + index), new=rng.randint(1, 48),
+                 temperature=rng.choice([0.0, 0.0, 0.8]), seed=40 + index, arrives=rng.randint(0, 40)) for index in range(18)]
+    engine = Engine(folder, max_new_tokens=64, max_batch_size=5, max_num_batched_tokens=96, prefill_chunk_size=70,
+                    kv_cache_num_blocks=44, kv_cache_block_size=16, ignore_eos=True, dtype="bfloat16", max_context=320)
+    requests, step = {}, 0
+    while len(requests) < len(jobs) or engine.scheduler.waiting or engine.scheduler.running:
+        for index, job in enumerate(jobs):
+            if index not in requests and job["arrives"] <= step:
+                requests[index] = engine.add_request(prompt_token_ids=job["prompt"], max_new_tokens=job["new"],
+                                                     temperature=job["temperature"], seed=job["seed"])
+        engine.step()
+        step += 1
+        assert step < 5000
+    engine.cache.check_invariants()
+    assert engine.cache.available() == engine.cache.capacity()
+    assert engine.stats["preemptions"] > 0 and engine.step_function.graph_steps > 0
+    for index, job in enumerate(jobs):
+        tokens = requests[index].generated_token_ids
+        assert len(tokens) == job["new"]
+        assert_tokens_are_argmax_of_plain(folder, job["prompt"], tokens, "bfloat16", job["temperature"], job["seed"])
