@@ -10,15 +10,15 @@ What differs by design: one step is ONE forward over decode tokens and prompt po
 (the reference runs them as separate forwards, utils/engine.py:437-443); sampling is a kernel that
 does greedy and seeded temperature sampling (the reference: argmax only, utils/engine.py:295-297).
 
-When pages run out (decided in ``schedule_step``, as utils/engine.py:418-435): the plan is checked
-against the pages available in every cache group; if it does not fit, the running request with the
-fewest preemptions and the least waiting is preempted (its pages freed, itself put at the back of
-the waiting queue, to be recomputed) and planning is repeated; a lone running request that does not
-fit raises ``KVCacheExhaustedError``.
+When pages run out (decided in ``schedule_step``): the plan is checked against the pages available
+in every cache group; if it does not fit, the youngest request in flight is put out (its pages
+freed, itself at the head of the queue, its cache to be rebuilt later) and planning is repeated; a
+lone request that does not fit raises ``KVCacheExhaustedError``.
 """
 from __future__ import annotations
 
 import itertools
+import time
 from typing import Dict, Iterable, List, Optional, Sequence
 
 import torch
@@ -26,7 +26,7 @@ import torch
 from ..cache import CacheManager, KVCacheExhaustedError
 from ..sampling import Sampler, SamplingRow
 from .request import Request, RequestFinishReason, RequestStatus
-from .scheduler import PageBudget, Scheduler, SchedulerOutput
+from .scheduler import PageBudget, Scheduler, StepPlan
 from .step import StepFunction
 
 
@@ -76,7 +76,8 @@ class Engine:
         self.cuda_graphs = (self.device.type == "cuda") if cuda_graphs is None else bool(cuda_graphs)
         if self.cuda_graphs and self.step_function.graphs is None:
             self.step_function.enable_graphs(min(max_context, self.num_blocks * self.block_size), max_batch_size)
-        self.stats = {"steps": 0, "preemptions": 0, "tokens": 0, "prefill_tokens": 0, "decode_tokens": 0, "prefix_tokens": 0}
+        self.stats = {"steps": 0, "preemptions": 0, "tokens": 0, "prefill_tokens": 0, "decode_tokens": 0, "prefix_tokens": 0,
+                      "schedule_s": 0.0, "pack_copy_s": 0.0, "launch_s": 0.0, "read_back_s": 0.0, "accept_s": 0.0, "step_s": 0.0}
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt=None, prompt_token_ids: Optional[Sequence[int]] = None,
@@ -138,75 +139,99 @@ class Engine:
         if not self.cache.prefix_sharing:
             return
         for request in itertools.islice(self.scheduler.waiting, self.scheduler.max_batch_size):
-            request.num_computed_tokens, request.prefix_idle_pages = self.cache.probe_prefix(request.prefill_token_ids)
+            request.num_computed_tokens, request.prefix_idle_pages = self.cache.probe_prefix(request.feed)
 
-    def preempt_request(self, request: Request) -> None:
+    def put_out(self, request: Request) -> None:
+        """Takes a request out of the batch to free its pages; it waits at the head of the queue."""
         self._release(request)
-        self.scheduler.running.remove(request)
-        request.preempt_for_compute()
-        self.scheduler.waiting.append(request)
+        self.scheduler.put_back(request)
         self.stats["preemptions"] += 1
 
-    def schedule_step(self) -> SchedulerOutput:
+    def schedule_step(self) -> StepPlan:
+        """Plans until the plan fits the cache.  When it does not, the youngest request in flight (the one let in
+        last) gives its pages back and waits at the head of the queue; the oldest is never put out while another
+        runs, so it always finishes and the engine cannot turn in circles.  The reference instead picks the request
+        that was put out least and waited least and queues it at the back (utils/engine.py:412-435); with four
+        requests that need most of a small cache each, that rotation puts one request out every step and none of
+        them ever ends."""
         while True:
             self._probe_waiting_prefixes()
-            out = self.scheduler.plan(self.budget)
-            if all(need <= have for need, have in zip(out.pages_needed, self.cache.available())):
-                for request in self.scheduler.commit(out):
-                    covered = self.step_function.admit(request.request_id, request.prefill_token_ids)
+            plan = self.scheduler.plan(self.budget)
+            have = self.cache.available()
+            if all(need <= got for need, got in zip(plan.pages, have)):
+                for request in self.scheduler.commit(plan):
+                    covered = self.step_function.admit(request.request_id, request.feed)
                     request.num_computed_tokens = covered
                     self.stats["prefix_tokens"] += covered
-                return out
-            if len(self.scheduler.running) <= 1:
-                raise KVCacheExhaustedError(f"Required pages {out.pages_needed} exceed the pages available {self.cache.available()}")
-            candidates = [request for request in reversed(self.scheduler.running)
-                          if any(self.cache.table(request.request_id, group) for group in range(len(self.cache.groups)))]
-            if not candidates:
-                raise KVCacheExhaustedError(f"Required pages {out.pages_needed} exceed the pages available {self.cache.available()}")
-            victim = sorted(candidates, key=lambda request: (request.preemption_count, request.waiting_steps))[0]
-            self.preempt_request(victim)
+                return plan
+            holders = [request for request in self.scheduler.running
+                       if any(self.cache.table(request.request_id, group) for group in range(len(self.cache.groups)))]
+            if len(self.scheduler.running) < 2 or not holders:
+                raise KVCacheExhaustedError(f"the step needs {plan.pages} pages per cache group, {have} are available, "
+                                            "and no other request is left to put out")
+            self.put_out(holders[-1])
 
     # ------------------------------------------------------------------ the step
     def step(self) -> bool:
         """Plans and runs one mixed step; returns whether work is left."""
         if not (self.scheduler.waiting or self.scheduler.running):
             return False
-        out = self.schedule_step()
+        clock = time.perf_counter
+        began = clock()
+        plan = self.schedule_step()
         entries, sampled = [], []     # sampled: requests that get a token from this step, in row order
-        for request in out.decode_requests:
-            entries.append((request.request_id, [request.generated_token_ids[-1]], [0]))
-            sampled.append(request)
-        finishing = []
-        for request, count in zip(out.prefill_requests, out.prefill_token_counts):
-            start = request.num_computed_tokens
-            tokens = request.prefill_token_ids[start:start + count]
-            done = start + count == len(request.prefill_token_ids)
-            wants = done and not request.needs_decode_resume   # utils/engine.py:380
-            entries.append((request.request_id, tokens, [count - 1] if wants else []))
+        for share in plan.shares:
+            request = share.request
+            if share.decode:
+                entries.append((request.request_id, request.generated_token_ids[-1:], [0]))
+                sampled.append(request)
+                continue
+            first = request.num_computed_tokens
+            last_portion = share.tokens == request.pending
+            # the end of a rebuilt cache samples nothing: its next token is known (utils/engine.py:380)
+            wants = last_portion and not request.replaying
+            entries.append((request.request_id, request.feed[first:first + share.tokens], [share.tokens - 1] if wants else []))
             if wants:
                 sampled.append(request)
-            finishing.append(done)
         rows = [SamplingRow(request.temperature, request.seed, len(request.generated_token_ids)) for request in sampled]
+        planned = clock()
         tokens = self.step_function.run_and_sample(entries, rows, self.sampler)
-        self.stats["steps"] += 1
-        self.stats["decode_tokens"] += len(out.decode_requests)
-        self.stats["prefill_tokens"] += sum(out.prefill_token_counts)
-        for request in out.decode_requests:
-            request.complete_decode()
-        for request, count, done in zip(out.prefill_requests, out.prefill_token_counts, finishing):
-            old = request.num_computed_tokens
-            request.advance_prefill(count)
-            self.cache.register_prefix(request.request_id, request.prompt_token_ids, old, request.num_computed_tokens)
-            if done:
-                request.complete_prefill()
+        ran = clock()
+        for share in plan.shares:
+            request = share.request
+            before = request.num_computed_tokens
+            request.ran(share.tokens)
+            if not share.decode:
+                self.cache.register_prefix(request.request_id, request.prompt_token_ids, before, request.num_computed_tokens)
         for request, token in zip(sampled, tokens):
             self._accept(request, token)
         self.scheduler.running[:] = [request for request in self.scheduler.running
                                      if request.status not in (RequestStatus.FINISHED, RequestStatus.CANCELLED)]
+        stats, phases = self.stats, self.step_function.last_phases
+        stats["steps"] += 1
+        stats["decode_tokens"] += len(plan.decoding)
+        stats["prefill_tokens"] += sum(share.tokens for share in plan.prompts)
+        done = clock()
+        stats["schedule_s"] += planned - began
+        stats["pack_copy_s"] += phases.get("pack_copy", 0.0)
+        stats["launch_s"] += phases.get("launch", 0.0)
+        stats["read_back_s"] += phases.get("read_back", 0.0)
+        stats["accept_s"] += done - ran
+        stats["step_s"] += done - began
         return bool(self.scheduler.waiting or self.scheduler.running)
 
+    def step_profile(self) -> Dict[str, float]:
+        """Mean host time per step, in milliseconds, by phase (the reference keeps such a record in
+        ``Engine.step_profile``, utils/engine.py:69,446-475): ``schedule`` planning and building the step's
+        entries; ``pack_copy`` page allocation, packing the batch and queueing its copy; ``launch`` issuing the
+        kernels or the graph replay; ``read_back`` waiting for the device and reading the tokens; ``accept``
+        bookkeeping after the step; ``step`` all of it."""
+        steps = max(1, self.stats["steps"])
+        return {name[:-2]: 1e3 * self.stats[name] / steps
+                for name in ("schedule_s", "pack_copy_s", "launch_s", "read_back_s", "accept_s", "step_s")}
+
     def _accept(self, request: Request, token: int) -> None:
-        request.append_generated_token(token)
+        request.take(token)
         self.stats["tokens"] += 1
         if token in self.eos_token_ids and not request.ignore_eos:
             request.finish(RequestFinishReason.EOS)
@@ -216,6 +241,16 @@ class Engine:
             return
         self._release(request)
         self._archive(request)
+
+    # ------------------------------------------------------------------ warm-up
+    def warmup(self, batch_sizes: Optional[Sequence[int]] = None) -> Dict[str, object]:
+        """Before the first request: chooses the variant of every matrix product of a decode step and captures the
+        decode graph of every batch-size bucket up to ``max_batch_size`` (or of the given sizes), so that no later
+        ``step()`` tunes or captures.  The engine must be idle.  The reference's counterpart is
+        ``Engine.warmup_graphs`` (utils/engine.py:150-161)."""
+        if self.scheduler.waiting or self.scheduler.running or self.cache.requests:
+            raise RuntimeError("warmup() needs an idle engine: requests are queued or in flight")
+        return self.step_function.warmup(self.scheduler.max_batch_size, batch_sizes)
 
     # ------------------------------------------------------------------ convenience
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: Optional[int] = None, temperature: float = 0.0,

@@ -1,9 +1,14 @@
-"""A request and its lifecycle: WAITING -> PREFILL -> DECODING -> FINISHED | CANCELLED.
+"""One generation request and where it stands.
 
-Same state machine as the reference (utils/request.py:5-121), for a token-id engine: no text, no
-output queue.  Preemption puts a request back to WAITING with nothing computed; if it had been
-decoding it then prefills ``prompt + generated[:-1]`` and does not sample again at the end, so no
-token is produced twice (utils/request.py:63-75).
+The stations are the reference's (utils/request.py:5-121: waiting, prefill, decoding, finished, cancelled) and so
+are the public names a caller reads (``request_id``, ``prompt_token_ids``, ``generated_token_ids``, ``status``,
+``finish_reason``); it is a token-id request without text or an output queue.  The engine moves a request with four
+calls: ``admit`` when it gets a row of the batch, ``ran`` after a step that fed some of its tokens, ``take`` for a
+sampled token, ``put_out`` when its pages are needed by older requests.
+
+Being put out loses the cache, not the tokens: the request then has to feed ``prompt + generated[:-1]`` again and
+samples nothing at the end of that, because the token that follows is already known, so no token is produced twice
+(the rule of utils/request.py:63-75).
 """
 from __future__ import annotations
 
@@ -28,93 +33,97 @@ class RequestFinishReason(Enum):
 
 
 class RequestStateError(RuntimeError):
-    pass
+    """A request was asked to do something its station does not allow."""
+
+
+_LIVE = (RequestStatus.PREFILL, RequestStatus.DECODING)
+_OVER = (RequestStatus.FINISHED, RequestStatus.CANCELLED)
 
 
 class Request:
     def __init__(self, request_id: str, prompt_token_ids: List[int], max_new_tokens: int, temperature: float = 0.0,
                  seed: int = 0, ignore_eos: bool = False):
-        if not prompt_token_ids:
-            raise ValueError("prompt_token_ids must not be empty")
-        if max_new_tokens <= 0:
-            raise ValueError(f"max_new_tokens is <= 0: {max_new_tokens}")
+        if len(prompt_token_ids) == 0:
+            raise ValueError(f"request {request_id!r} has an empty prompt")
+        if max_new_tokens < 1:
+            raise ValueError(f"request {request_id!r} asks for {max_new_tokens} new tokens; at least one is needed")
         if temperature < 0:
-            raise ValueError(f"temperature must not be negative: {temperature}")
+            raise ValueError(f"request {request_id!r}: a temperature cannot be negative ({temperature})")
         self.request_id = request_id
         self.prompt_token_ids = list(prompt_token_ids)
         self.generated_token_ids: List[int] = []
         self.max_new_tokens = max_new_tokens
-        self.temperature = float(temperature)
-        self.seed = int(seed)
-        self.ignore_eos = ignore_eos
-        self.num_computed_tokens = 0
-        self.prefix_idle_pages = 0     # idle cached pages a shared prefix would take back into use
+        self.temperature, self.seed, self.ignore_eos = float(temperature), int(seed), ignore_eos
         self.status = RequestStatus.WAITING
         self.finish_reason: Optional[RequestFinishReason] = None
+        self.num_computed_tokens = 0      # tokens of ``feed`` whose keys and values are in the cache
+        self.replaying = False            # put out while decoding: the cache is rebuilt, nothing is sampled at its end
+        self.prefix_idle_pages = 0        # idle cached pages a shared prefix would take back into use
+        self.times_put_out = 0
+        self.steps_queued = 0
         self.created_at = time.time()
         self.first_token_at: Optional[float] = None
         self.finished_at: Optional[float] = None
-        self.needs_decode_resume = False
-        self.waiting_steps = 0
-        self.preemption_count = 0
 
+    # ------------------------------------------------------------------ what has to be fed
     @property
-    def prefill_token_ids(self) -> List[int]:
-        if self.needs_decode_resume:
+    def feed(self) -> List[int]:
+        """The tokens whose keys and values must be cached before the next token can be sampled or decoded."""
+        if self.replaying:
             return self.prompt_token_ids + self.generated_token_ids[:-1]
         return self.prompt_token_ids
 
     @property
-    def remaining_prefill(self) -> int:
-        return len(self.prefill_token_ids) - self.num_computed_tokens
+    def pending(self) -> int:
+        return len(self.feed) - self.num_computed_tokens
 
-    def preempt_for_compute(self) -> None:
-        if self.status not in (RequestStatus.PREFILL, RequestStatus.DECODING):
-            raise RequestStateError(f"Request cannot be preempted, current request status is {self.status.value}")
-        self.needs_decode_resume = self.needs_decode_resume or self.status == RequestStatus.DECODING
-        self.status = RequestStatus.WAITING
-        self.num_computed_tokens = 0
-        self.prefix_idle_pages = 0
-        self.preemption_count += 1
+    def _require(self, allowed, doing: str) -> None:
+        if self.status not in allowed:
+            raise RequestStateError(f"request {self.request_id!r} is {self.status.value.lower()}: it cannot {doing}")
 
-    def start_prefill(self) -> None:
-        if self.status != RequestStatus.WAITING:
-            raise RequestStateError(f"Request cannot be put for prefill, current request status is {self.status.value}")
+    # ------------------------------------------------------------------ moves
+    def admit(self) -> None:
+        self._require((RequestStatus.WAITING,), "be admitted")
         self.status = RequestStatus.PREFILL
 
-    def advance_prefill(self, num_tokens: int) -> None:
-        if self.status != RequestStatus.PREFILL:
-            raise RequestStateError(f"Request prefill cannot advance, current request status is {self.status.value}")
-        if num_tokens <= 0 or num_tokens > self.remaining_prefill:
-            raise ValueError(f"Invalid number of prefill tokens: num_tokens: {num_tokens}, remaining_prompt: {self.remaining_prefill}")
-        self.num_computed_tokens += num_tokens
+    def ran(self, count: int) -> None:
+        """A step ran ``count`` more of this request's tokens.  When the last token of ``feed`` is in, the request
+        decodes from then on."""
+        self._require(_LIVE, "run tokens")
+        if self.status is RequestStatus.DECODING:
+            if count != 1:
+                raise ValueError(f"request {self.request_id!r} decodes one token a step, not {count}")
+            self.num_computed_tokens += 1
+            return
+        if not 1 <= count <= self.pending:
+            raise ValueError(f"request {self.request_id!r}: {count} tokens were run, {self.pending} were pending")
+        self.num_computed_tokens += count
+        if self.pending == 0:
+            self.status = RequestStatus.DECODING
+            self.replaying = False
 
-    def complete_prefill(self) -> None:
-        if self.status != RequestStatus.PREFILL:
-            raise RequestStateError(f"Request prefill cannot be completed, current request status is {self.status.value}")
-        if self.remaining_prefill != 0:
-            raise RequestStateError("Request prefill cannot be completed before all prompt tokens are computed: "
-                                    f"num_computed_tokens: {self.num_computed_tokens}, prompt_tokens: {len(self.prefill_token_ids)}")
-        self.status = RequestStatus.DECODING
-        self.needs_decode_resume = False
-
-    def append_generated_token(self, token_id: int) -> None:
-        if self.status != RequestStatus.DECODING:
-            raise RequestStateError(f"Request is not in the decoding stage: current request status is {self.status.value}")
+    def take(self, token_id: int) -> None:
+        """Appends a sampled token."""
+        self._require((RequestStatus.DECODING,), "take a sampled token")
         if self.first_token_at is None:
             self.first_token_at = time.time()
         self.generated_token_ids.append(int(token_id))
 
-    def complete_decode(self) -> None:
-        if self.status != RequestStatus.DECODING:
-            raise RequestStateError(f"Request decoding cannot be completed, it is not in the decoding stage: current request status is {self.status.value}")
-        self.num_computed_tokens += 1
+    def put_out(self) -> None:
+        """Its pages go to others: back to waiting with nothing cached."""
+        self._require(_LIVE, "be put out")
+        if self.status is RequestStatus.DECODING:
+            self.replaying = True
+        self.status = RequestStatus.WAITING
+        self.num_computed_tokens = 0
+        self.prefix_idle_pages = 0
+        self.times_put_out += 1
 
-    def finish(self, finish_reason) -> None:
-        if self.status in (RequestStatus.FINISHED, RequestStatus.CANCELLED):
-            raise RequestStateError(f"Request cannot be finished, it has already been finished or cancelled: current request status is {self.status.value}")
+    def finish(self, reason) -> None:
+        if self.status in _OVER:
+            raise RequestStateError(f"request {self.request_id!r} is over already ({self.status.value.lower()})")
         self.status = RequestStatus.FINISHED
-        self.finish_reason = RequestFinishReason(finish_reason)
+        self.finish_reason = RequestFinishReason(reason)
         self.finished_at = time.time()
 
     def cancel(self) -> None:

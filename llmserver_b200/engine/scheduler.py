@@ -1,36 +1,57 @@
-"""Continuous batching under a token budget.
+"""Continuous batching: who runs how many tokens in the next step.
 
-Policy of the reference's scheduler (utils/scheduler.py:24-65): every decoding request gets one
-token, counted first against the budget; running prefills get min(remaining prompt, chunk size,
-tokens left); then waiting requests are admitted first-in first-out while request slots, tokens and
-cache pages last, keeping one page of headroom per running request, and admission stops at the first
-request that gets nothing.  ``plan`` changes nothing; ``commit`` applies it.
+A step has a budget of tokens, a number of rows (requests in flight) and the cache's pages.  The order of claims is
+the reference's (utils/scheduler.py:24-65): every decoding request first, one token each; then requests that are in
+the middle of their prompt, a portion each; then newcomers from the queue, first come first served, and the first
+newcomer that cannot be given anything ends the admission, so nobody overtakes.  ``plan`` only reads; ``commit``
+moves the newcomers into the batch.
 
-Unlike the reference, whose engine runs decode rows and prompt chunks as separate forwards
-(utils/engine.py:437-443), one plan becomes ONE mixed step.  Pages are counted per cache group, so a
-plan fits only if it fits every group.
+What is this engine's own:
+
+* a plan is ONE step: decode tokens and prompt portions run in the same forward (the reference runs two,
+  utils/engine.py:437-443);
+* pages are counted per cache group, and a plan must fit every group;
+* a newcomer is taken only if the pages of *everything it still has to feed* are available beyond one spare page
+  per request in flight, although it may then be fed in portions.  A request that is let in on a part of its prompt
+  and cannot go on holds pages that older requests need, is put out, comes back and is put out again; asking for
+  the whole prompt's pages at the door avoids most of that.
 """
 from __future__ import annotations
 
 from collections import deque
-from typing import List
+from dataclasses import dataclass, field
+from typing import Deque, List
 
 from ..cache import KVCacheExhaustedError
 from .request import Request, RequestStatus
 
 
-class SchedulerOutput:
-    def __init__(self):
-        self.num_admitted_requests = 0
-        self.prefill_requests: List[Request] = []
-        self.prefill_token_counts: List[int] = []
-        self.decode_requests: List[Request] = []
-        self.num_scheduled_tokens = 0
-        self.pages_needed: List[int] = []     # per cache group
+@dataclass
+class Share:
+    """One request's part of a step."""
+    request: Request
+    tokens: int              # how many of its tokens the step runs
+    decode: bool = False     # the one token is the request's last sampled token; else a portion of what it has to feed
+    newcomer: bool = False   # comes from the queue with this plan
+
+
+@dataclass
+class StepPlan:
+    shares: List[Share] = field(default_factory=list)
+    pages: List[int] = field(default_factory=list)     # per cache group: pages the step has to allocate
+    tokens: int = 0
 
     @property
-    def empty(self) -> bool:
-        return not self.prefill_requests and not self.decode_requests
+    def decoding(self) -> List[Share]:
+        return [share for share in self.shares if share.decode]
+
+    @property
+    def prompts(self) -> List[Share]:
+        return [share for share in self.shares if not share.decode]
+
+    @property
+    def newcomers(self) -> int:
+        return sum(1 for share in self.shares if share.newcomer)
 
 
 class PageBudget:
@@ -50,81 +71,89 @@ class PageBudget:
 
 class Scheduler:
     def __init__(self, max_batch_size: int, max_num_batched_tokens: int, prefill_chunk_size: int = None):
-        if max_batch_size <= 0:
-            raise ValueError(f"max_batch_size must be positive: {max_batch_size}")
-        if max_num_batched_tokens <= 0:
-            raise ValueError(f"max_num_batched_tokens must be positive: {max_num_batched_tokens}")
+        if max_batch_size < 1:
+            raise ValueError(f"a batch needs at least one row (max_batch_size={max_batch_size})")
         if max_num_batched_tokens < max_batch_size:
-            raise ValueError(f"max_num_batched_tokens must be >= max_batch_size: max_num_batched_tokens: {max_num_batched_tokens}, max_batch_size: {max_batch_size}")
-        if prefill_chunk_size is None:
-            prefill_chunk_size = max_num_batched_tokens
-        if prefill_chunk_size <= 0:
-            raise ValueError(f"prefill_chunk_size must be positive: {prefill_chunk_size}")
-        self.max_batch_size = max_batch_size
-        self.max_num_batched_tokens = max_num_batched_tokens
-        self.prefill_chunk_size = prefill_chunk_size
-        self.waiting: deque = deque()
-        self.running: List[Request] = []
+            raise ValueError(f"a step of {max_num_batched_tokens} tokens cannot give each of {max_batch_size} rows its "
+                             "decode token; raise max_num_batched_tokens or lower max_batch_size")
+        portion = max_num_batched_tokens if prefill_chunk_size is None else prefill_chunk_size
+        if portion < 1:
+            raise ValueError(f"prompt portions need at least one token (prefill_chunk_size={prefill_chunk_size})")
+        self.max_batch_size, self.max_num_batched_tokens, self.prefill_chunk_size = max_batch_size, max_num_batched_tokens, portion
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []      # in the order they were let in: the last is the youngest
 
-    def plan(self, budget: PageBudget) -> SchedulerOutput:
-        out = SchedulerOutput()
-        page_size = budget.page_size
-        free = budget.available()
-        n_groups = len(free)
-        needed_total = [0] * n_groups
-        available_slots = self.max_batch_size - len(self.running)
-        out.decode_requests = [request for request in self.running if request.status == RequestStatus.DECODING]
-        remaining_tokens = self.max_num_batched_tokens - len(out.decode_requests)
+    def plan(self, budget: PageBudget) -> StepPlan:
+        plan = StepPlan()
+        left = budget.available()
+        plan.pages = [0] * len(left)
+        tokens_left = self.max_num_batched_tokens
+
+        def claim(share: Share, pages: List[int]) -> None:
+            nonlocal tokens_left
+            plan.shares.append(share)
+            tokens_left -= share.tokens
+            for group, count in enumerate(pages):
+                left[group] -= count
+                plan.pages[group] += count
+
+        # 1. requests in flight: decode tokens are set apart first, then the prompts go on
+        in_prompt = []
         for request in self.running:
-            needed = [0] * n_groups
-            if request.status == RequestStatus.PREFILL:
-                chunk = min(request.remaining_prefill, self.prefill_chunk_size, remaining_tokens)
-                if chunk > 0:
-                    needed = budget.needed(request, request.num_computed_tokens + chunk)
-                    out.prefill_requests.append(request)
-                    out.prefill_token_counts.append(chunk)
-                    remaining_tokens -= chunk
-            elif request.status == RequestStatus.DECODING:
-                needed = budget.needed(request, request.num_computed_tokens + 1)
-            free = [a - b for a, b in zip(free, needed)]
-            needed_total = [a + b for a, b in zip(needed_total, needed)]
-        reserved = len(self.running)   # one page of headroom per running request (utils/scheduler.py:43,50)
-        index = 0
-        while index < len(self.waiting) and available_slots > 0 and remaining_tokens > 0:
-            request = self.waiting[index]
-            if request.remaining_prefill <= 0:
-                raise ValueError(f"No prompt tokens remain to prefill: request_id: {request.request_id}, num_computed_tokens: {request.num_computed_tokens}")
-            spare = min(free) - reserved if free else 1 << 30
-            # pages a shared prefix already covers cost nothing; count only what lies beyond it
-            covered_pages = request.num_computed_tokens // page_size
-            fitting = max(0, spare - request.prefix_idle_pages) * page_size - (request.num_computed_tokens - covered_pages * page_size)
-            chunk = min(request.remaining_prefill, self.prefill_chunk_size, remaining_tokens, max(0, fitting))
-            if chunk == 0:
-                break
-            # cached pages that are idle now stop being available once the request takes them
-            pages = -(-(request.num_computed_tokens + chunk) // page_size) - covered_pages + request.prefix_idle_pages
-            out.prefill_requests.append(request)
-            out.prefill_token_counts.append(chunk)
-            free = [a - pages for a in free]
-            needed_total = [a + pages for a in needed_total]
-            available_slots -= 1
-            remaining_tokens -= chunk
-            index += 1
-        out.num_admitted_requests = index
-        out.num_scheduled_tokens = self.max_num_batched_tokens - remaining_tokens
-        out.pages_needed = needed_total
-        if self.waiting and out.empty:
-            raise KVCacheExhaustedError("No request can fit into the KV cache")
-        return out
+            if request.status is RequestStatus.DECODING:
+                claim(Share(request, 1, decode=True), budget.needed(request, request.num_computed_tokens + 1))
+            elif request.status is RequestStatus.PREFILL:
+                in_prompt.append(request)
+        page = budget.page_size
+        promised = 0       # pages that prompts in flight will still ask for after this step
+        for request in in_prompt:
+            portion = min(request.pending, self.prefill_chunk_size, tokens_left)
+            if portion > 0:
+                claim(Share(request, portion), budget.needed(request, request.num_computed_tokens + portion))
+            promised += -(-len(request.feed) // page) - -(-(request.num_computed_tokens + portion) // page)
 
-    def commit(self, out: SchedulerOutput) -> List[Request]:
-        """Moves the admitted requests from waiting to running; returns them."""
-        admitted = []
-        for _ in range(out.num_admitted_requests):
-            request = self.waiting.popleft()
-            request.start_prefill()
-            self.running.append(request)
-            admitted.append(request)
+        # 2. the queue, in order, while rows, tokens and pages last
+        rows_left = self.max_batch_size - len(self.running)
+        spare_kept = len(self.running)        # a page per request in flight stays free for its next tokens
         for request in self.waiting:
-            request.waiting_steps += 1
-        return admitted
+            if rows_left == 0 or tokens_left == 0:
+                break
+            if request.pending < 1:
+                raise ValueError(f"request {request.request_id!r} waits with nothing left to feed")
+            # pages of a shared prefix cost nothing, except those that are idle now and stop being available
+            covered = request.num_computed_tokens // page
+            whole = -(-len(request.feed) // page) - covered + request.prefix_idle_pages
+            if left and whole > min(left) - promised - spare_kept:
+                break
+            portion = min(request.pending, self.prefill_chunk_size, tokens_left)
+            now = -(-(request.num_computed_tokens + portion) // page) - covered + request.prefix_idle_pages
+            claim(Share(request, portion, newcomer=True), [now] * len(left))
+            promised += whole - now
+            rows_left -= 1
+            spare_kept += 1
+        plan.tokens = self.max_num_batched_tokens - tokens_left
+        if not plan.shares and self.waiting:
+            raise KVCacheExhaustedError(f"the cache cannot hold request {self.waiting[0].request_id!r} "
+                                        f"({len(self.waiting[0].feed)} tokens to feed) even with nothing else in flight")
+        return plan
+
+    def commit(self, plan: StepPlan) -> List[Request]:
+        """Lets the plan's newcomers in (they leave the queue in order); returns them."""
+        let_in = []
+        for share in plan.shares:
+            if share.newcomer:
+                request = self.waiting.popleft()
+                if request is not share.request:
+                    raise RuntimeError("the queue changed between plan and commit")
+                request.admit()
+                self.running.append(request)
+                let_in.append(request)
+        for request in self.waiting:
+            request.steps_queued += 1
+        return let_in
+
+    def put_back(self, request: Request) -> None:
+        """A request that was put out returns to the head of the queue: it is older than anything that waits."""
+        self.running.remove(request)
+        request.put_out()
+        self.waiting.appendleft(request)

@@ -26,102 +26,130 @@ def test_constructor_checks():
     assert Scheduler(2, 8).prefill_chunk_size == 8
 
 
+def names(shares):
+    return [share.request.request_id for share in shares]
+
+
 def test_admission_is_fifo_under_the_token_budget_and_plan_is_pure():
     scheduler = Scheduler(max_batch_size=3, max_num_batched_tokens=10, prefill_chunk_size=6)
     a, b, c = make_request("a", 5), make_request("b", 9), make_request("c", 2)
     scheduler.waiting.extend([a, b, c])
     pages = budget()
-    out = scheduler.plan(pages)
-    assert [r.request_id for r in out.prefill_requests] == ["a", "b"] and out.prefill_token_counts == [5, 5]
-    assert out.num_admitted_requests == 2 and out.num_scheduled_tokens == 10
+    plan = scheduler.plan(pages)
+    assert names(plan.prompts) == ["a", "b"] and [share.tokens for share in plan.shares] == [5, 5]
+    assert plan.newcomers == 2 and plan.tokens == 10 and not plan.decoding
     assert len(scheduler.waiting) == 3 and not scheduler.running      # nothing changed yet
-    assert scheduler.plan(pages).prefill_token_counts == [5, 5]
-    admitted = scheduler.commit(out)
-    assert [r.request_id for r in admitted] == ["a", "b"] and c.waiting_steps == 1
+    assert [share.tokens for share in scheduler.plan(pages).shares] == [5, 5]
+    admitted = scheduler.commit(plan)
+    assert [r.request_id for r in admitted] == ["a", "b"] and c.steps_queued == 1
     assert a.status == RequestStatus.PREFILL and list(scheduler.waiting) == [c]
 
 
 def test_decode_tokens_are_counted_first_and_running_prefills_go_on():
     scheduler = Scheduler(max_batch_size=4, max_num_batched_tokens=8, prefill_chunk_size=8)
     pages = budget()
-    decoding, prefilling = make_request("d", 3), make_request("p", 20)
-    for request in (decoding, prefilling):
+    prefilling, decoding = make_request("p", 20), make_request("d", 3)
+    for request in (prefilling, decoding):
         pages.cache.admit(request.request_id)
-        request.start_prefill()
-    decoding.advance_prefill(3)
-    decoding.complete_prefill()
-    decoding.append_generated_token(7)
-    prefilling.advance_prefill(6)
-    scheduler.running.extend([decoding, prefilling])
+        request.admit()
+    decoding.ran(3)
+    decoding.take(7)
+    prefilling.ran(6)
+    scheduler.running.extend([prefilling, decoding])     # the prompt is older, the decode token still comes first
     scheduler.waiting.append(make_request("w", 9))
-    out = scheduler.plan(pages)
-    assert out.decode_requests == [decoding]
-    assert out.prefill_requests[0] is prefilling and out.prefill_token_counts[0] == 7     # 8 - 1 decode token
-    assert out.num_admitted_requests == 0                                                  # no tokens left
-    assert out.pages_needed == [1 + 4]     # decode: position 3 opens page 0; prefill to 13 tokens: 4 pages
+    plan = scheduler.plan(pages)
+    assert names(plan.shares) == ["d", "p"] and plan.shares[0].decode and not plan.shares[1].decode
+    assert plan.shares[1].tokens == 7                       # 8 - 1 decode token
+    assert plan.newcomers == 0                              # no tokens left
+    assert plan.pages == [1 + 4]     # decode: position 3 opens page 0; prefill to 13 tokens: 4 pages
 
 
-def test_admission_respects_free_pages_with_headroom_and_stops_at_the_first_misfit():
-    scheduler = Scheduler(max_batch_size=4, max_num_batched_tokens=64)
-    pages = budget(pages=6, page_size=4)
-    running = make_request("r", 4)
-    pages.cache.admit("r")
-    pages.cache.ensure("r", 4)
-    running.start_prefill()
-    running.advance_prefill(4)
-    running.complete_prefill()
-    running.append_generated_token(1)
-    scheduler.running.append(running)
+def running_decoder(pages, name="r", length=4):
+    request = make_request(name, length)
+    pages.cache.admit(name)
+    pages.cache.ensure(name, length)
+    request.admit()
+    request.ran(length)
+    request.take(1)
+    return request
+
+
+def test_a_newcomer_needs_room_for_its_whole_prompt_and_nobody_overtakes():
+    scheduler = Scheduler(max_batch_size=4, max_num_batched_tokens=64, prefill_chunk_size=8)
+    pages = budget(pages=8, page_size=4)
+    scheduler.running.append(running_decoder(pages))
     big, small = make_request("big", 30), make_request("small", 2)
     scheduler.waiting.extend([big, small])
-    out = scheduler.plan(pages)
-    # 5 pages free, the decode takes 1, one is kept as headroom for the running request: 3 pages = 12 tokens
-    assert out.prefill_requests == [big] and out.prefill_token_counts == [12]
-    # nothing fits: a request behind the first misfit is not taken ahead of it
-    pages = budget(pages=2, page_size=4)
-    pages.cache.admit("r")
-    pages.cache.ensure("r", 4)
-    out = scheduler.plan(pages)
-    assert out.prefill_requests == [] and out.decode_requests == [running]
+    # 7 pages free, the decode takes 1, one stays spare for the running request: 5 pages, the prompt needs 8
+    plan = scheduler.plan(pages)
+    assert names(plan.shares) == ["r"] and plan.newcomers == 0      # "small" would fit but does not overtake
+    # with room for all of it, the prompt is let in and fed in portions
+    scheduler.waiting.popleft()
+    fits = make_request("fits", 20)
+    scheduler.waiting.appendleft(fits)
+    plan = scheduler.plan(pages)
+    assert names(plan.shares) == ["r", "fits"] and plan.shares[1].tokens == 8 and plan.shares[1].newcomer
+    assert plan.pages == [1 + 2]          # only the first portion's pages are taken now
+    # "small" is not taken: after "fits" two requests are in flight, and 6 - 5 pages do not leave a spare one each
+    assert plan.newcomers == 1
 
 
 def test_nothing_schedulable_raises():
     scheduler = Scheduler(2, 8)
     scheduler.waiting.append(make_request("a", 5))
     pages = budget(pages=1, page_size=4)
-    pages.cache.admit("x")
-    pages.cache.ensure("x", 4)
     with pytest.raises(KVCacheExhaustedError):
         scheduler.plan(pages)
+
+
+def test_put_back_queues_at_the_head():
+    scheduler = Scheduler(4, 16)
+    pages = budget()
+    old, young = running_decoder(pages, "old"), running_decoder(pages, "young")
+    scheduler.running.extend([old, young])
+    scheduler.waiting.append(make_request("w", 3))
+    scheduler.put_back(young)
+    assert names([type("S", (), {"request": r}) for r in scheduler.waiting]) == ["young", "w"]
+    assert scheduler.running == [old] and young.status == RequestStatus.WAITING and young.replaying
 
 
 def test_request_state_machine():
     request = make_request("a", 3, max_new=2)
     with pytest.raises(RequestStateError):
-        request.advance_prefill(1)
-    request.start_prefill()
-    with pytest.raises(ValueError):
-        request.advance_prefill(4)
-    request.advance_prefill(2)
+        request.ran(1)
+    request.admit()
     with pytest.raises(RequestStateError):
-        request.complete_prefill()
-    request.advance_prefill(1)
-    request.complete_prefill()
-    request.append_generated_token(9)
-    request.complete_decode()
-    request.append_generated_token(8)
-    request.preempt_for_compute()
-    assert request.status == RequestStatus.WAITING and request.needs_decode_resume and request.num_computed_tokens == 0
-    assert request.prefill_token_ids == [1, 2, 3, 9]          # the last generated token is fed by the next decode
-    request.start_prefill()
-    request.advance_prefill(4)
-    request.complete_prefill()
-    assert not request.needs_decode_resume
+        request.admit()
+    with pytest.raises(ValueError):
+        request.ran(4)
+    request.ran(2)
+    assert request.status == RequestStatus.PREFILL and request.pending == 1
+    with pytest.raises(RequestStateError):
+        request.take(9)
+    request.ran(1)
+    assert request.status == RequestStatus.DECODING
+    request.take(9)
+    request.ran(1)
+    with pytest.raises(ValueError):
+        request.ran(2)
+    request.take(8)
+    request.put_out()
+    assert request.status == RequestStatus.WAITING and request.replaying and request.num_computed_tokens == 0
+    assert request.feed == [1, 2, 3, 9]          # the last generated token is fed by the next decode
+    request.admit()
+    request.ran(4)
+    assert request.status == RequestStatus.DECODING and not request.replaying
     request.finish(RequestFinishReason.LENGTH)
     with pytest.raises(RequestStateError):
         request.finish(RequestFinishReason.EOS)
     with pytest.raises(ValueError):
         Request("b", [], 1)
+    # put out in the middle of its prompt: nothing was sampled, nothing is replayed
+    early = make_request("e", 6)
+    early.admit()
+    early.ran(4)
+    early.put_out()
+    assert not early.replaying and early.feed == early.prompt_token_ids and early.pending == 6
 
 
 def engine_with(pages, page_size=4, **kwargs):
@@ -144,14 +172,35 @@ def test_engine_mixes_prompt_portions_and_decode_tokens_in_one_step():
 
 
 def test_engine_preempts_when_pages_run_out_and_resumes_without_duplicate_tokens():
-    # 5 pages of 4 tokens: three requests that grow to 5 + 12 tokens each cannot all stay
+    # 7 pages of 4 tokens: three requests that grow to 5 + 12 tokens each cannot all stay
     engine = engine_with(pages=7, max_new_tokens=12, max_batch_size=3)
     prompts = [[1, 2, 3, 4, 5], [9, 8, 7, 6, 5], [20, 21, 22, 23, 24]]
-    outputs = engine.generate(prompts)
+    requests = [engine.add_request(prompt_token_ids=prompt) for prompt in prompts]
+    while engine.step():
+        pass
     assert engine.stats["preemptions"] > 0
-    assert outputs == [expected_generation(prompt, 12) for prompt in prompts]
+    assert [request.generated_token_ids for request in requests] == [expected_generation(prompt, 12) for prompt in prompts]
+    # the oldest request is never the one that is put out, and finishes first
+    assert requests[0].times_put_out == 0 and requests[1].times_put_out + requests[2].times_put_out > 0
+    assert requests[0].finished_at <= requests[1].finished_at <= requests[2].finished_at
     engine.cache.check_invariants()
     assert engine.cache.available() == [7]
+
+
+def test_requests_that_each_need_most_of_the_cache_all_finish():
+    """Four requests that need 7 of 8 pages each: only one can be in its last tokens at a time.  A policy that takes
+    turns in putting requests out (fewest times put out first) ends none of them; putting out the youngest ends them
+    one after the other."""
+    engine = engine_with(pages=8, max_new_tokens=16, max_batch_size=4, max_num_batched_tokens=24)
+    prompts = [[index + 1] * 11 for index in range(4)]
+    requests = [engine.add_request(prompt_token_ids=prompt) for prompt in prompts]
+    steps = 0
+    while engine.step():
+        steps += 1
+        assert steps < 400, "the engine turns in circles"
+    assert [request.generated_token_ids for request in requests] == [expected_generation(prompt, 16) for prompt in prompts]
+    assert engine.stats["tokens"] == 64
+    engine.cache.check_invariants()
 
 
 def test_a_lone_request_that_does_not_fit_raises():
