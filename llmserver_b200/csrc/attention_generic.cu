@@ -21,7 +21,8 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, int q_stride, 
                                          const T* __restrict__ v_pages, const int* __restrict__ block_tables,
                                          int max_blocks, const int* __restrict__ seq_of_token,
                                          const int* __restrict__ positions, T* __restrict__ out, int n_q_heads,
-                                         int n_kv_heads, int head_dim, int page_size, float scale, int window) {
+                                         int n_kv_heads, int head_dim, int page_size, int num_pages, float scale,
+                                         int window, int* __restrict__ error_flag) {
     pdl_trigger();   // let the next kernel start launching
     pdl_wait();      // everything before this kernel in the stream is complete and visible
     extern __shared__ float q_shared[];  // [warps][head_dim]
@@ -51,7 +52,11 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, int q_stride, 
         long long offset = 0;  // element offset of this lane's key (and value) row inside the pages
         float score = -INFINITY;
         if (valid) {
-            const int page = table[key / page_size];
+            int page = table[key / page_size];
+            if ((unsigned)page >= (unsigned)num_pages) {      // no page of the pool: report it, read page 0 instead
+                if (error_flag) atomicExch(error_flag, 5);
+                page = 0;
+            }
             offset = (((long long)page * n_kv_heads + kv_head) * page_size + key % page_size) * head_dim;
             const T* k_row = k_pages + offset;
             float dot = 0.0f;
@@ -90,11 +95,15 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, int q_stride, 
 LLM_EXPORT int llm_attention_generic(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                                      const int* block_tables, int max_blocks, const int* seq_of_token,
                                      const int* positions, void* out, int n_tokens, int n_q_heads, int n_kv_heads,
-                                     int head_dim, int page_size, float scale, int window, int dtype,
-                                     cudaStream_t stream) {
+                                     int head_dim, int page_size, int num_pages, float scale, int window,
+                                     int* error_flag, int dtype, cudaStream_t stream) {
     if (n_tokens == 0) return LLM_OK;
     if (head_dim > ATTN_MAX_D || head_dim <= 0) {
         llm_set_error("attention_generic: head_dim %d is outside 1..%d", head_dim, ATTN_MAX_D);
+        return LLM_REFUSED;
+    }
+    if (num_pages <= 0) {
+        llm_set_error("attention_generic: the page pool has %d pages", num_pages);
         return LLM_REFUSED;
     }
     if (n_kv_heads <= 0 || n_q_heads % n_kv_heads) {
@@ -107,6 +116,6 @@ LLM_EXPORT int llm_attention_generic(const void* q, int q_stride, const void* k_
     LLM_DISPATCH_DTYPE(dtype, (llm_launch(attention_generic_kernel<T>, grid, warps * 32, shared, stream, 
                                   (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_tables,
                                   max_blocks, seq_of_token, positions, (T*)out, n_q_heads, n_kv_heads, head_dim,
-                                  page_size, scale, window)));
+                                  page_size, num_pages, scale, window, error_flag)));
     return llm_check_launch("attention_generic");
 }

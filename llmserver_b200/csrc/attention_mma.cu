@@ -38,6 +38,7 @@ struct AttnParams {
     const __nv_bfloat16* v_pages;
     const int* block_tables;
     int max_blocks;
+    int num_pages;           // pages in the pool: block-table entries outside 0 .. num_pages - 1 are not followed
     const int* q_start;      // [S + 1]
     const int* context_len;  // [S]
     __nv_bfloat16* out;      // [N, Hq * D]
@@ -49,8 +50,18 @@ struct AttnParams {
     int max_splits;
     float* partial_out;      // [N, Hq, max_splits, D]
     float* partial_ml;       // [N, Hq, max_splits, 2]
-    int* error_flag;         // set when a bounded wait of the TMA decode kernel runs out (may be null)
+    int slot_by_seq;         // scratch slots are counted by sequence instead of by the sequence's token index
+    int* error_flag;         // 3: a bounded wait of the TMA decode kernel ran out; 5: a block-table entry names no page
+                             // of the pool; 6: a context needs more splits than max_splits (may be null)
 };
+
+// A block-table entry as the kernels may follow it: an entry that names no page of the pool is reported and replaced
+// by page 0, so nothing outside the pool is ever addressed (the keys it stands for are wrong, and the flag says so).
+__device__ __forceinline__ int checked_page(const AttnParams& p, int page) {
+    if ((unsigned)page < (unsigned)p.num_pages) return page;
+    if (p.error_flag) atomicExch(p.error_flag, 5);
+    return 0;
+}
 
 // Keys per split of a sequence that sees `span` keys: the fixed length, or (split_len < 0) the span divided into
 // -split_len equal parts, in whole tiles and no shorter than three tiles.  With equal parts every sequence of a
@@ -144,7 +155,7 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_tile, __nv_bfloat1
         const bool valid = key < end_key;
         size_t offset = 0;
         if (valid) {
-            const int page = table[key / p.page_size];
+            const int page = checked_page(p, table[key / p.page_size]);
             offset = (((size_t)page * p.n_kv_heads + kv_head) * p.page_size + key % p.page_size) * D + chunk * 8;
         }
         const int destination = swizzled<D>(row, chunk);
@@ -376,6 +387,13 @@ __global__ void __launch_bounds__(kThreads) attention_portions_kernel(const Attn
 // ------------------------------------------------------------------------------------------------
 // decode: one token per sequence, keys split across blocks
 // ------------------------------------------------------------------------------------------------
+// A decode row whose sequence holds no token (context_len <= 0) has nothing to attend to: its output is zero.
+template <int D>
+__device__ __forceinline__ void zero_output(const AttnParams& p, int token, int kv_head, int group) {
+    for (int index = threadIdx.x; index < group * D; index += blockDim.x)
+        p.out[(size_t)token * p.n_q_heads * D + (size_t)(kv_head * group) * D + index] = __float2bfloat16_rn(0.0f);
+}
+
 template <int D>
 __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnParams p) {
     pdl_trigger();   // let the next kernel start launching
@@ -394,6 +412,8 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnPa
     const int first_key = (low_key / kTileKeys) * kTileKeys;
     const int split_len = split_length(p, context - first_key);
     const int n_splits = (context - first_key + split_len - 1) / split_len;
+    if (n_splits > p.max_splits && split == 0 && kv_head == 0 && threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 6);
+    if (context <= 0 && split == 0) zero_output<D>(p, token, kv_head, group);     // nothing to attend to
     if (split >= n_splits) return;
     const int split_begin = first_key + split * split_len;
     const int split_end = min(split_begin + split_len, context);
@@ -495,7 +515,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnPa
         if (n_splits == 1) {
             p.out[(size_t)token * p.n_q_heads * D + (size_t)head * D + d] = __float2bfloat16_rn(numerator / denominator);
         } else {
-            const size_t slot = ((size_t)token * p.n_q_heads + head) * p.max_splits + split;
+            const size_t slot = ((size_t)(p.slot_by_seq ? seq : token) * p.n_q_heads + head) * p.max_splits + split;
             p.partial_out[slot * D + d] = numerator / denominator;
             if (d == 0) {
                 p.partial_ml[slot * 2] = best;
@@ -545,6 +565,8 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
     const int first_key = (low_key / kTileKeys) * kTileKeys;
     const int split_len = split_length(p, context - first_key);
     const int n_splits = (context - first_key + split_len - 1) / split_len;
+    if (n_splits > p.max_splits && split == 0 && kv_head == 0 && threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 6);
+    if (context <= 0 && split == 0) zero_output<D>(p, token, kv_head, group);     // nothing to attend to
     if (split >= n_splits) return;
     const int split_begin = first_key + split * split_len;
     const int split_end = min(split_begin + split_len, context);
@@ -585,7 +607,9 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
             __syncwarp();
             if (lane < copies) {
                 const int key = split_begin + t * kTileKeys + my_page * p.page_size;
+                // an entry that names no page of the pool lies outside the tensor map's extent and is copied as zeros
                 const int page = table[min(key / p.page_size, p.max_blocks - 1)];
+                if ((unsigned)page >= (unsigned)p.num_pages && p.error_flag) atomicExch(p.error_flag, 5);
                 const int y = (page * p.n_kv_heads + kv_head) * p.page_size;
                 if (D == 128) {
                     const uint32_t dst = base + s * kStageBytes + (my_v ? kTileBytes : 0u) + (uint32_t)(my_page * p.page_size) * 256u;
@@ -689,7 +713,7 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
         if (n_splits == 1) {
             p.out[(size_t)token * p.n_q_heads * D + (size_t)head * D + d] = __float2bfloat16_rn(numerator / denominator);
         } else {
-            const size_t slot = ((size_t)token * p.n_q_heads + head) * p.max_splits + split;
+            const size_t slot = ((size_t)(p.slot_by_seq ? seq : token) * p.n_q_heads + head) * p.max_splits + split;
             p.partial_out[slot * D + d] = numerator / denominator;
             if (d == 0) {
                 p.partial_ml[slot * 2] = best;
@@ -711,9 +735,9 @@ __global__ void attention_decode_merge_kernel(const AttnParams p) {
     const int low_key = p.window > 0 ? max(0, context - p.window) : 0;
     const int first_key = (low_key / kTileKeys) * kTileKeys;
     const int split_len = split_length(p, context - first_key);
-    const int n_splits = (context - first_key + split_len - 1) / split_len;
+    const int n_splits = min((context - first_key + split_len - 1) / split_len, p.max_splits);
     if (n_splits <= 1) return;
-    const size_t slot0 = ((size_t)token * p.n_q_heads + head) * p.max_splits;
+    const size_t slot0 = ((size_t)(p.slot_by_seq ? seq : token) * p.n_q_heads + head) * p.max_splits;
     float best = -INFINITY;
     for (int s = 0; s < n_splits; ++s) best = fmaxf(best, p.partial_ml[(slot0 + s) * 2]);
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
@@ -730,15 +754,7 @@ __global__ void attention_decode_merge_kernel(const AttnParams p) {
 template <int D>
 int launch_portions(const AttnParams& p, int total_tiles, cudaStream_t stream) {
     const size_t shared = (size_t)(kTileRows * D + 4 * kTileKeys * D) * sizeof(__nv_bfloat16);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t status = cudaFuncSetAttribute(attention_portions_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-        if (status != cudaSuccess) {
-            llm_set_error("attention_portions: cannot get %zu bytes of shared memory: %s", shared, cudaGetErrorString(status));
-            return (int)status;
-        }
-        configured = true;
-    }
+    if (int limit_status = llm_raise_shared_limit(reinterpret_cast<const void*>(attention_portions_kernel<D>), shared, "attention_portions")) return limit_status;
     dim3 grid(total_tiles, p.n_kv_heads);
     llm_launch(attention_portions_kernel<D>, grid, kThreads, shared, stream, p);
     return llm_check_launch("attention_portions");
@@ -749,15 +765,7 @@ int launch_decode_cp_async(const AttnParams& p, cudaStream_t stream) {
     size_t shared = (size_t)(16 * D + 4 * kTileKeys * D) * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)4 * 16 * (D + 2) * sizeof(float) + 16 * D * sizeof(__nv_bfloat16);
     if (merge > shared) shared = merge;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t status = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-        if (status != cudaSuccess) {
-            llm_set_error("attention_decode: cannot get %zu bytes of shared memory: %s", shared, cudaGetErrorString(status));
-            return (int)status;
-        }
-        configured = true;
-    }
+    if (int limit_status = llm_raise_shared_limit(reinterpret_cast<const void*>(attention_decode_kernel<D>), shared, "attention_decode")) return limit_status;
     dim3 grid(p.max_splits, p.n_kv_heads, p.n_seqs);
     llm_launch(attention_decode_kernel<D>, grid, kThreads, shared, stream, p);
     return llm_check_launch("attention_decode");
@@ -765,30 +773,22 @@ int launch_decode_cp_async(const AttnParams& p, cudaStream_t stream) {
 
 template <int D>
 int launch_decode_tma(const AttnParams& p, cudaStream_t stream) {
-    // rows of the page pool seen as a [pages * kv_heads * page_size, D] matrix; the extent only bounds
-    // address generation, so a generous one is fine when the number of pages is not known
-    const uint64_t rows = (uint64_t)1 << 30;
+    // rows of the page pool seen as a [pages * kv_heads * page_size, D] matrix: the real extent, so that a block-table
+    // entry that names no page of the pool is copied as zeros and nothing outside the pool is read
+    const uint64_t rows = (uint64_t)p.num_pages * p.n_kv_heads * p.page_size;
     CUtensorMap map_k, map_v;
     bool described;
     if (D == 128) {
         tma::EncodeTiled encode = tma::encode_tiled();
-        described = encode != nullptr && tc5::make_page_map(&map_k, encode, p.k_pages, p.page_size) &&
-                    tc5::make_page_map(&map_v, encode, p.v_pages, p.page_size);
+        described = encode != nullptr && tc5::make_page_map(&map_k, encode, p.k_pages, p.page_size, (long long)p.num_pages * p.n_kv_heads) &&
+                    tc5::make_page_map(&map_v, encode, p.v_pages, p.page_size, (long long)p.num_pages * p.n_kv_heads);
     } else {
         described = tma::make_map_bf16(&map_k, p.k_pages, rows, D, (uint32_t)p.page_size) &&
                     tma::make_map_bf16(&map_v, p.v_pages, rows, D, (uint32_t)p.page_size);
     }
     if (!described) return launch_decode_cp_async<D>(p, stream);
     const size_t shared = (size_t)kDecodeStages * 2 * kTileKeys * D * 2 + (size_t)16 * D * 2 + 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t status = cudaFuncSetAttribute(attention_decode_tma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-        if (status != cudaSuccess) {
-            llm_set_error("attention_decode_tma: cannot get %zu bytes of shared memory: %s", shared, cudaGetErrorString(status));
-            return (int)status;
-        }
-        configured = true;
-    }
+    if (int limit_status = llm_raise_shared_limit(reinterpret_cast<const void*>(attention_decode_tma_kernel<D>), shared, "attention_decode_tma")) return limit_status;
     dim3 grid(p.max_splits, p.n_kv_heads, p.n_seqs);
     llm_launch(attention_decode_tma_kernel<D>, grid, kDecodeThreads, shared, stream, map_k, map_v, p);
     return llm_check_launch("attention_decode_tma");
@@ -820,7 +820,7 @@ LLM_EXPORT int llm_attention_mma_supports(int head_dim, int n_q_heads, int n_kv_
 LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                                  const int* block_tables, int max_blocks, const int* q_start, const int* context_len,
                                  void* out, int n_seqs, int n_q_heads, int n_kv_heads, int head_dim, int page_size,
-                                 float scale, int window, int run_portions, int total_tiles, int run_decode,
+                                 int num_pages, float scale, int window, int run_portions, int total_tiles, int run_decode,
                                  int split_len, int max_splits, float* partial_out, float* partial_ml,
                                  int* error_flag, cudaStream_t stream) {
     if (!llm_attention_mma_supports(head_dim, n_q_heads, n_kv_heads)) {
@@ -836,6 +836,10 @@ LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, const void* k_page
         llm_set_error("attention_mma: at most 65535 sequences per launch, got %d", n_seqs);
         return LLM_REFUSED;
     }
+    if (num_pages <= 0) {
+        llm_set_error("attention_mma: the page pool has %d pages", num_pages);
+        return LLM_REFUSED;
+    }
     AttnParams p;
     p.q = (const __nv_bfloat16*)q;
     p.q_stride = q_stride;
@@ -843,6 +847,8 @@ LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, const void* k_page
     p.v_pages = (const __nv_bfloat16*)v_pages;
     p.block_tables = block_tables;
     p.max_blocks = max_blocks;
+    p.num_pages = num_pages;
+    p.slot_by_seq = 0;
     p.q_start = q_start;
     p.context_len = context_len;
     p.out = (__nv_bfloat16*)out;
@@ -873,19 +879,32 @@ LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, const void* k_page
 #include "attention_noalloc.h"
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[LLM_NOALLOC_SCRATCH_BYTES];
+// What the kernels of the last call reported (0: nothing); see llm_attention_decode_noalloc_status.
+static __device__ int g_noalloc_status;
 
 namespace {
 constexpr int kMaxDevices = 64;
-// Device address of g_noalloc_scratch per device.  In host code the array's name is only a handle for
-// cudaGetSymbolAddress; the kernels must be given the address that call returns.
+// Device addresses of g_noalloc_scratch and g_noalloc_status per device.  In host code the names are only
+// handles for cudaGetSymbolAddress; the kernels must be given the addresses that call returns.
 float* g_noalloc_address[kMaxDevices] = {};
+int* g_noalloc_status_address[kMaxDevices] = {};
+
+int noalloc_device(const char* what) {
+    int device = 0;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status != cudaSuccess || device < 0 || device >= kMaxDevices) {
+        llm_set_error("%s: cannot tell the current device: %s", what, cudaGetErrorString(status));
+        return -1;
+    }
+    return device;
+}
 }  // namespace
 
 LLM_EXPORT int llm_attention_decode_noalloc(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                                             const int* block_tables, int max_blocks, const int* q_start,
                                             const int* context_len, void* out, int n_seqs, int n_q_heads,
-                                            int n_kv_heads, int head_dim, int page_size, float scale, int window,
-                                            int split_len, int max_splits, cudaStream_t stream) {
+                                            int n_kv_heads, int head_dim, int page_size, int num_pages, float scale,
+                                            int window, int split_len, int max_splits, cudaStream_t stream) {
     if (n_seqs <= 0) return LLM_OK;
     if (!llm_attention_mma_supports(head_dim, n_q_heads, n_kv_heads)) {
         llm_set_error("attention_decode_noalloc: head_dim %d with %d/%d heads is not supported (head_dim 64 or 128, group <= 16)",
@@ -901,6 +920,10 @@ LLM_EXPORT int llm_attention_decode_noalloc(const void* q, int q_stride, const v
         llm_set_error("attention_decode_noalloc: at most 65535 sequences per call, got %d", n_seqs);
         return LLM_REFUSED;
     }
+    if (num_pages <= 0) {
+        llm_set_error("attention_decode_noalloc: the page pool has %d pages", num_pages);
+        return LLM_REFUSED;
+    }
     const size_t slots = (size_t)n_seqs * n_q_heads * max_splits;
     const size_t needed = slots * (size_t)(head_dim + 2) * sizeof(float);
     if (needed > LLM_NOALLOC_SCRATCH_BYTES) {
@@ -909,20 +932,25 @@ LLM_EXPORT int llm_attention_decode_noalloc(const void* q, int q_stride, const v
                       n_seqs, n_q_heads, max_splits, needed, (unsigned)LLM_NOALLOC_SCRATCH_BYTES);
         return LLM_REFUSED;
     }
-    int device = 0;
-    cudaError_t status = cudaGetDevice(&device);
-    if (status != cudaSuccess || device < 0 || device >= kMaxDevices) {
-        llm_set_error("attention_decode_noalloc: cannot tell the current device: %s", cudaGetErrorString(status));
-        return status != cudaSuccess ? (int)status : LLM_REFUSED;
-    }
+    const int device = noalloc_device("attention_decode_noalloc");
+    if (device < 0) return LLM_REFUSED;
     if (g_noalloc_address[device] == nullptr) {   // first call on this device
         void* address = nullptr;
-        status = cudaGetSymbolAddress(&address, g_noalloc_scratch);
-        if (status != cudaSuccess || address == nullptr) {
+        void* status_address = nullptr;
+        cudaError_t status = cudaGetSymbolAddress(&address, g_noalloc_scratch);
+        if (status == cudaSuccess) status = cudaGetSymbolAddress(&status_address, g_noalloc_status);
+        if (status != cudaSuccess || address == nullptr || status_address == nullptr) {
             llm_set_error("attention_decode_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(status));
             return status != cudaSuccess ? (int)status : LLM_REFUSED;
         }
+        g_noalloc_status_address[device] = static_cast<int*>(status_address);
         g_noalloc_address[device] = static_cast<float*>(address);
+    }
+    // the status word starts every call at zero (ordered on the caller's stream, like the kernels)
+    cudaError_t cleared = cudaMemsetAsync(g_noalloc_status_address[device], 0, sizeof(int), stream);
+    if (cleared != cudaSuccess) {
+        llm_set_error("attention_decode_noalloc: cannot clear the status word: %s", cudaGetErrorString(cleared));
+        return (int)cleared;
     }
     AttnParams p;
     p.q = (const __nv_bfloat16*)q;
@@ -931,6 +959,8 @@ LLM_EXPORT int llm_attention_decode_noalloc(const void* q, int q_stride, const v
     p.v_pages = (const __nv_bfloat16*)v_pages;
     p.block_tables = block_tables;
     p.max_blocks = max_blocks;
+    p.num_pages = num_pages;
+    p.slot_by_seq = 1;      // the size check above counts sequences, whatever q_start holds
     p.q_start = q_start;
     p.context_len = context_len;
     p.out = (__nv_bfloat16*)out;
@@ -945,6 +975,24 @@ LLM_EXPORT int llm_attention_decode_noalloc(const void* q, int q_stride, const v
     p.max_splits = max_splits;
     p.partial_out = g_noalloc_address[device];                       // [slots][head_dim]
     p.partial_ml = g_noalloc_address[device] + slots * head_dim;      // [slots][2]
-    p.error_flag = nullptr;
+    p.error_flag = g_noalloc_status_address[device];
     return head_dim == 128 ? launch_decode<128>(p, stream) : launch_decode<64>(p, stream);
+}
+
+// What the kernels of the most recent llm_attention_decode_noalloc call on the current device reported, after
+// waiting for `stream`: 0 nothing; 3 a bounded wait on a copy ran out; 5 a block-table entry named no page of the
+// pool (its keys were read as zeros or from page 0); 6 a context needed more splits than max_splits (its last keys
+// were left out).  With any code but 0 the call's output is not valid.  Negative: a CUDA error (llm_last_error).
+LLM_EXPORT int llm_attention_decode_noalloc_status(cudaStream_t stream) {
+    const int device = noalloc_device("attention_decode_noalloc_status");
+    if (device < 0) return LLM_REFUSED;
+    if (g_noalloc_status_address[device] == nullptr) return 0;      // no call yet on this device
+    int value = 0;
+    cudaError_t status = cudaMemcpyAsync(&value, g_noalloc_status_address[device], sizeof(int), cudaMemcpyDeviceToHost, stream);
+    if (status == cudaSuccess) status = cudaStreamSynchronize(stream);
+    if (status != cudaSuccess) {
+        llm_set_error("attention_decode_noalloc_status: %s", cudaGetErrorString(status));
+        return -(int)status;
+    }
+    return value;
 }

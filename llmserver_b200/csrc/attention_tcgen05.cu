@@ -58,6 +58,7 @@ static_assert(kTileBytes + kControlBytes <= kSharedBytes, "shared memory layout"
 struct PrefillParams {
     const int* block_tables;
     int max_blocks;
+    int num_pages;       // block-table entries outside 0 .. num_pages - 1 lie outside the tensor maps and read as zeros
     const int* q_start;
     const int* context_len;
     __nv_bfloat16* out;
@@ -198,6 +199,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_prefill_tcgen05_kernel(
                         // table names (an existing page with finite contents, masked out below)
                         const int key = first_tile_key + t * kKeys + my_page * p.page_size;
                         const int page = table[min(key / p.page_size, p.max_blocks - 1)];
+                        if ((unsigned)page >= (unsigned)p.num_pages && p.error_flag) atomicExch(p.error_flag, 5);
                         const uint32_t offset = s * kKVBytes + (uint32_t)(my_page * p.page_size) * 256u;
                         tma_load_5d(k_smem + offset, &map_k, smem_u32(&k_full[s]), 0, 0, 0, 0, page * p.n_kv_heads + kv_head);
                     }
@@ -407,9 +409,13 @@ LLM_EXPORT int llm_attention_prefill_tcgen05_supports(int head_dim, int n_q_head
 LLM_EXPORT int llm_attention_prefill_tcgen05(const void* q, int q_stride, int n_tokens, const void* k_pages, const void* v_pages,
                                              const int* block_tables, int max_blocks, const int* q_start,
                                              const int* context_len, void* out, int n_seqs, int n_q_heads, int n_kv_heads,
-                                             int head_dim, int page_size, float scale, int window, int skip_single, int pairing,
+                                             int head_dim, int page_size, int num_pages, float scale, int window, int skip_single, int pairing,
                                              int total_pairs, int* error_flag, cudaStream_t stream) {
     if (total_pairs <= 0) return LLM_OK;
+    if (num_pages <= 0) {
+        llm_set_error("attention_prefill_tcgen05: the page pool has %d pages", num_pages);
+        return LLM_REFUSED;
+    }
     if (!llm_attention_prefill_tcgen05_supports(head_dim, n_q_heads, n_kv_heads, page_size) || !aligned16(q) || q_stride % 8 ||
         !(scale > 0.0f)) {
         llm_set_error("attention_prefill_tcgen05: unsupported sizes (head_dim %d, %d/%d heads, page %d)", head_dim, n_q_heads,
@@ -428,13 +434,15 @@ LLM_EXPORT int llm_attention_prefill_tcgen05(const void* q, int q_stride, int n_
     }
     CUtensorMap map_q, map_k, map_v;
     if (!make_query_map(&map_q, encode, q, q_stride, n_tokens, head_dim, group, n_kv_heads, kRows / group) ||
-        !make_page_map(&map_k, encode, k_pages, page_size) || !make_page_map(&map_v, encode, v_pages, page_size)) {
+        !make_page_map(&map_k, encode, k_pages, page_size, (long long)num_pages * n_kv_heads) ||
+        !make_page_map(&map_v, encode, v_pages, page_size, (long long)num_pages * n_kv_heads)) {
         llm_set_error("attention_prefill_tcgen05: cannot describe Q or the cache pages to TMA");
         return LLM_REFUSED;
     }
     PrefillParams p;
     p.block_tables = block_tables;
     p.max_blocks = max_blocks;
+    p.num_pages = num_pages;
     p.q_start = q_start;
     p.context_len = context_len;
     p.out = (__nv_bfloat16*)out;
@@ -448,16 +456,7 @@ LLM_EXPORT int llm_attention_prefill_tcgen05(const void* q, int q_stride, int n_
     p.pairing = pairing;
     p.error_flag = error_flag;
     const size_t shared = kSharedBytes;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t status = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-        if (status != cudaSuccess) {
-            llm_set_error("attention_prefill_tcgen05: cannot get %zu bytes of shared memory: %s", shared, cudaGetErrorString(status));
-            return (int)status;
-        }
-        cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        configured = true;
-    }
+    if (int limit_status = llm_raise_shared_limit(reinterpret_cast<const void*>(attention_prefill_tcgen05_kernel), shared, "attention_prefill_tcgen05", true)) return limit_status;
     dim3 grid(total_pairs, n_kv_heads);
     llm_launch(attention_prefill_tcgen05_kernel, grid, kThreads, shared, stream, map_q, map_k, map_v, p);
     return llm_check_launch("attention_prefill_tcgen05");

@@ -63,6 +63,7 @@ static_assert(sizeof(Control) <= kControlBytes, "control block");
 struct WideParams {
     const int* block_tables;
     int max_blocks;
+    int num_pages;       // block-table entries outside 0 .. num_pages - 1 lie outside the tensor maps and read as zeros
     const int* q_start;
     const int* context_len;
     __nv_bfloat16* out;
@@ -184,6 +185,7 @@ __global__ void __launch_bounds__(kThreads, 1) attention_prefill_wide_kernel(con
                         // table names (an existing page with finite contents, masked out below)
                         const int key = first_tile_key + t * kKeys + lane * p.page_size;
                         const int page = table[min(key / p.page_size, p.max_blocks - 1)];
+                        if ((unsigned)page >= (unsigned)p.num_pages && p.error_flag) atomicExch(p.error_flag, 5);
                         tma_load_5d(k_smem + s * kKVBytes + (uint32_t)(lane * p.page_size) * 256u, &map_k,
                                     smem_u32(&control.k_full[s]), 0, 0, 0, 0, page * p.n_kv_heads + kv_head);
                     }
@@ -424,10 +426,13 @@ LLM_EXPORT int llm_attention_prefill_wide_supports(int head_dim, int n_q_heads, 
 // (each CTA takes a 256-row tile and its mirror, which evens out the work of a causal prompt); without, one CTA per tile; sequences of one token are skipped when skip_single is set (the decode kernel takes them).
 LLM_EXPORT int llm_attention_prefill_wide(const void* q, int q_stride, int n_tokens, const void* k_pages, const void* v_pages,
                                           const int* block_tables, int max_blocks, const int* q_start, const int* context_len,
-                                          void* out, int n_seqs, int n_q_heads, int n_kv_heads, int head_dim, int page_size,
-                                          float scale, int window, int skip_single, int pairing, int total_pairs, int* error_flag,
+                                          void* out, int n_seqs, int n_q_heads, int n_kv_heads, int head_dim, int page_size, int num_pages, float scale, int window, int skip_single, int pairing, int total_pairs, int* error_flag,
                                           cudaStream_t stream) {
     if (total_pairs <= 0) return LLM_OK;
+    if (num_pages <= 0) {
+        llm_set_error("attention_prefill_wide: the page pool has %d pages", num_pages);
+        return LLM_REFUSED;
+    }
     if (!llm_attention_prefill_wide_supports(head_dim, n_q_heads, n_kv_heads, page_size) || !aligned16(q) || q_stride % 8 ||
         !(scale > 0.0f)) {
         llm_set_error("attention_prefill_wide: unsupported sizes (head_dim %d, %d/%d heads, page %d)", head_dim, n_q_heads,
@@ -446,13 +451,15 @@ LLM_EXPORT int llm_attention_prefill_wide(const void* q, int q_stride, int n_tok
     }
     CUtensorMap map_q, map_k, map_v;
     if (!make_query_map(&map_q, encode, q, q_stride, n_tokens, head_dim, group, n_kv_heads, kHalfRows / group) ||
-        !make_page_map(&map_k, encode, k_pages, page_size) || !make_page_map(&map_v, encode, v_pages, page_size)) {
+        !make_page_map(&map_k, encode, k_pages, page_size, (long long)num_pages * n_kv_heads) ||
+        !make_page_map(&map_v, encode, v_pages, page_size, (long long)num_pages * n_kv_heads)) {
         llm_set_error("attention_prefill_wide: cannot describe Q or the cache pages to TMA");
         return LLM_REFUSED;
     }
     WideParams p;
     p.block_tables = block_tables;
     p.max_blocks = max_blocks;
+    p.num_pages = num_pages;
     p.q_start = q_start;
     p.context_len = context_len;
     p.out = (__nv_bfloat16*)out;
@@ -465,15 +472,7 @@ LLM_EXPORT int llm_attention_prefill_wide(const void* q, int q_stride, int n_tok
     p.skip_single = skip_single;
     p.pairing = pairing;
     p.error_flag = error_flag;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t status = cudaFuncSetAttribute(attention_prefill_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSharedBytes);
-        if (status != cudaSuccess) {
-            llm_set_error("attention_prefill_wide: cannot get %u bytes of shared memory: %s", kSharedBytes, cudaGetErrorString(status));
-            return (int)status;
-        }
-        configured = true;
-    }
+    if (int limit_status = llm_raise_shared_limit(reinterpret_cast<const void*>(attention_prefill_wide_kernel), kSharedBytes, "attention_prefill_wide")) return limit_status;
     dim3 grid(total_pairs, n_kv_heads);
     llm_launch(attention_prefill_wide_kernel, grid, kThreads, kSharedBytes, stream, map_q, map_k, map_v, p);
     return llm_check_launch("attention_prefill_wide");

@@ -27,6 +27,11 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 
 bool llm_pdl_enabled();
 
+// Raises a kernel's dynamic shared-memory limit to `bytes` on the current device, once per (kernel, device); with
+// `max_carveout` the kernel also asks for the largest shared-memory carve-out.  Returns LLM_OK or a CUDA error (with
+// the message recorded).
+int llm_raise_shared_limit(const void* kernel, size_t bytes, const char* what, bool max_carveout = false);
+
 // Launches `kernel` on `stream` with programmatic stream serialization (unless switched off with
 // LLMSERVER_B200_PDL=0).  Every kernel launched this way begins with pdl_trigger(); pdl_wait();
 template <typename... Params, typename... Args>

@@ -356,15 +356,7 @@ LLM_EXPORT int llm_gemm_small_m(const void* x, const void* w, void* out, int m, 
         llm_set_error("gemm_small_m: cuTensorMapEncodeTiled failed (m %d, n %d, k %d)", m, n, k);
         return LLM_REFUSED;
     }
-    static size_t configured = 0;
-    if (shared > configured) {
-        cudaError_t status = cudaFuncSetAttribute(gemm_small_m_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(226 * 1024));
-        if (status != cudaSuccess) {
-            llm_set_error("gemm_small_m: cannot raise the shared-memory limit: %s", cudaGetErrorString(status));
-            return (int)status;
-        }
-        configured = 226 * 1024;
-    }
+    if (int limit_status = llm_raise_shared_limit(reinterpret_cast<const void*>(gemm_small_m_kernel), (size_t)226 * 1024, "gemm_small_m")) return limit_status;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)(tiles * split), 1, 1);
     config.blockDim = dim3(kThreads, 1, 1);

@@ -158,8 +158,10 @@ inline bool make_query_map(CUtensorMap* map, tma::EncodeTiled encode, const void
 // A cache page of one kv head, [page_size keys][128 columns], as (64 columns, 8 keys, 2 column halves, page_size / 8 key
 // groups, page x kv head): one box brings the whole page as 8-key groups of [low half | high half], each half a
 // 1024-byte swizzle atom, which is the operand layout both MMAs read.
-inline bool make_page_map(CUtensorMap* map, tma::EncodeTiled encode, const void* pages, int page_size) {
-    const cuuint64_t dims[5] = {64u, 8u, 2u, (cuuint64_t)(page_size / 8), (cuuint64_t)1 << 30};
+// `page_heads` = pages of the pool x kv heads is the real extent: a box named by a block-table entry that is no page of
+// the pool reads zeros instead of memory outside the allocation.
+inline bool make_page_map(CUtensorMap* map, tma::EncodeTiled encode, const void* pages, int page_size, long long page_heads) {
+    const cuuint64_t dims[5] = {64u, 8u, 2u, (cuuint64_t)(page_size / 8), (cuuint64_t)page_heads};
     const cuuint64_t strides[4] = {(cuuint64_t)128 * 2, 128u, (cuuint64_t)8 * 128 * 2, (cuuint64_t)page_size * 128 * 2};
     const cuuint32_t box[5] = {64u, 8u, 2u, (cuuint32_t)(page_size / 8), 1u};
     const cuuint32_t ones[5] = {1, 1, 1, 1, 1};

@@ -135,7 +135,8 @@ def pack(slices: List[SequenceSlice], layout: BatchLayout, host: np.ndarray, voc
             if pages.size > width:
                 raise ValueError(f"request {piece.request_id!r} holds {pages.size} pages; the batch has room for {width}")
             begin = table_offset + row * width
-            # released pages (negative entries) are never read; they become page 0 on the device
+            # pages a window has given back (negative entries) become page 0 on the device: the attention kernels
+            # still load the tile such an entry lies in when the window starts inside it, and mask those keys
             host[begin:begin + pages.size] = np.maximum(pages, 0)
     host[off["q_start"]:off["q_start"] + len(q_start)] = q_start
     if sampling is not None:

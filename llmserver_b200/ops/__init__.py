@@ -12,7 +12,7 @@ from typing import Optional
 import torch
 
 from .library import (KernelError, call, check, declare, dtype_code, launch_count, library, pointer,
-                      require_device, stream_handle)
+                      require_device, stream_handle, wait_error_flag)
 
 __all__ = ["KernelError", "embedding", "add_rmsnorm", "rmsnorm", "silu_mul", "sample", "qk_norm_rope_kv_write",
            "attention_generic", "gemm_f32", "linear", "require_device", "library", "launch_count"]
@@ -152,9 +152,11 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k
 def attention_generic(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
                       block_tables: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor,
                       n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0,
-                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      out: Optional[torch.Tensor] = None, error_flag: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal (optionally windowed) attention of every token over its sequence's pages, 32-bit
-    arithmetic.  ``q`` holds head h of token n at q[n * q_stride + h * D]; returns [N, Hq * D]."""
+    arithmetic.  ``q`` holds head h of token n at q[n * q_stride + h * D]; returns [N, Hq * D].  A block-table entry
+    that names no page of the pool is not followed: page 0 is read instead and ``error_flag`` (default: the device's
+    shared flag) is set to 5."""
     check(q, "q")
     tokens = positions.numel()
     check(k_pages, "k pages", q.dtype, head_dim)
@@ -167,8 +169,9 @@ def attention_generic(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_p
     check(out, "attention output", q.dtype, n_q_heads * head_dim)
     call("llm_attention_generic", q.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(),
          block_tables.data_ptr(), block_tables.shape[-1], seq_of_token.data_ptr(), positions.data_ptr(),
-         out.data_ptr(), tokens, n_q_heads, n_kv_heads, head_dim, k_pages.shape[2], float(scale), int(window),
-         dtype_code(q.dtype), stream_handle())
+         out.data_ptr(), tokens, n_q_heads, n_kv_heads, head_dim, k_pages.shape[2], k_pages.shape[0], float(scale),
+         int(window), (error_flag if error_flag is not None else wait_error_flag(q.device)).data_ptr(), dtype_code(q.dtype),
+         stream_handle())
     return out
 
 

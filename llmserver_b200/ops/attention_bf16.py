@@ -12,7 +12,7 @@ from .library import call, check, library, stream_handle, wait_error_flag
 
 TILE = 64          # rows per block of the portions kernel, keys per tile of both kernels
 MIN_SPLIT = 192    # fewest keys one decode block walks
-WAVE_BLOCKS = 296   # one wave of two blocks per SM on 148 SMs
+DECODE_BLOCKS_PER_SM = 2    # blocks of the decode kernel an SM holds at a time (shared memory)
 
 
 # "tcgen05": the 256-row kernel for long portions and the 128-row kernel otherwise; "tcgen05-128" / "tcgen05-256":
@@ -36,12 +36,16 @@ FORCE_PAIRING = None     # True / False: tests set it to run both ways of handin
 _SM_COUNT = {}
 
 
-def _block_slots(device, wide: bool) -> int:
-    """Blocks of a prompt kernel the GPU holds at a time (one per SM for the 256-row kernel, two for the 128-row one)."""
+def _sm_count(device) -> int:
     index = device.index if device.index is not None else torch.cuda.current_device()
     if index not in _SM_COUNT:
         _SM_COUNT[index] = torch.cuda.get_device_properties(index).multi_processor_count
-    return _SM_COUNT[index] * (1 if wide else 2)
+    return _SM_COUNT[index]
+
+
+def _block_slots(device, wide: bool) -> int:
+    """Blocks of a prompt kernel the GPU holds at a time (one per SM for the 256-row kernel, two for the 128-row one)."""
+    return _sm_count(device) * (1 if wide else 2)
 
 
 def prefill_wide_wanted(batch, group: int, head_dim: int, n_q_heads: int, n_kv_heads: int, page_size: int) -> bool:
@@ -61,12 +65,14 @@ def supported(head_dim: int, n_q_heads: int, n_kv_heads: int) -> bool:
     return bool(library().llm_attention_mma_supports(head_dim, n_q_heads, n_kv_heads))
 
 
-def plan(batch, group: int, n_kv_heads: int):
-    """Launch shape of a batch, derived once per step from its host-side lengths."""
+def plan(batch, group: int, n_kv_heads: int, device=None):
+    """Launch shape of a batch, derived once per step from its host-side lengths (and the number of SMs: the split
+    count fixes the order of the partial sums, so it is a function of the batch and the GPU model only)."""
     key = ("attention_mma", group, n_kv_heads)
     cached = batch.scratch.get(key)
     if cached is not None:
         return cached
+    wave_blocks = DECODE_BLOCKS_PER_SM * _sm_count(device if device is not None else batch.token_ids.device)
     singles = sum(1 for length in batch.q_lens if length == 1)
     run_decode = singles > 0
     run_portions = singles < batch.n_seqs
@@ -78,15 +84,15 @@ def plan(batch, group: int, n_kv_heads: int):
         # wave's worth of (sequence, kv head) pairs already, no split at all.  Measured on the 8B head shape:
         # equal splits beat ragged ones, and one wave beats one and a half.
         pairs = singles * n_kv_heads
-        splits = max(1, min(WAVE_BLOCKS // pairs, -(-longest // MIN_SPLIT)))
-        if pairs > WAVE_BLOCKS:
+        splits = max(1, min(wave_blocks // pairs, -(-longest // MIN_SPLIT)))
+        if pairs > wave_blocks:
             # More than a wave of whole contexts: when the last wave would leave most SMs idle (40 sequences x 8 kv
             # heads = 1.08 waves take as long as 2), the contexts are split after all.  Measured on the 8B head shape at
             # context 3072: unsplit wins while the waves are three quarters full, else the fewest splits that fill
             # them to 0.85 (batch 40: 119 -> 100 us, batch 48: 123 -> 105, batch 80: 182 -> 170).
             def filled(count):
                 blocks = pairs * count
-                return blocks / (-(-blocks // WAVE_BLOCKS) * WAVE_BLOCKS)
+                return blocks / (-(-blocks // wave_blocks) * wave_blocks)
             if filled(1) < 0.75:
                 candidates = [count for count in (2, 3, 4) if longest // count >= 4 * TILE]
                 good = [count for count in candidates if filled(count) >= 0.85]
@@ -113,7 +119,7 @@ def try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_head
     check(k_pages, "k pages", torch.bfloat16, head_dim)
     check(v_pages, "v pages", torch.bfloat16, head_dim)
     check(block_tables, "block_tables", torch.int32)
-    run_portions, tiles, run_decode, split_len, max_splits = plan(batch, n_q_heads // n_kv_heads, n_kv_heads)
+    run_portions, tiles, run_decode, split_len, max_splits = plan(batch, n_q_heads // n_kv_heads, n_kv_heads, qkv.device)
     out = torch.empty((batch.n_tokens, n_q_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
     partial_out = partial_ml = None
     if run_decode and max_splits > 1:
@@ -145,14 +151,14 @@ def try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_head
         call("llm_attention_prefill_wide" if wide else "llm_attention_prefill_tcgen05", qkv.data_ptr(), q_stride, batch.n_tokens,
              k_pages.data_ptr(), v_pages.data_ptr(),
              block_tables.data_ptr(), block_tables.shape[-1], batch.q_start.data_ptr(), batch.context_len.data_ptr(),
-             out.data_ptr(), batch.n_seqs, n_q_heads, n_kv_heads, head_dim, page_size, float(scale), int(window),
+             out.data_ptr(), batch.n_seqs, n_q_heads, n_kv_heads, head_dim, page_size, k_pages.shape[0], float(scale), int(window),
              int(run_decode), int(pairing), paired if pairing else sum(tile_counts), flag, stream_handle())
         run_portions = False
         if not run_decode:
             return out
     call("llm_attention_mma", qkv.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(), block_tables.data_ptr(),
          block_tables.shape[-1], batch.q_start.data_ptr(), batch.context_len.data_ptr(), out.data_ptr(), batch.n_seqs,
-         n_q_heads, n_kv_heads, head_dim, page_size, float(scale), int(window), int(run_portions), tiles,
+         n_q_heads, n_kv_heads, head_dim, page_size, k_pages.shape[0], float(scale), int(window), int(run_portions), tiles,
          int(run_decode), split_len, max_splits, 0 if partial_out is None else partial_out.data_ptr(),
          0 if partial_ml is None else partial_ml.data_ptr(), flag, stream_handle())
     return out

@@ -30,13 +30,69 @@ def small_m_supported(rows: int, cols: int, inner: int) -> bool:
 # (row bucket, N, K, out dtype) -> split of K to use with this package's kernel, or 0 for the library product.
 _choice = {}
 SPLITS = (1, 2, 3, 4, 6, 8)
+ROW_BUCKETS = (1, 2, 4, 8, 16, 32, 48, 64)
+_tunings = 0
+
+
+def tunings() -> int:
+    """How many (row bucket, shape) choices were made by measurement in this process."""
+    return _tunings
 
 
 def _row_bucket(rows: int) -> int:
-    for bucket in (1, 2, 4, 8, 16, 32, 48, 64):
+    for bucket in ROW_BUCKETS:
         if rows <= bucket:
             return bucket
     return SMALL_M
+
+
+# The choices can be kept in a file (LLMSERVER_B200_GEMM_PLAN): what is in the file is used as it is, what is
+# measured is added to it.  The choice fixes the order in which a product's partial sums are added, so two processes
+# that read the same file give bit-identical bfloat16 results; without a file each process measures for itself and a
+# close race may go either way.
+PLAN_FILE = os.environ.get("LLMSERVER_B200_GEMM_PLAN")
+_plan_loaded = False
+
+
+def _key_text(key) -> str:
+    bucket, cols, inner, out_dtype = key
+    return f"{bucket},{cols},{inner},{'f32' if out_dtype == torch.float32 else 'bf16'}"
+
+
+def load_plan(path: Optional[str] = None) -> int:
+    """Reads choices from ``path`` (default: the file named by LLMSERVER_B200_GEMM_PLAN); returns how many."""
+    global _plan_loaded
+    _plan_loaded = True
+    path = path or PLAN_FILE
+    if not path or not os.path.isfile(path):
+        return 0
+    count = 0
+    with open(path) as handle:
+        for line in handle:
+            line = line.strip()
+            if not line or line.startswith("#"):
+                continue
+            try:
+                bucket, cols, inner, kind, split = line.split(",")
+                key = (int(bucket), int(cols), int(inner), torch.float32 if kind == "f32" else torch.bfloat16)
+                _choice.setdefault(key, int(split))
+                count += 1
+            except ValueError as error:
+                raise KernelError(f"{path}: cannot read the line {line!r} (row bucket,N,K,f32|bf16,split)") from error
+    return count
+
+
+def save_plan(path: Optional[str] = None) -> None:
+    """Writes every known choice to ``path`` (default: the file named by LLMSERVER_B200_GEMM_PLAN)."""
+    path = path or PLAN_FILE
+    if not path:
+        raise KernelError("no plan file was named (LLMSERVER_B200_GEMM_PLAN)")
+    lines = ["# row bucket,N,K,output,split of K (0: library product)"]
+    lines += [f"{_key_text(key)},{split}" for key, split in sorted(_choice.items(), key=lambda item: _key_text(item[0]))]
+    temporary = f"{path}.{os.getpid()}.tmp"
+    with open(temporary, "w") as handle:
+        handle.write("\n".join(lines) + "\n")
+    os.replace(temporary, path)
 
 
 _flush_buffer = {}
@@ -107,21 +163,40 @@ def _plan_for(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> 
     the same operands and give the same result up to rounding, so the choice changes speed only.
     While a CUDA graph is being captured nothing can be timed: an unknown shape then uses this
     package's kernel with its default split."""
+    global _tunings
     rows, inner = x.shape
     cols = weight.shape[0]
     key = (_row_bucket(rows), cols, inner, out_dtype)
     known = _choice.get(key)
     if known is not None:
         return known
+    if not _plan_loaded:
+        load_plan()
+        if key in _choice:
+            return _choice[key]
     if torch.cuda.is_current_stream_capturing():
         return -1
+    if out_dtype == torch.float32:
+        # 32-bit results always come from this package's kernel, straight from its accumulators; only the split is
+        # measured (the library's product would have to be rounded to bfloat16 on the way)
+        out = torch.empty((rows, cols), dtype=out_dtype, device=x.device)
+        best, best_time = 1, float("inf")
+        tiles, k_blocks = -(-cols // 128), -(-inner // 128)
+        for split in SPLITS:
+            if split > 1 and (tiles * split > 600 or k_blocks // split < 2):
+                continue
+            elapsed = _time_in_step(lambda: _small_m(x, weight, out, split), x.device)
+            if elapsed < best_time:
+                best_time, best = elapsed, split
+        _choice[key] = best
+        _tunings += 1
+        if PLAN_FILE:
+            save_plan()
+        return best
     out = torch.empty((rows, cols), dtype=out_dtype, device=x.device)
 
     def library_product():
-        if out_dtype == torch.bfloat16:
-            torch.matmul(x, weight.t(), out=out)
-        else:
-            out.copy_(torch.matmul(x, weight.t()))
+        torch.matmul(x, weight.t(), out=out)
 
     favour_library = key[0] > 16
     best_time = _time_in_step(library_product, x.device) * ((1.0 - _CLOSE_MANY_ROWS) if favour_library else (1.0 + _CLOSE_FEW_ROWS))
@@ -134,6 +209,9 @@ def _plan_for(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> 
         if elapsed < best_time:
             best_time, best = elapsed, split
     _choice[key] = best
+    _tunings += 1
+    if PLAN_FILE:
+        save_plan()
     return best
 
 
@@ -142,23 +220,40 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tenso
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
         raise KernelError(f"linear_bf16 takes bfloat16 operands, got {x.dtype} and {weight.dtype}")
     out_dtype = out_dtype or torch.bfloat16
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"linear_bf16 writes bfloat16 or float32, not {out_dtype}")
     rows, inner = x.shape
     cols = weight.shape[0]
-    if rows <= SMALL_M and x.is_contiguous() and weight.is_contiguous() and small_m_supported(rows, cols, inner) \
-            and out_dtype in (torch.bfloat16, torch.float32):
+    if out is not None and (out.dtype != out_dtype or not out.is_contiguous() or out.shape != (rows, cols)):
+        raise KernelError("linear_bf16: the output tensor does not match")
+    own_kernel = x.is_contiguous() and weight.is_contiguous() and small_m_supported(min(rows, SMALL_M), cols, inner)
+    if out_dtype == torch.float32:
+        # logits: 32-bit sums written as they are, whatever the number of rows (never a bfloat16 product widened
+        # afterwards: rounding 150 thousand logits to 8 bits makes ties, and ties would then depend on the row count)
+        if not own_kernel:
+            return _float32_by_library(x, weight, out)
+        if out is None:
+            out = torch.empty((rows, cols), dtype=out_dtype, device=x.device)
+        for begin in range(0, rows, SMALL_M):
+            part = x[begin:begin + SMALL_M]
+            _small_m(part, weight, out[begin:begin + SMALL_M], max(_plan_for(part, weight, out_dtype), 0))
+        return out
+    if rows <= SMALL_M and own_kernel:
         split = _plan_for(x, weight, out_dtype)
         if split != 0:
             if out is None:
                 out = torch.empty((rows, cols), dtype=out_dtype, device=x.device)
-            elif out.dtype != out_dtype or not out.is_contiguous() or out.shape != (rows, cols):
-                raise KernelError("linear_bf16: the output tensor does not match")
             _small_m(x, weight, out, max(split, 0))
             return out
-    if out_dtype == torch.bfloat16:
-        if out is not None:
-            return torch.matmul(x, weight.t(), out=out)
-        return torch.matmul(x, weight.t())
-    result = torch.matmul(x, weight.t()).to(out_dtype)
+    if out is not None:
+        return torch.matmul(x, weight.t(), out=out)
+    return torch.matmul(x, weight.t())
+
+
+def _float32_by_library(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor]) -> torch.Tensor:
+    """For shapes this package's kernel does not take: the library's product with a 32-bit result (32-bit sums of
+    bfloat16 products, not a rounded bfloat16 result widened)."""
+    result = torch.mm(x, weight.t(), out_dtype=torch.float32)
     if out is not None:
         out.copy_(result)
         return out

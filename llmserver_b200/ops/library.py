@@ -23,16 +23,16 @@ SIGNATURES = {
     "llm_sample": [_P, _P, _P, _P, _P, _I, _I, _P, _P, _S],
     "llm_sample_slices": [_I, _I],
     "llm_qk_norm_rope_kv_write": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _I, _S],
-    "llm_attention_generic": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _S],
+    "llm_attention_generic": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _S],
     "llm_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _S],
     "llm_attention_mma_supports": [_I, _I, _I],
     "llm_attention_prefill_tcgen05_supports": [_I, _I, _I, _I],
-    "llm_attention_prefill_tcgen05": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _S],
+    "llm_attention_prefill_tcgen05": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _S],
     "llm_attention_prefill_wide_supports": [_I, _I, _I, _I],
-    "llm_attention_prefill_wide": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _S],
+    "llm_attention_prefill_wide": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _S],
     "llm_gemm_small_m_supports": [_I, _I, _I],
     "llm_gemm_small_m": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _S],
-    "llm_attention_mma": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _I, _I, _P, _P, _P, _S],
+    "llm_attention_mma": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _I, _I, _P, _P, _P, _S],
 }
 
 _lock = threading.Lock()
@@ -159,4 +159,6 @@ def check_wait_errors() -> None:
         if code != 0:
             flag.zero_()
             raise KernelError(f"a kernel gave up waiting on one of its barriers (code {code}: 2 matrix product, "
-                              "3 decode attention, 4 prompt attention); the step's result is invalid")
+                              "3 decode attention, 4 prompt attention), or attention met a block-table entry that names no "
+                              "page of the pool (5) or a context that needs more splits than it was given (6); the step's "
+                              "result is invalid")

@@ -4,12 +4,15 @@ Some users of the kernel library cannot allocate device memory where they call i
 given all free memory to its cache, a latency-critical loop, a C program without PyTorch's allocator);
 for them ``llm_attention_decode_noalloc`` keeps the split-KV scratch in a fixed array inside the
 library.  This test calls it twice in a row with different inputs, through ctypes, and compares each
-result with the regular entry point's, which takes its scratch from the caller.  It is collected last
-so that a run that stops at the first failure has already run every other test."""
+result with the regular entry point's, which takes its scratch from the caller, and with plain attention
+in float64.  It is collected last so that a run that stops at the first failure has already run every
+other test."""
 import ctypes
 
 import pytest
 import torch
+
+import plain_model
 
 pytestmark = pytest.mark.gpu
 
@@ -33,6 +36,20 @@ def make_case(seed, contexts, heads, kv_heads, dim, page_size):
     return qkv, q_stride, k_pages, v_pages, tables.to(DEVICE)
 
 
+def plain_decode_attention(qkv, k_pages, v_pages, tables, contexts, heads, kv_heads, dim, page_size, scale, window):
+    """float64 attention of each sequence's last position over its pages, by the plain implementation."""
+    rows = []
+    tables = tables.cpu()
+    for row, context in enumerate(contexts):
+        pages = tables[row, :-(-context // page_size)].long()
+        keys = k_pages.cpu()[pages].permute(0, 2, 1, 3).reshape(-1, kv_heads, dim)[:context].double()
+        values = v_pages.cpu()[pages].permute(0, 2, 1, 3).reshape(-1, kv_heads, dim)[:context].double()
+        queries = torch.zeros((context, heads, dim), dtype=torch.float64)
+        queries[-1] = qkv[row, :heads * dim].cpu().double().reshape(heads, dim)
+        rows.append(plain_model.causal_attention(queries, keys, values, scale, window or None)[-1].reshape(-1))
+    return torch.stack(rows)
+
+
 class Batch:
     def __init__(self, contexts):
         self.q_lens, self.context_lens = [1] * len(contexts), list(contexts)
@@ -50,8 +67,10 @@ def test_no_alloc_decode_attention_matches_the_regular_entry_point_twice_in_a_ro
     entry = lib.llm_attention_decode_noalloc          # the exported C symbol
     pointer, integer = ctypes.c_void_p, ctypes.c_int
     entry.argtypes = [pointer, integer, pointer, pointer, pointer, integer, pointer, pointer, pointer, integer, integer,
-                      integer, integer, integer, ctypes.c_float, integer, integer, integer, pointer]
+                      integer, integer, integer, integer, ctypes.c_float, integer, integer, integer, pointer]
     entry.restype = integer
+    status_of = lib.llm_attention_decode_noalloc_status
+    status_of.argtypes, status_of.restype = [pointer], integer
     heads, kv_heads, dim, page_size = 8, 2, 128, 16
     scale = dim ** -0.5
     stream = torch.cuda.current_stream().cuda_stream
@@ -60,19 +79,36 @@ def test_no_alloc_decode_attention_matches_the_regular_entry_point_twice_in_a_ro
         batch = Batch(contexts)
         expected = attention_bf16.try_attention(qkv, q_stride, batch, tables, k_pages, v_pages, heads, kv_heads, dim,
                                                 scale, window)
-        _, _, _, split_len, max_splits = attention_bf16.plan(batch, heads // kv_heads, kv_heads)
+        _, _, _, split_len, max_splits = attention_bf16.plan(batch, heads // kv_heads, kv_heads, qkv.device)
         assert max_splits > 1, "the case is meant to use the scratch memory"
         out = torch.full_like(expected, float("nan"))
         status = entry(qkv.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(), tables.data_ptr(),
                        tables.shape[1], batch.q_start.data_ptr(), batch.context_len.data_ptr(), out.data_ptr(),
-                       len(contexts), heads, kv_heads, dim, page_size, scale, window, split_len, max_splits, stream)
+                       len(contexts), heads, kv_heads, dim, page_size, k_pages.shape[0], scale, window, split_len,
+                       max_splits, stream)
         assert status == 0, lib.llm_last_error().decode()
-        torch.cuda.synchronize()
+        assert status_of(stream) == 0
         assert torch.isfinite(out.float()).all()
         error = (out.float() - expected.float()).abs().max().item() / expected.float().abs().max().item()
         assert error <= 1e-2, f"call {call}: relative error {error:.3e}"
+        plain = plain_decode_attention(qkv, k_pages, v_pages, tables, contexts, heads, kv_heads, dim, page_size, scale, window)
+        error = (out.cpu().double() - plain).abs().max().item() / plain.abs().max().item()
+        assert error <= 1e-2, f"call {call}: relative error {error:.3e} against plain attention"
     # a request beyond the fixed array is refused with a message, not run
     status = entry(qkv.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(), tables.data_ptr(), tables.shape[1],
                    batch.q_start.data_ptr(), batch.context_len.data_ptr(), out.data_ptr(), len(contexts), heads,
-                   kv_heads, dim, page_size, scale, 0, 64, 4096, stream)
+                   kv_heads, dim, page_size, k_pages.shape[0], scale, 0, 64, 4096, stream)
     assert status == -1 and b"scratch" in lib.llm_last_error()
+    # a table entry that names no page of the pool is not followed (zeros are read), and the status word says so;
+    # too few splits for a context are reported too
+    tables[1, 0] = k_pages.shape[0] + 7
+    status = entry(qkv.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(), tables.data_ptr(), tables.shape[1],
+                   batch.q_start.data_ptr(), batch.context_len.data_ptr(), out.data_ptr(), len(contexts), heads,
+                   kv_heads, dim, page_size, k_pages.shape[0], scale, 0, split_len, max_splits, stream)
+    assert status == 0 and status_of(stream) == 5
+    assert torch.isfinite(out.float()).all()
+    tables[1, 0] = 0
+    status = entry(qkv.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(), tables.data_ptr(), tables.shape[1],
+                   batch.q_start.data_ptr(), batch.context_len.data_ptr(), out.data_ptr(), len(contexts), heads,
+                   kv_heads, dim, page_size, k_pages.shape[0], scale, 0, 256, 2, stream)
+    assert status == 0 and status_of(stream) == 6
