@@ -34,17 +34,30 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: a block arrangement over a mixer, a feed-forward and their norms.
+    """One layer: a block arrangement and the parts it arranges.
 
-    ``prefix`` is the layer's tensor-name prefix in the checkpoint; each part's tensors live
-    under ``prefix + <sub-prefix the block gives the part>``."""
+    Which parts a block has is the block's business: its class names its *roles* (``Block.roles``), each filled by
+    a part of some registry (a mixer, a feed-forward, a norm).  The usual four roles have fields of their own here;
+    a block with further roles (more norms, say) finds them in ``extra`` under the role's name.  ``prefix`` is the
+    layer's tensor-name prefix in the checkpoint; each part's tensors live under ``prefix + <sub-prefix the block
+    gives the role>``."""
     prefix: str
     block: PartSpec
     mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward: Optional[PartSpec] = None
+    mixer_norm: Optional[PartSpec] = None
+    feed_forward_norm: Optional[PartSpec] = None
     position: Optional[str] = None  # key of ModelSpec.positions used by the mixer
+    extra: Tuple[Tuple[str, PartSpec], ...] = ()
+
+    def part(self, role: str) -> PartSpec:
+        """The part that fills ``role`` in this layer."""
+        found = dict(self.extra).get(role)
+        if found is None and role in ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm"):
+            found = getattr(self, role)
+        if found is None:
+            raise KeyError(f"layer {self.prefix!r}: its block wants a part in the role {role!r}, the layer names none")
+        return found
 
 
 @dataclass(frozen=True)

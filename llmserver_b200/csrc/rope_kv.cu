@@ -11,6 +11,10 @@
 // the activation type after the norm, after the weight and after x*cos; here all of it is 32-bit
 // (angles and cos/sin too) and each value is rounded once.
 //
+// Only the first `rotary_dim` elements of a head are rotated (the rest pass through after the norm), paired either
+// as halves (i with i + rotary_dim / 2, the reference's form) or interleaved (2i with 2i + 1); anything but the
+// reference's form (all of the head, halves) runs in the plain one-element-per-lane form of the first kernel.
+//
 // Pages are laid out [page, kv_head, slot, D]: one (page, head) is a contiguous page_size * D run.
 // A token's page is block_tables[seq_of_token[n], position / page_size].
 #include "common.cuh"
@@ -31,15 +35,16 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const W* __res
                                              const int* __restrict__ block_tables, int max_blocks,
                                              T* __restrict__ k_pages, T* __restrict__ v_pages, int n_q_heads,
                                              int n_kv_heads, int head_dim, int page_size, int num_pages, float eps,
-                                             int write_cache, int* __restrict__ error_flag, int vector_form, int heads_per_block) {
+                                             int write_cache, int* __restrict__ error_flag, int vector_form, int heads_per_block,
+                                             int rotary_dim, int interleaved) {
     pdl_trigger();   // let the next kernel start launching
     pdl_wait();      // everything before this kernel in the stream is complete and visible
-    extern __shared__ float2 rotation[];   // (cos, sin) of angle = position * inv_freq[i], i < head_dim / 2
+    extern __shared__ float2 rotation[];   // (cos, sin) of angle = position * inv_freq[i], i < rotary_dim / 2
     const int token = blockIdx.x;
     const int warps_per_block = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     const int total_heads = n_q_heads + 2 * n_kv_heads;
-    const int half = head_dim >> 1;
+    const int half = rotary_dim >> 1;      // the vector form below is used only when rotary_dim == head_dim
     const int position = positions[token];
     // the angles depend on the token only: computed once per block, used by every head the block handles
     if (inv_freq) {
@@ -134,10 +139,12 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const W* __res
             inverse = rsqrtf(warp_sum(sum_squares) / (float)head_dim + eps);
         }
         for (int i = lane; i < half; i += 32) {
-            float low = Num<T>::load(src + i), high = Num<T>::load(src + half + i);
+            // the two elements that rotate together: halves (i, i + rotary_dim / 2) or neighbours (2i, 2i + 1)
+            const int first = interleaved ? 2 * i : i, second = interleaved ? 2 * i + 1 : half + i;
+            float low = Num<T>::load(src + first), high = Num<T>::load(src + second);
             if (weight) {
-                low = low * inverse * Num<W>::load(weight + i);
-                high = high * inverse * Num<W>::load(weight + half + i);
+                low = low * inverse * Num<W>::load(weight + first);
+                high = high * inverse * Num<W>::load(weight + second);
             }
             if (inv_freq) {
                 const float c = rotation[i].x, sn = rotation[i].y;
@@ -146,8 +153,13 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, const W* __res
                 low = rotated_low;
                 high = rotated_high;
             }
-            Num<T>::store(dst + i, low);
-            Num<T>::store(dst + half + i, high);
+            Num<T>::store(dst + first, low);
+            Num<T>::store(dst + second, high);
+        }
+        for (int i = rotary_dim + lane; i < head_dim; i += 32) {      // beyond the rotated part: the norm only
+            float value = Num<T>::load(src + i);
+            if (weight) value = value * inverse * Num<W>::load(weight + i);
+            Num<T>::store(dst + i, value);
         }
     }
 }
@@ -253,13 +265,18 @@ LLM_EXPORT int llm_qk_norm_rope_kv_write(void* qkv, const void* q_weight, const 
                                          const int* positions, const int* seq_of_token, const int* block_tables,
                                          int max_blocks, void* k_pages, void* v_pages, int n_tokens, int n_q_heads,
                                          int n_kv_heads, int head_dim, int page_size, int num_pages, float eps,
-                                         int write_cache, int* error_flag, int dtype, int weight_dtype,
-                                         cudaStream_t stream) {
+                                         int write_cache, int* error_flag, int rotary_dim, int interleaved, int dtype,
+                                         int weight_dtype, cudaStream_t stream) {
     if (n_tokens == 0) return LLM_OK;
-    if (head_dim % 2) {
-        llm_set_error("qk_norm_rope_kv_write: head_dim must be even, got %d", head_dim);
+    if (inv_freq == nullptr) {        // no rotation at all: the pairs are only the order in which elements are visited
+        rotary_dim = head_dim;
+        interleaved = 0;
+    }
+    if (rotary_dim < 0 || rotary_dim > head_dim || rotary_dim % 2) {
+        llm_set_error("qk_norm_rope_kv_write: rotary_dim must be even and at most head_dim %d, got %d", head_dim, rotary_dim);
         return LLM_REFUSED;
     }
+    const bool whole_head_in_halves = rotary_dim == head_dim && !interleaved;
     const int total_heads = n_q_heads + 2 * n_kv_heads;
     // many tokens (prompts): one block of 8 warps per token takes all heads and computes the token's angles
     // once; few tokens (decode): four heads per block of four warps, for more blocks in flight
@@ -267,10 +284,10 @@ LLM_EXPORT int llm_qk_norm_rope_kv_write(void* qkv, const void* q_weight, const 
     const int heads_per_block = n_tokens >= 256 ? total_heads : warps;
     // pair and 16-byte accesses need head_dim to be a multiple of 8 (bfloat16) or 4 (float) and aligned bases
     const int per_vector = dtype == LLM_F32 ? 4 : 8;
-    const int vector_form = head_dim % per_vector == 0 && head_dim % 4 == 0 && head_dim <= 512 && aligned16(qkv) && aligned16(k_pages) &&
+    const int vector_form = whole_head_in_halves && head_dim % per_vector == 0 && head_dim % 4 == 0 && head_dim <= 512 && aligned16(qkv) && aligned16(k_pages) &&
                             aligned16(v_pages) && aligned16(q_weight) && aligned16(k_weight);
     dim3 grid(n_tokens, (total_heads + heads_per_block - 1) / heads_per_block);
-    const size_t shared = (size_t)(head_dim / 2) * sizeof(float2);
+    const size_t shared = (size_t)(rotary_dim / 2 + 1) * sizeof(float2);
     // head sizes 64 / 128 / 256 with aligned operands: the wide form
     const bool wide = vector_form && (head_dim == 64 || head_dim == 128 || head_dim == 256) && aligned16(q_weight) && aligned16(k_weight);
     if (wide) {
@@ -297,7 +314,8 @@ LLM_EXPORT int llm_qk_norm_rope_kv_write(void* qkv, const void* q_weight, const 
         LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype, (llm_launch(qk_norm_rope_kv_write_kernel<T, W, HELD>, grid, warps * 32, shared, stream,  \
                                       (T*)qkv, (const W*)q_weight, (const W*)k_weight, inv_freq, positions, seq_of_token, \
                                       block_tables, max_blocks, (T*)k_pages, (T*)v_pages, n_q_heads, n_kv_heads, head_dim, \
-                                      page_size, num_pages, eps, write_cache, error_flag, vector_form, heads_per_block))); \
+                                      page_size, num_pages, eps, write_cache, error_flag, vector_form, heads_per_block, \
+                                      rotary_dim, interleaved))); \
 
     if (head_dim <= 128) {
         LLM_ROPE_LAUNCH(1)

@@ -136,6 +136,7 @@ class DecodeGraph:
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
             logits = self.model.step(self.batch)
+            self.logits = logits        # [batch_size, vocab] of the last replay (tests compare them with eager steps)
             tokens = ops.sample(logits, self.batch.temperatures, self.batch.seeds, self.batch.sample_steps)
             self.result = torch.cat([tokens, self.batch.error_flag, wait_error_flag(device)])
 

@@ -12,7 +12,8 @@ import torch
 
 from .. import ops
 from ..config.spec import ModelSpec
-from ..parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, EntryCache, Runtime
+from ..parts import BLOCKS, MIXERS, NORMS, POSITION_ENCODINGS, EntryCache, Runtime
+from ..parts.registry import parts_of_layer
 from ..parts.base import Block
 
 
@@ -32,16 +33,11 @@ class DecoderModel:
             block_cls = BLOCKS.get(layer.block.kind)
             block_params = layer.block.as_dict()
             built = {}
-            for role, part, table in (("mixer", layer.mixer, MIXERS), ("feed_forward", layer.feed_forward, FEED_FORWARDS),
-                                      ("mixer_norm", layer.mixer_norm, NORMS),
-                                      ("feed_forward_norm", layer.feed_forward_norm, NORMS)):
-                cls = table.get(part.kind)
-                prefix = layer.prefix + block_cls.prefix_of(block_params, role)
+            for role, part, cls, prefix in parts_of_layer(layer):
                 weights = {local: source.get(prefix + local) for local in cls.declare_weights(part.as_dict())}
                 built[role] = cls(part.as_dict(), weights, runtime)
-            built["mixer"].attach(self.positions.get(layer.position) if layer.position else None)
-            self.layers.append(block_cls(block_params, built["mixer"], built["feed_forward"], built["mixer_norm"],
-                                         built["feed_forward_norm"]))
+            built[block_cls.mixer_role(block_params)].attach(self.positions.get(layer.position) if layer.position else None)
+            self.layers.append(block_cls(block_params, built))
         norm_cls = NORMS.get(spec.final_norm.kind)
         self.final_norm = norm_cls(spec.final_norm.as_dict(),
                                    {local: source.get(spec.final_norm_prefix + local)
@@ -56,7 +52,9 @@ class DecoderModel:
         needs = []
         for entry in self.spec.schedule:
             layer = self.spec.layers[entry.layer]
-            need = MIXERS.get(layer.mixer.kind).cache_need(layer.mixer.as_dict())
+            block_cls = BLOCKS.get(layer.block.kind)
+            mixer = layer.part(block_cls.mixer_role(layer.block.as_dict()))
+            need = MIXERS.get(mixer.kind).cache_need(mixer.as_dict())
             needs.append(None if entry.cache_from is not None else need)
         return needs
 

@@ -117,10 +117,16 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k
                           inv_freq: Optional[torch.Tensor], positions: torch.Tensor, seq_of_token: torch.Tensor,
                           block_tables: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, n_q_heads: int,
                           n_kv_heads: int, head_dim: int, eps: float, write_cache: bool,
-                          error_flag: torch.Tensor) -> None:
+                          error_flag: torch.Tensor, rotary_dim: Optional[int] = None, interleaved: bool = False) -> None:
     """In place on qkv [N, (Hq + 2 Hkv) D]: Q heads normalised and rotated where they are; K heads
     normalised, rotated and written to the K pages; V heads copied to the V pages.  Pages are
-    [page, Hkv, page_size, D]; block_tables int32 [S, max_blocks]."""
+    [page, Hkv, page_size, D]; block_tables int32 [S, max_blocks].  ``rotary_dim`` (default: all of the head)
+    elements of each head are rotated, by the angles position * inv_freq[i], i < rotary_dim / 2, paired as halves
+    (i, i + rotary_dim / 2) or, ``interleaved``, as neighbours (2i, 2i + 1)."""
+    if rotary_dim is None:
+        rotary_dim = head_dim if inv_freq is None else 2 * inv_freq.numel()
+    if rotary_dim % 2 or not 0 <= rotary_dim <= head_dim:
+        raise KernelError(f"rotary_dim must be even and at most head_dim {head_dim}, got {rotary_dim}")
     check(qkv, "qkv", last_dim=(n_q_heads + 2 * n_kv_heads) * head_dim)
     tokens = qkv.shape[0]
     weight_dtype = qkv.dtype
@@ -131,7 +137,7 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k
     if q_weight is not None and k_weight is not None and q_weight.dtype != k_weight.dtype:
         raise KernelError("q and k norm weights must share a dtype")
     if inv_freq is not None:
-        check(inv_freq, "inv_freq", torch.float32, head_dim // 2)
+        check(inv_freq, "inv_freq", torch.float32, rotary_dim // 2)
     check(positions, "positions", torch.int32)
     check(seq_of_token, "seq_of_token", torch.int32)
     check(block_tables, "block_tables", torch.int32)
@@ -145,8 +151,8 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k
     call("llm_qk_norm_rope_kv_write", qkv.data_ptr(), pointer(q_weight), pointer(k_weight), pointer(inv_freq),
          positions.data_ptr(), seq_of_token.data_ptr(), block_tables.data_ptr(), block_tables.shape[-1],
          k_pages.data_ptr(), v_pages.data_ptr(), tokens, n_q_heads, n_kv_heads, head_dim, k_pages.shape[2],
-         k_pages.shape[0], float(eps), int(write_cache), error_flag.data_ptr(), dtype_code(qkv.dtype),
-         dtype_code(weight_dtype), stream_handle())
+         k_pages.shape[0], float(eps), int(write_cache), error_flag.data_ptr(), int(rotary_dim), int(bool(interleaved)),
+         dtype_code(qkv.dtype), dtype_code(weight_dtype), stream_handle())
 
 
 def attention_generic(q: torch.Tensor, q_stride: int, k_pages: torch.Tensor, v_pages: torch.Tensor,

@@ -22,7 +22,7 @@ SIGNATURES = {
     "llm_silu_mul": [_P, _P, _I, _I, _I, _S],
     "llm_sample": [_P, _P, _P, _P, _P, _I, _I, _P, _P, _S],
     "llm_sample_slices": [_I, _I],
-    "llm_qk_norm_rope_kv_write": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _I, _S],
+    "llm_qk_norm_rope_kv_write": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _I, _I, _I, _S],
     "llm_attention_generic": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _S],
     "llm_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _S],
     "llm_attention_mma_supports": [_I, _I, _I],

@@ -21,7 +21,23 @@ class GQAttention(Mixer):
 
     Parameters: ``hidden``, ``heads``, ``kv_heads``, ``head_dim``, ``scale``, ``qk_norm`` (bool),
     ``eps`` (of the Q/K norms), ``window`` (None = all keys; else a query at position p reads keys
-    p - window + 1 .. p)."""
+    p - window + 1 .. p).  ``bias`` and ``softcap`` are known and must be off: the kernels have neither a bias
+    epilogue nor score capping, and say so instead of computing without them.
+
+    How positions are encoded comes from the position encoding the layer names (``attach``): its inverse
+    frequencies, how many elements of a head rotate (``rotary_dim``, at most head_dim) and how they pair
+    ("halves" or "interleaved").  An encoding that scales the rotated values (``attention_factor`` other than 1) is
+    refused: the rotation kernel does not scale."""
+
+    KNOWN_PARAMS = ("hidden", "heads", "kv_heads", "head_dim", "scale", "qk_norm", "eps", "window", "bias", "softcap")
+
+    @classmethod
+    def check_params(cls, params):
+        super().check_params(params)
+        if params.get("bias"):
+            raise ValueError("gqa_attention has no biases in its projections (bias must be absent or false)")
+        if params.get("softcap"):
+            raise ValueError("gqa_attention does not cap attention scores (softcap must be absent or 0)")
 
     @classmethod
     def declare_weights(cls, params):
@@ -51,20 +67,35 @@ class GQAttention(Mixer):
         self.out = weights["o_proj.weight"].contiguous()
         self.q_norm = weights["q_norm.weight"].contiguous() if params.get("qk_norm") else None
         self.k_norm = weights["k_norm.weight"].contiguous() if params.get("qk_norm") else None
-        self.inv_freq = None
+        self.inv_freq, self.rotary_dim, self.interleaved = None, self.head_dim, False
 
     def attach(self, position):
-        if position is not None:
-            if getattr(position, "head_dim", self.head_dim) != self.head_dim:
-                raise ValueError("the position encoding was built for another head_dim")
-            self.inv_freq = position.inv_freq
+        """``position``: None (no rotation) or an encoding with ``inv_freq`` (float32 [rotary_dim / 2] on the device)
+        and, optionally, ``rotary_dim``, ``pairing`` ("halves" | "interleaved") and ``attention_factor``."""
+        if position is None:
+            return
+        inv_freq = getattr(position, "inv_freq", None)
+        if inv_freq is None:
+            raise ValueError(f"gqa_attention rotates queries and keys: the position encoding {type(position).__name__} "
+                             "gives no inv_freq (an encoding that acts on the embedding is not named by a layer)")
+        rotary_dim = int(getattr(position, "rotary_dim", 2 * inv_freq.numel()))
+        if rotary_dim != 2 * inv_freq.numel() or rotary_dim > self.head_dim or rotary_dim % 2:
+            raise ValueError(f"the position encoding rotates {rotary_dim} elements with {inv_freq.numel()} frequencies; "
+                             f"gqa_attention needs an even rotary_dim of at most head_dim {self.head_dim} and half as many frequencies")
+        pairing = getattr(position, "pairing", "halves")
+        if pairing not in ("halves", "interleaved"):
+            raise ValueError(f"gqa_attention pairs rotated elements as 'halves' or 'interleaved', not {pairing!r}")
+        if float(getattr(position, "attention_factor", 1.0)) != 1.0:
+            raise ValueError("gqa_attention's rotation kernel does not scale the rotated values: the position encoding's "
+                             f"attention_factor is {position.attention_factor}, only 1 is supported")
+        self.inv_freq, self.rotary_dim, self.interleaved = inv_freq, rotary_dim, pairing == "interleaved"
 
     def forward(self, x, batch, cache):
         qkv = ops.linear(x, self.qkv)
         tables = batch.block_tables[cache.group]
         ops.qk_norm_rope_kv_write(qkv, self.q_norm, self.k_norm, self.inv_freq, batch.positions, batch.seq_of_token,
                                   tables, cache.k_pages, cache.v_pages, self.heads, self.kv_heads, self.head_dim,
-                                  self.eps, cache.writes, batch.error_flag)
+                                  self.eps, cache.writes, batch.error_flag, self.rotary_dim, self.interleaved)
         attended = ops.attention(qkv, batch, tables, cache.k_pages, cache.v_pages, self.heads, self.kv_heads,
                                  self.head_dim, self.scale, self.window)
         return ops.linear(attended, self.out)

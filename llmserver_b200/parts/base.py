@@ -30,12 +30,26 @@ class Runtime:
 
 
 class Part:
+    # Names of the parameters the part understands (None: anything goes).  A specification that gives a part a
+    # parameter it does not know is refused: a "bias=True" that is silently dropped would compute another model.
+    KNOWN_PARAMS = None
+
+    @classmethod
+    def check_params(cls, params: dict) -> None:
+        """Raises ``ValueError`` for a parameter the part does not know or a value it cannot honour."""
+        if cls.KNOWN_PARAMS is not None:
+            unknown = sorted(set(params) - set(cls.KNOWN_PARAMS))
+            if unknown:
+                raise ValueError(f"{cls.__name__} does not know the parameter(s) {', '.join(unknown)} "
+                                 f"(it takes: {', '.join(sorted(cls.KNOWN_PARAMS))})")
+
     @classmethod
     def declare_weights(cls, params: dict) -> Dict[str, WeightDecl]:
         """Local tensor name -> declaration."""
         return {}
 
     def __init__(self, params: dict, weights: Dict[str, torch.Tensor], runtime: Runtime):
+        self.check_params(params)
         self.params, self.runtime = params, runtime
 
 
@@ -69,17 +83,32 @@ class PositionEncoding(Part):
 
 
 class Block(Part):
-    ROLES = ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm")
+    """An arrangement of parts around the residual stream.  The class says which parts it arranges: ``roles`` maps
+    each role's name to the registry its part comes from ("mixer", "feed_forward" or "norm").  The model builds one
+    part per role from the layer's specification and hands them over by name; they become attributes of the block.
+    Exactly one role comes from the mixer registry: it is the part that owns the layer's cache."""
+
+    @classmethod
+    def roles(cls, params: dict) -> Dict[str, str]:
+        return {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
 
     @classmethod
     def prefix_of(cls, params: dict, role: str) -> str:
         """Tensor-name prefix (inside the layer) of the part in ``role``."""
         return params.get(f"{role}_prefix", role + ".")
 
-    def __init__(self, params, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
-        self.params = params
-        self.mixer, self.feed_forward = mixer, feed_forward
-        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+    @classmethod
+    def mixer_role(cls, params: dict) -> str:
+        mixers = [role for role, registry in cls.roles(params).items() if registry == "mixer"]
+        if len(mixers) != 1:
+            raise ValueError(f"{cls.__name__} must arrange exactly one mixer, it names {len(mixers)}")
+        return mixers[0]
+
+    def __init__(self, params, parts: Dict[str, Part]):
+        self.check_params(params)
+        self.params, self.parts = params, dict(parts)
+        for role, part in parts.items():
+            setattr(self, role, part)
 
     def forward(self, residual, delta, batch, cache):
         raise NotImplementedError

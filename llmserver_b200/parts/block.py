@@ -14,6 +14,8 @@ class PreNormBlock(Block):
     not been added yet, and returns the stream and its feed-forward's output, still to be added.
     Parameters: the tensor-name prefixes of its four parts (``mixer_prefix`` ...)."""
 
+    KNOWN_PARAMS = ("mixer_prefix", "feed_forward_prefix", "mixer_norm_prefix", "feed_forward_norm_prefix")
+
     def forward(self, residual, delta, batch, cache):
         normed = self.mixer_norm.add_norm(residual, delta)
         mixed = self.mixer.forward(normed, batch, cache)

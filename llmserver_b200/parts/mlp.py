@@ -13,7 +13,18 @@ from .registry import FEED_FORWARDS
 class SwiGLU(FeedForward):
     """down(silu(gate(x)) * up(x)) without biases (utils/layers.py:182-218).  gate and up are
     concatenated once at load into one [2 I, H] matrix, gate rows first, as the reference's
-    ``fuse_projections`` (utils/layers.py:194-203).  Parameters: ``hidden``, ``intermediate``."""
+    ``fuse_projections`` (utils/layers.py:194-203).  Parameters: ``hidden``, ``intermediate``; ``bias`` must be off
+    and ``activation``, if given, "silu"."""
+
+    KNOWN_PARAMS = ("hidden", "intermediate", "bias", "activation")
+
+    @classmethod
+    def check_params(cls, params):
+        super().check_params(params)
+        if params.get("bias"):
+            raise ValueError("swiglu has no biases (bias must be absent or false)")
+        if params.get("activation", "silu") != "silu":
+            raise ValueError(f"swiglu gates with SiLU, not {params['activation']!r}")
 
     @classmethod
     def declare_weights(cls, params):

@@ -13,6 +13,8 @@ class RMSNorm(Norm):
     (1 + weight); no bias.  Parameters: ``width``, ``eps``.  Fused with the residual add that precedes
     it, as the reference's add_rms_norm (utils/fused_ops.py:145-155)."""
 
+    KNOWN_PARAMS = ("width", "eps")
+
     @classmethod
     def declare_weights(cls, params):
         return {"weight": WeightDecl((params["width"],), NORM)}

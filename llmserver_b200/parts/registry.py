@@ -35,3 +35,21 @@ FEED_FORWARDS = PartRegistry("feed-forward")
 NORMS = PartRegistry("norm")
 POSITION_ENCODINGS = PartRegistry("position encoding")
 BLOCKS = PartRegistry("block")
+
+REGISTRIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS}
+
+
+def parts_of_layer(layer):
+    """What a layer is made of, as its block says: a list of (role, part specification, part class, tensor-name
+    prefix).  The model builder and the weight declarations both go by this list."""
+    block_cls = BLOCKS.get(layer.block.kind)
+    block_params = layer.block.as_dict()
+    block_cls.check_params(block_params)
+    found = []
+    for role, registry in block_cls.roles(block_params).items():
+        if registry not in REGISTRIES:
+            raise KeyError(f"block {layer.block.kind!r}: role {role!r} names the unknown registry {registry!r}")
+        spec = layer.part(role)
+        REGISTRIES[registry].get(spec.kind).check_params(spec.as_dict())
+        found.append((role, spec, REGISTRIES[registry].get(spec.kind), layer.prefix + block_cls.prefix_of(block_params, role)))
+    return found

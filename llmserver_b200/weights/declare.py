@@ -21,13 +21,9 @@ def declared_weights(spec) -> Dict[str, WeightDecl]:
 
     wanted: Dict[str, WeightDecl] = {spec.embedding_name: WeightDecl((spec.vocab_size, spec.hidden_size))}
     for layer in spec.layers:
-        block = parts.BLOCKS.get(layer.block.kind)
-        for role, part_spec, table in (("mixer", layer.mixer, parts.MIXERS), ("feed_forward", layer.feed_forward, parts.FEED_FORWARDS),
-                                       ("mixer_norm", layer.mixer_norm, parts.NORMS),
-                                       ("feed_forward_norm", layer.feed_forward_norm, parts.NORMS)):
-            sub_prefix = block.prefix_of(layer.block.as_dict(), role)
-            for local, declaration in table.get(part_spec.kind).declare_weights(part_spec.as_dict()).items():
-                wanted[layer.prefix + sub_prefix + local] = declaration
+        for _, part_spec, part_cls, prefix in parts.parts_of_layer(layer):
+            for local, declaration in part_cls.declare_weights(part_spec.as_dict()).items():
+                wanted[prefix + local] = declaration
     for local, declaration in parts.NORMS.get(spec.final_norm.kind).declare_weights(spec.final_norm.as_dict()).items():
         wanted[spec.final_norm_prefix + local] = declaration
     for name, position in spec.positions.items():

@@ -174,7 +174,7 @@ def test_random_serving_schedule_changes_no_token(tiny_folders):
         jobs.append(dict(prompt=prompt, new=rng.randint(1, 40), temperature=rng.choice([0.0, 0.0, 0.7]), seed=900 + index,
                          arrives=rng.randint(0, 60)))
     engine = Engine(folder, max_new_tokens=64, max_batch_size=6, max_num_batched_tokens=48, prefill_chunk_size=20,
-                    kv_cache_num_blocks=22, kv_cache_block_size=16, ignore_eos=True, dtype="float32", max_context=256)
+                    kv_cache_num_blocks=13, kv_cache_block_size=16, ignore_eos=True, dtype="float32", max_context=256)
     requests, step = {}, 0
     while len(requests) < len(jobs) or engine.scheduler.waiting or engine.scheduler.running:
         for index, job in enumerate(jobs):
@@ -229,3 +229,96 @@ def test_random_serving_schedule_in_bfloat16_at_head_dim_128(tiny_folders):
         tokens = requests[index].generated_token_ids
         assert len(tokens) == job["new"]
         assert_tokens_are_argmax_of_plain(folder, job["prompt"], tokens, "bfloat16", job["temperature"], job["seed"])
+
+
+def run_alone(model, prompt, new_tokens, temperature=0.0, seed=0, block=16):
+    from llmserver_b200 import Engine
+    alone = Engine(model, max_new_tokens=new_tokens, max_batch_size=1, max_num_batched_tokens=512, kv_cache_num_blocks=40,
+                   kv_cache_block_size=block, ignore_eos=True, prefix_caching=False, cuda_graphs=False, max_context=512)
+    request = alone.add_request(prompt_token_ids=prompt, temperature=temperature, seed=seed)
+    while alone.step():
+        pass
+    return request.generated_token_ids
+
+
+@pytest.mark.parametrize("name,dtype", [("b", "float32"), ("e", "bfloat16")])
+def test_a_request_put_out_between_replayed_steps_reads_its_new_pages(tiny_folders, name, dtype):
+    """Three requests decode through the graph of four rows; the youngest is put out, waits at the head of the queue,
+    has its cache rebuilt in other pages beside the two others' decode tokens, and returns to the same row beside the
+    same neighbours.  The replayed step must read its new pages: a graph that recognised rows by request id kept the
+    old ones, read pages that now belong to nobody and wrote the new token's keys into them."""
+    from llmserver_b200 import Engine
+    folder, vocab = tiny_folders[name], TINY[name][0]["vocab_size"]
+    prompts = [tokens_for(vocab, length, 300 + length) for length in (23, 40, 31)]
+    engine = Engine(folder, max_new_tokens=36, max_batch_size=4, max_num_batched_tokens=128, kv_cache_num_blocks=40,
+                    kv_cache_block_size=16, ignore_eos=True, dtype=dtype, prefix_caching=False, max_context=256)
+    requests = [engine.add_request(prompt_token_ids=prompt) for prompt in prompts]
+    while engine.step_function.graph_steps < 4:
+        assert engine.step()
+    before = engine.step_function.graph_steps
+    old_pages = [list(engine.cache.table(requests[2].request_id, group)) for group in range(len(engine.cache.groups))]
+    # other requests come and go in between, so that the freed pages are taken and the free list moves on
+    engine.put_out(requests[2])
+    filler = engine.add_request(prompt_token_ids=tokens_for(vocab, 50, 77), max_new_tokens=1)
+    engine.scheduler.waiting.rotate(1)        # the filler first: it takes the pages the victim gave back
+    engine.step()
+    assert len(filler.generated_token_ids) == 1
+    while requests[2].status.value != "Decoding":
+        engine.step()
+    new_pages = [list(engine.cache.table(requests[2].request_id, group)) for group in range(len(engine.cache.groups))]
+    assert new_pages != old_pages
+    while engine.step():
+        pass
+    assert engine.step_function.graph_steps > before + 5 and requests[2].times_put_out == 1
+    for prompt, request in zip(prompts, requests):
+        assert len(request.generated_token_ids) == 36
+        if dtype == "float32":
+            assert request.generated_token_ids == run_alone(engine.model, prompt, 36)
+        assert_tokens_are_argmax_of_plain(folder, prompt, request.generated_token_ids, dtype)
+    engine.cache.check_invariants()
+    assert engine.cache.available() == engine.cache.capacity()
+
+
+def test_a_tight_cache_puts_the_youngest_out_under_graphs_and_changes_no_token(tiny_folders):
+    """Three requests that together outgrow the cache, graphs on: the youngest gives way, the others go on through the
+    graph of two rows, it returns later; every request's tokens are those it produces alone."""
+    from llmserver_b200 import Engine
+    folder = tiny_folders["b"]
+    prompts = [tokens_for(509, length, 400 + length) for length in (20, 27, 30)]
+    engine = Engine(folder, max_new_tokens=48, max_batch_size=4, max_num_batched_tokens=96, kv_cache_num_blocks=12,
+                    kv_cache_block_size=16, ignore_eos=True, dtype="float32", prefix_caching=False, max_context=128)
+    requests = [engine.add_request(prompt_token_ids=prompt) for prompt in prompts]
+    while engine.step():
+        pass
+    assert engine.stats["preemptions"] > 0 and engine.step_function.graph_steps > 20
+    assert requests[0].times_put_out == 0
+    for prompt, request in zip(prompts, requests):
+        assert request.generated_token_ids == run_alone(engine.model, prompt, 48)
+    engine.cache.check_invariants()
+    assert engine.cache.available() == engine.cache.capacity()
+
+
+def test_warmup_leaves_nothing_to_tune_or_capture_and_the_step_profile_adds_up(tiny_folders):
+    from llmserver_b200 import Engine
+    from llmserver_b200.ops import gemm_bf16
+    folder = tiny_folders["e"]
+    engine = Engine(folder, max_new_tokens=12, max_batch_size=4, max_num_batched_tokens=96, kv_cache_num_blocks=40,
+                    kv_cache_block_size=16, ignore_eos=True, dtype="bfloat16", max_context=256)
+    report = engine.warmup()
+    assert report["graphs"] == [1, 2, 4]
+    engine.cache.check_invariants()
+    assert engine.cache.available() == engine.cache.capacity() and not engine.cache.requests
+    tuned, captured = gemm_bf16.tunings(), dict(engine.step_function.graphs.graphs)
+    prompts = [tokens_for(333, length, 800 + length) for length in (9, 33, 60, 17)]
+    generated = engine.generate(prompts)
+    assert gemm_bf16.tunings() == tuned, "a product was tuned inside a step after warmup()"
+    assert engine.step_function.graphs.graphs == captured, "a graph was captured inside a step after warmup()"
+    assert engine.step_function.graph_steps >= 8
+    for prompt, tokens in zip(prompts, generated):
+        assert_tokens_are_argmax_of_plain(folder, prompt, tokens, "bfloat16")
+    profile = engine.step_profile()
+    parts = sum(profile[name] for name in ("schedule", "pack_copy", "launch", "read_back", "accept"))
+    assert 0 < parts <= profile["step"] * 1.001
+    with pytest.raises(RuntimeError):
+        engine.add_request(prompt_token_ids=[1, 2, 3])
+        engine.warmup()
