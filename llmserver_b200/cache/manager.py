@@ -124,8 +124,12 @@ class CacheManager:
         self.slots = StateSlots(num_slots)
         self.requests: Dict[object, int] = {}   # request -> tokens that have a slot in every group
         self.has_windows = any(group.window is not None for group in self.groups)
+        # A prefix can be skipped only if every layer's cache of it is at hand.  Groups that keep every key qualify:
+        # what their pages hold is a function of the prefix alone, and each keeps a digest chain of its own.  A
+        # windowed group gives pages back and per-request state is not kept in pages at all, so a model with
+        # either recomputes its prompts.
         only_full = not self.has_windows and not self.state_entries
-        self.prefix_sharing = bool(prefix_sharing and only_full and len(self.groups) == 1)
+        self.prefix_sharing = bool(prefix_sharing and only_full and self.groups)
         self.model_identity = model_identity
         self.device = None
         self.dtype = None
@@ -271,57 +275,62 @@ class CacheManager:
         payload = json.dumps([parent, list(tokens), self.model_identity, "none"], separators=(",", ":")).encode("utf-8")
         return hashlib.sha256(payload).hexdigest()
 
-    def share_prefix(self, request_id, prompt: Sequence[int]) -> int:
-        """Takes over cached pages for the longest known prefix of complete blocks, leaving at least
-        one token to compute (utils/engine.py:197-208).  Returns the number of tokens covered."""
-        if not self.prefix_sharing or not self.groups:
-            return 0
-        group = self.groups[0]
-        table = group.tables[request_id]
-        if table:
-            raise KVCacheStateError("shared prefixes are looked up before anything is allocated")
-        parent, covered = "root", 0
+    def _prompt_digests(self, prompt: Sequence[int]):
+        """Chain digests of the prompt's complete blocks that may be shared: all but the block holding the last
+        token, so that at least one token is left to compute (utils/engine.py:197-208)."""
+        parent = "root"
         for block in range((len(prompt) - 1) // self.page_size):
-            digest = self.block_digest(parent, prompt[block * self.page_size:(block + 1) * self.page_size])
-            if group.pool.share(digest, table) is None:
+            parent = self.block_digest(parent, prompt[block * self.page_size:(block + 1) * self.page_size])
+            yield parent
+
+    def share_prefix(self, request_id, prompt: Sequence[int]) -> int:
+        """Takes over cached pages for the longest prefix of complete blocks that EVERY group still holds.  Returns the
+        number of tokens covered."""
+        if not self.prefix_sharing:
+            return 0
+        tables = [group.tables[request_id] for group in self.groups]
+        if any(tables):
+            raise KVCacheStateError("shared prefixes are looked up before anything is allocated")
+        covered = 0
+        for digest in self._prompt_digests(prompt):
+            if any(group.pool.lookup(digest) is None for group in self.groups):
                 break
+            for group, table in zip(self.groups, tables):
+                group.pool.share(digest, table)
             covered += self.page_size
-            parent = digest
         self.requests[request_id] = covered
         return covered
 
     def probe_prefix(self, prompt: Sequence[int]):
-        """What ``share_prefix`` would do, without doing it: (tokens covered, how many of the pages
-        taken are idle now and would stop counting as available)."""
-        if not self.prefix_sharing or not self.groups:
+        """What ``share_prefix`` would do, without doing it: (tokens covered, how many of the pages taken are idle
+        now and would stop counting as available; with several groups, the most in any of them)."""
+        if not self.prefix_sharing:
             return 0, 0
-        pool = self.groups[0].pool
-        parent, covered, idle = "root", 0, 0
-        for block in range((len(prompt) - 1) // self.page_size):
-            digest = self.block_digest(parent, prompt[block * self.page_size:(block + 1) * self.page_size])
-            page = pool.lookup(digest)
-            if page is None:
+        covered, idle = 0, [0] * len(self.groups)
+        for digest in self._prompt_digests(prompt):
+            pages = [group.pool.lookup(digest) for group in self.groups]
+            if any(page is None for page in pages):
                 break
-            idle += page in pool.idle
+            for index, (group, page) in enumerate(zip(self.groups, pages)):
+                idle[index] += page in group.pool.idle
             covered += self.page_size
-            parent = digest
-        return covered, idle
+        return covered, max(idle)
 
     def register_prefix(self, request_id, prompt: Sequence[int], old_computed: int, new_computed: int) -> None:
-        """Hashes the prompt blocks completed by the step that moved the request from ``old_computed``
-        to ``new_computed`` tokens (utils/engine.py:382-401)."""
-        if not self.prefix_sharing or not self.groups:
+        """Hashes, in every group, the prompt blocks completed by the step that moved the request from
+        ``old_computed`` to ``new_computed`` tokens (utils/engine.py:382-401)."""
+        if not self.prefix_sharing:
             return
-        group = self.groups[0]
-        table = group.tables[request_id]
         first = min(old_computed, len(prompt)) // self.page_size
         last = min(new_computed, len(prompt)) // self.page_size
-        for block in range(first, last):
-            parent = "root" if block == 0 else group.pool.digest_of.get(table[block - 1])
-            if parent is None:
-                return
-            digest = self.block_digest(parent, prompt[block * self.page_size:(block + 1) * self.page_size])
-            group.pool.register_digest(table[block], digest)
+        for group in self.groups:
+            table = group.tables[request_id]
+            for block in range(first, last):
+                parent = "root" if block == 0 else group.pool.digest_of.get(table[block - 1])
+                if parent is None:
+                    break
+                digest = self.block_digest(parent, prompt[block * self.page_size:(block + 1) * self.page_size])
+                group.pool.register_digest(table[block], digest)
 
     # ------------------------------------------------------------------ checks
     def check_invariants(self) -> None:

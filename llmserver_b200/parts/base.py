@@ -74,6 +74,11 @@ class FeedForward(Part):
 class Norm(Part):
     def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor],
                  rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """residual += delta (when delta is given), then the normalised stream in the activation type."""
+        raise NotImplementedError
+
+    def norm(self, x: torch.Tensor) -> torch.Tensor:
+        """Normalises activations that are not the stream (a sub-layer's output, in blocks that do so)."""
         raise NotImplementedError
 
 

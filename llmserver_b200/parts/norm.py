@@ -26,3 +26,6 @@ class RMSNorm(Norm):
 
     def add_norm(self, residual, delta, rows=None):
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, rows=rows, act_dtype=self.runtime.dtype)
+
+    def norm(self, x):
+        return ops.rmsnorm(x, self.weight, self.eps)

@@ -175,6 +175,37 @@ def test_shared_prefix_blocks():
     assert not make([FULL, StateNeed((1,))], sharing=True).prefix_sharing
 
 
+def test_shared_prefix_across_two_groups_of_full_attention():
+    """Two groups that keep every key (other head sizes): each keeps its own digest chain; a prefix is taken over only
+    as far as both still hold it."""
+    other_shape = KVPagesNeed(1, 8, None)
+    cache = make([FULL, other_shape, FULL], pages=6, page_size=4, sharing=True)
+    assert cache.prefix_sharing and len(cache.groups) == 2
+    prompt = list(range(13))
+    cache.admit("a")
+    cache.ensure("a", 13)
+    cache.register_prefix("a", prompt, 0, 13)              # three complete blocks in both groups
+    assert [len(group.pool.digest_of) for group in cache.groups] == [3, 3]
+    cache.admit("b")
+    assert cache.probe_prefix(prompt) == (12, 0)
+    assert cache.share_prefix("b", prompt) == 12
+    assert [cache.table("b", group) == cache.table("a", group)[:3] for group in (0, 1)] == [True, True]
+    cache.free("a")
+    cache.free("b")
+    assert cache.probe_prefix(prompt) == (12, 3)
+    # the second group loses its cached blocks (another request takes every page there); the first still has them:
+    # nothing can be skipped, since the second group's layers would have no keys for the prefix
+    pool = cache.groups[1].pool
+    held = [pool.allocate() for _ in range(pool.num_available)]
+    assert cache.probe_prefix(prompt) == (0, 0)
+    cache.admit("c")
+    assert cache.share_prefix("c", prompt) == 0 and cache.table("c", 0) == []
+    for page in held:
+        pool.release(page)
+    cache.free("c")
+    cache.check_invariants()
+
+
 @pytest.mark.parametrize("seed", range(6))
 def test_random_orders_never_lose_or_duplicate_a_page(seed):
     rng = random.Random(seed)

@@ -219,6 +219,55 @@ def test_attention_finds_a_far_key_and_respects_the_window_edge(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dim,rotary,interleaved,qk_norm", [(48, 24, True, True), (128, 64, False, True), (128, 128, True, False),
+                                                            (80, 2, False, True), (64, 0, False, True)])
+def test_rotation_of_a_part_of_the_head_and_of_interleaved_pairs(dtype, dim, rotary, interleaved, qk_norm):
+    """Only the first ``rotary`` elements of each head rotate, as halves or as neighbouring pairs; the rest is
+    normalised and passes through.  rotary 0 with no frequencies: no position encoding at all."""
+    from llmserver_b200 import ops
+    heads, kv_heads, page_size, theta, eps = 3, 1, 8, 10000.0, 1e-6
+    positions = torch.tensor([0, 1, 2, 3, 40, 41, 977], dtype=torch.int32)
+    total, width = positions.numel(), (heads + 2 * kv_heads) * dim
+    qkv = rand((total, width), dtype, 60)
+    q_weight = rand((dim,), dtype, 61) + 1 if qk_norm else None
+    k_weight = rand((dim,), dtype, 62) + 1 if qk_norm else None
+    n_pages = 977 // page_size + 2
+    tables = torch.arange(n_pages, dtype=torch.int32).flip(0).reshape(1, -1).contiguous()
+    k_pages = torch.zeros((n_pages, kv_heads, page_size, dim), dtype=dtype, device=DEVICE)
+    v_pages = torch.zeros_like(k_pages)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEVICE)
+    inv_freq = (1.0 / (theta ** (torch.arange(0, rotary, 2).float() / rotary))).to(DEVICE) if rotary else None
+    work = qkv.clone()
+    ops.qk_norm_rope_kv_write(work, q_weight, k_weight, inv_freq, positions.to(DEVICE), torch.zeros(total, dtype=torch.int32, device=DEVICE),
+                              tables.to(DEVICE), k_pages, v_pages, heads, kv_heads, dim, eps, True, flag,
+                              rotary_dim=rotary if rotary else None, interleaved=interleaved)
+    assert flag.item() == 0
+    source = qkv.double().cpu()
+    q = source[:, :heads * dim].view(total, heads, dim)
+    k = source[:, heads * dim:(heads + kv_heads) * dim].view(total, kv_heads, dim)
+    if qk_norm:
+        q, k = plain_model.rms_norm(q, q_weight.double().cpu(), eps), plain_model.rms_norm(k, k_weight.double().cpu(), eps)
+
+    def rotated(x):
+        if not rotary:
+            return x
+        angles = (positions.float().unsqueeze(-1) * inv_freq.cpu().view(1, -1)).double()
+        cosine, sine = torch.cos(angles).unsqueeze(1), torch.sin(angles).unsqueeze(1)
+        out = x.clone()
+        first, second = (slice(0, rotary, 2), slice(1, rotary, 2)) if interleaved else (slice(0, rotary // 2), slice(rotary // 2, rotary))
+        out[..., first] = x[..., first] * cosine - x[..., second] * sine
+        out[..., second] = x[..., second] * cosine + x[..., first] * sine
+        return out
+
+    close(work[:, :heads * dim], rotated(q).reshape(total, -1), dtype, "rotated q")
+    got_k = torch.stack([k_pages[tables[0, p // page_size].item(), :, p % page_size] for p in positions.tolist()])
+    close(got_k, rotated(k), dtype, "cached k")
+    with pytest.raises(ops.KernelError):
+        ops.qk_norm_rope_kv_write(work, q_weight, k_weight, inv_freq, positions.to(DEVICE), torch.zeros(total, dtype=torch.int32, device=DEVICE),
+                                  tables.to(DEVICE), k_pages, v_pages, heads, kv_heads, dim, eps, True, flag, rotary_dim=dim + 2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,dim,page_size,qk_norm", [(4, 2, 16, 4, True), (6, 1, 48, 16, True),
                                                                   (8, 8, 128, 16, False), (5, 5, 80, 3, True)])
 def test_qk_norm_rope_kv_write(dtype, heads, kv_heads, dim, page_size, qk_norm):

@@ -154,7 +154,7 @@ def test_pre_norm_block_alone(dtype):
             plain_weights[prefix + name] = weights[name].double()
         parts[role] = cls(params, {k: v.to(DEVICE) for k, v in weights.items()}, run)
     parts["mixer"].attach(POSITION_ENCODINGS.get("rotary")({"head_dim": dim, "theta": theta}, {}, run))
-    block = BLOCKS.get("pre_norm")({}, parts["mixer"], parts["feed_forward"], parts["mixer_norm"], parts["feed_forward_norm"])
+    block = BLOCKS.get("pre_norm")({}, parts)
     tokens = 23
     stream, pending = rand((tokens, hidden), 70), rand((tokens, hidden), 71).to(dtype)
     pages = torch.zeros((2, 8, kv_heads, 4, dim), dtype=dtype, device=DEVICE)
