@@ -24,242 +24,88 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936, hidden_size=4096,
-                intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,
-                head_dim=128, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
-                max_position_embeddings=40960, hidden_act="silu", attention_bias=False, use_sliding_window=False)
-CONTEXT = 4096          # prompts of 2048 tokens decoded to 4096
-PROMPT = 2048
-MEAN_DECODE_CONTEXT = (CONTEXT + PROMPT) // 2
-PAGE_SIZE = 16
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+from llmserver_b200.cli.harness import (CONTEXT, MEAN_DECODE_CONTEXT, PAGE_SIZE, PROMPT, QWEN3_8B, ClockSampler,  # noqa: E402
+                                        Harness, decode_bytes, prefill_flops, read_peaks)
 
 
-def read_peaks():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.isfile(path):
+def reference_arm(args) -> int:
+    """Runs the unmodified reference (a copy of its files under baseline/_ref) on the same metric and configuration, in
+    a process of its own that imports nothing of this package: ``baseline/reference_arm.py`` drives the reference's
+    ``model_loader`` and ``Engine`` over a model folder with seeded random weights of the benchmark's shape, which is
+    written here first.  Whatever stops it is printed as ``unavailable`` in its own words."""
+    import shutil
+    import subprocess
+    import tempfile
+
+    line = {"impl": "reference", "metric": "decode tok/s (Qwen3-8B shape, batch 8, context 4096)", "unit": "tokens/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic: seeded random weights N(0,0.02), uniform random token ids"}
+
+    def unavailable(why: str) -> int:
+        print(json.dumps({"impl": "reference", "unavailable": " ".join(why.split())[:700]}))
+        return 0
+
+    reference = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isfile(os.path.join(reference, "utils", "engine.py")):
+        return unavailable("baseline/_ref does not hold the reference's files: pip cannot install AshvinSehgal/LLMServer (it has "
+                           "neither setup.py nor pyproject.toml), so it runs from a plain copy of its files, which is missing here")
+    if args.gpus != 1:
+        return unavailable("the reference's engine is measured on one GPU, like this one")
+    import torch
+    import llmserver_b200.models  # noqa: F401  (registers the architecture)
+    from llmserver_b200.config import Qwen3Config
+    from llmserver_b200.weights import write_model_folder
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA device is visible")
+    raw = dict(QWEN3_8B, num_hidden_layers=args.layers, bos_token_id=1, eos_token_id=2, pad_token_id=0)
+    free = {path: shutil.disk_usage(path).free for path in ("/dev/shm", tempfile.gettempdir()) if os.path.isdir(path)}
+    need = 2.2 * (args.layers * 0.2e9 + 1.3e9) + (1 << 30)
+    places = [path for path, room in free.items() if room > need]
+    if not places:
+        return unavailable(f"no room for the {need / 1e9:.0f} GB model folder the reference's loader reads: free space {free}")
+    folder = tempfile.mkdtemp(prefix="llmserver_b200_ref_", dir=places[0])
+    try:
+        write_model_folder(Qwen3Config.from_dict(raw), folder, 0, torch.bfloat16, device="cuda:0")
+        with open(os.path.join(folder, "config.json")) as handle:
+            config_json = json.load(handle)
+        config_json.update(bos_token_id=1, eos_token_id=2, pad_token_id=0, torch_dtype="bfloat16")
+        with open(os.path.join(folder, "config.json"), "w") as handle:
+            json.dump(config_json, handle)
+        with open(os.path.join(folder, "generation_config.json"), "w") as handle:
+            json.dump({"bos_token_id": 1, "eos_token_id": 2, "pad_token_id": 0}, handle)
+        torch.cuda.empty_cache()
+        command = [sys.executable, os.path.join(ROOT, "baseline", "reference_arm.py"), "--model", folder, "--batch", str(args.batch),
+                   "--steps", str(args.steps), "--warmup", str(max(args.warmup, 3)), "--context-mean", str(MEAN_DECODE_CONTEXT),
+                   "--context", str(CONTEXT), "--block-size", str(PAGE_SIZE)]
+        environment = dict(os.environ, HF_HUB_OFFLINE="1", TRANSFORMERS_OFFLINE="1", PYTHONPATH=reference)
         try:
-            with open(path) as handle:
-                raw = json.load(handle)
-            peaks = {key: float(raw[key]) for key in FALLBACK_PEAKS if key in raw}
-            if "hbm_gbs" in peaks and "bf16_tflops" in peaks:
-                peaks.setdefault("bf16_tflops_sustained", peaks["bf16_tflops"])
-                return peaks, "measured"
-        except (OSError, ValueError, KeyError, TypeError):
-            pass
-    return dict(FALLBACK_PEAKS), "fallback"
-
-
-class ClockSampler:
-    """Samples SM clocks and throttle reasons through NVML while the timed region runs (reads only)."""
-
-    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
-
-    def __init__(self, index: int = 0, period: float = 0.1):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
-        self.period, self.index = period, index
-        self._stop = threading.Event()
-        self._thread = None
+            done = subprocess.run(command, capture_output=True, text=True, timeout=1500, env=environment, cwd=reference)
+        except subprocess.TimeoutExpired:
+            return unavailable("the reference did not finish within 1500 s")
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+    result = None
+    for text in reversed(done.stdout.strip().splitlines()):
         try:
-            import pynvml
-            pynvml.nvmlInit()
-            self.nvml = pynvml
-            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
-        except Exception:  # NVML missing: report nothing rather than fail the benchmark
-            self.nvml = None
-
-    def _loop(self):
-        while not self._stop.is_set():
-            try:
-                self.samples.append(self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM))
-                mask = self.nvml.nvmlDeviceGetCurrentClocksEventReasons(self.handle) if hasattr(
-                    self.nvml, "nvmlDeviceGetCurrentClocksEventReasons") else self.nvml.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
-                for bit, name in self.REASONS.items():
-                    if mask & bit:
-                        self.reasons.add(name)
-            except Exception:
-                pass
-            self._stop.wait(self.period)
-
-    def __enter__(self):
-        if self.nvml is not None:
-            self._thread = threading.Thread(target=self._loop, daemon=True)
-            self._thread.start()
-        return self
-
-    def __exit__(self, *exc):
-        self._stop.set()
-        if self._thread is not None:
-            self._thread.join()
-
-    def summary(self):
-        ordered = sorted(self.samples)
-        return {"sm_mhz": ordered[len(ordered) // 2] if ordered else None, "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons)}
-
-
-def decode_bytes(config, layers: int, batch: int, context: int) -> float:
-    """Bytes one decode step has to read: every weight it uses once, and the cache of the live requests."""
-    hidden, inter, dim = config.hidden_size, config.intermediate_size, config.head_dim
-    heads, kv_heads = config.num_attention_heads, config.num_key_value_heads
-    per_layer = ((heads + 2 * kv_heads) * dim * hidden + hidden * heads * dim + 3 * hidden * inter + 2 * hidden + 2 * dim) * 2
-    head = config.vocab_size * hidden * 2
-    cache = 2 * kv_heads * dim * 2 * layers * batch * context
-    return layers * per_layer + head + hidden * 2 + cache
-
-
-def prefill_flops(config, layers: int, tokens: int) -> float:
-    hidden, inter, dim = config.hidden_size, config.intermediate_size, config.head_dim
-    heads, kv_heads = config.num_attention_heads, config.num_key_value_heads
-    linear = 2 * tokens * ((heads + 2 * kv_heads) * dim * hidden + hidden * heads * dim + 3 * hidden * inter)
-    attention = 2 * 2 * heads * dim * tokens * (tokens + 1) / 2      # QK^T and PV over the causal half
-    return layers * (linear + attention) + 2 * config.vocab_size * hidden   # logits of the last token only
-
-
-class Harness:
-    """Model, cache and step function sized for the largest batch, reused by every measurement."""
-
-    def __init__(self, layers: int, max_batch: int, seed: int = 0):
-        import torch
-        from llmserver_b200.cache import CacheManager
-        from llmserver_b200.config import Qwen3Config
-        from llmserver_b200.engine.step import StepFunction
-        from llmserver_b200.models import random_model
-
-        self.torch = torch
-        raw = dict(QWEN3_8B, num_hidden_layers=layers)
-        self.config = Qwen3Config.from_dict(raw)
-        self.layers = layers
-        self.model = random_model(self.config, seed, "bfloat16", "cuda:0")
-        pages = max_batch * (CONTEXT // PAGE_SIZE) + 8     # the reference benchmark's sizing rule
-        self.cache = CacheManager(self.model.cache_needs(), PAGE_SIZE, pages, num_slots=max_batch, prefix_sharing=False)
-        self.cache.materialize(self.model.runtime.device, self.model.runtime.dtype)
-        for group in self.cache.groups:     # contents do not change the timing; avoid an all-zero cache anyway
-            group.storage.normal_(0.0, 0.5)
-        self.step_function = StepFunction(self.model, self.cache)
-        self.generator = torch.Generator().manual_seed(seed)
-
-    def tokens(self, count: int):
-        return self.torch.randint(0, self.config.vocab_size, (count,), generator=self.generator).tolist()
-
-    def place(self, batch: int, context: int):
-        """Puts ``batch`` requests at ``context`` cached tokens each (pages allocated, contents as they are)."""
-        for request_id in list(self.step_function.computed):
-            self.step_function.release(request_id)
-        ids = [f"b{index}" for index in range(batch)]
-        for request_id in ids:
-            self.step_function.admit(request_id)
-            self.cache.ensure(request_id, context)
-            self.step_function.computed[request_id] = context
-        return ids
-
-    def time_decode(self, batch: int, steps: int, warmup: int):
-        torch = self.torch
-        from llmserver_b200 import ops
-        start_context = max(1, MEAN_DECODE_CONTEXT - steps // 2 - warmup)
-        ids = self.place(batch, start_context)
-        from llmserver_b200.sampling import SamplingRow
-        if self.step_function.graphs is None:
-            self.step_function.enable_graphs(CONTEXT, 64)
-        tokens = self.tokens(batch)
-        events = []
-        launches_before = None
-        rows = [SamplingRow() for _ in ids]
-        for step in range(warmup + steps):
-            if step == warmup:
-                torch.cuda.synchronize()
-                launches_before = ops.launch_count()
-            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            begin.record()
-            # one decode step: batch in (one copy), forward, sampling, tokens out (one copy)
-            tokens = self.step_function.run_and_sample([(request_id, [token], [0]) for request_id, token in zip(ids, tokens)], rows)
-            end.record()
-            if step >= warmup:
-                events.append((begin, end))
-        torch.cuda.synchronize()
-        launches = ops.launch_count() - launches_before
-        if self.step_function.graph_steps:      # replayed steps launch the captured kernels: count them per step
-            launches = steps * self.launches_per_step(batch)
-        self.step_function.check_errors()
-        times = [begin.elapsed_time(end) for begin, end in events]
-        total_ms = sum(times)
-        mean_context = start_context + warmup + (steps + 1) / 2
-        return {"ms_per_step": total_ms / steps, "tokens_per_s": batch * steps / (total_ms / 1e3),
-                "launches": launches, "mean_context": mean_context}
-
-    def launches_per_step(self, batch: int) -> int:
-        """Kernels of this package in one decode step, counted on an eager step of the same shape."""
-        from llmserver_b200 import ops
-        ids = list(self.step_function.computed)[:batch]
-        graphs, self.step_function.graphs = self.step_function.graphs, None
-        before = ops.launch_count()
-        self.step_function.run([(request_id, [0], [0]) for request_id in ids])
-        count = ops.launch_count() - before + 1     # + the sampling kernel
-        self.step_function.graphs = graphs
-        return count
-
-    def time_prefill(self, tokens: int, repeats: int = 3):
-        torch = self.torch
-        best = None
-        for _ in range(repeats + 1):     # the first run warms up
-            for request_id in list(self.step_function.computed):
-                self.step_function.release(request_id)
-            self.step_function.admit("p")
-            prompt = self.tokens(tokens)
-            torch.cuda.synchronize()
-            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            begin.record()
-            self.step_function.run([("p", prompt, [tokens - 1])])
-            end.record()
-            torch.cuda.synchronize()
-            elapsed = begin.elapsed_time(end)
-            best = elapsed if best is None else min(best, elapsed)
-        self.step_function.release("p")
-        return best
-
-    def time_e2e(self, batch: int, steps: int, warmup: int):
-        """The same decode through the public entry point: host token ids in, sampled ids out; every
-        step copies its batch from pinned host memory and reads the sampled tokens back."""
-        torch = self.torch
-        from llmserver_b200.engine.engine import Engine
-        from llmserver_b200.engine.request import RequestStatus
-
-        for request_id in list(self.step_function.computed):
-            self.step_function.release(request_id)
-        prompt_len = max(1, MEAN_DECODE_CONTEXT - steps // 2 - warmup)
-        # the engine shares the model and the cache that are already on the device
-        # requests that finish their prompt first decode while the others still prefill: leave room for that
-        prefill_steps = -(-batch * prompt_len // max(8192, batch)) + 2
-        engine = Engine(self.model, max_new_tokens=warmup + steps + prefill_steps + 8, max_batch_size=batch,
-                        max_num_batched_tokens=max(8192, batch), ignore_eos=True, cache=self.cache,
-                        step_function=self.step_function)
-        requests = [engine.add_request(prompt_token_ids=self.tokens(prompt_len)) for _ in range(batch)]
-        while any(request.status != RequestStatus.DECODING for request in requests):
-            engine.step()
-        for _ in range(warmup):
-            engine.step()
-        torch.cuda.synchronize()
-        before = sum(len(request.generated_token_ids) for request in requests)
-        started = time.perf_counter()
-        for _ in range(steps):
-            engine.step()
-        torch.cuda.synchronize()
-        elapsed = time.perf_counter() - started
-        generated = sum(len(request.generated_token_ids) for request in requests) - before
-        if generated != batch * steps:
-            raise RuntimeError(f"the timed steps produced {generated} tokens, not {batch} x {steps}")
-        h2d = engine.step_function.last_batch_bytes
-        for request in requests:
-            engine.cancel_request(request.request_id)
-        return {"value": batch * steps / elapsed, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": batch * 4, "ms_per_step": elapsed * 1e3 / steps}
-
-
-def reference_arm():
-    line = {"impl": "reference",
-            "unavailable": "AshvinSehgal/LLMServer has no setup.py or pyproject.toml, so pip cannot install it into baseline/_ref; "
-                           "its job files also exclude compute capability >= 10 and it needs Hugging Face weights from the network"}
+            result = json.loads(text)
+            break
+        except ValueError:
+            continue
+    if result is None:
+        tail = (done.stderr or done.stdout).strip().splitlines()[-3:]
+        return unavailable(f"the reference's process ended with code {done.returncode}: " + " | ".join(tail))
+    if "unavailable" in result:
+        return unavailable("the reference failed on this box: " + result["unavailable"])
+    config = Qwen3Config.from_dict(raw)
+    line.update(value=round(result["value"], 1), ms_per_step=round(result["ms_per_step"], 4),
+                e2e={key: (round(value, 1) if isinstance(value, float) else value) for key, value in result["e2e"].items()},
+                config={"model": "Qwen3-8B shape", "layers": args.layers, "layers_full": QWEN3_8B["num_hidden_layers"],
+                        "hidden": config.hidden_size, "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,
+                        "head_dim": config.head_dim, "intermediate": config.intermediate_size, "vocab": config.vocab_size,
+                        "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT,
+                        "decode_context_mean": round(result["mean_context"]), "page_size": PAGE_SIZE, "parallelism": "none (1 GPU)",
+                        "path": "utils.model_loader + utils.engine.Engine, paged decode, CUDA graphs"},
+                reference={key: result[key] for key in ("load_s", "prefill_s", "graphs", "paged_decode") if key in result})
     print(json.dumps(line))
     return 0
 
@@ -275,8 +121,10 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
     args = parser.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (the engine has no multi-GPU path)")
         return 2

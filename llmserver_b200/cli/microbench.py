@@ -165,12 +165,10 @@ def bench_step(args, prefill: bool) -> dict:
     """One model step of the 8B layer sizes with ``--layers`` layers (decode at ``--context`` or a prompt)."""
     import torch
 
-    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-    sys.path.insert(0, root)
-    import bench
     from .. import ops
+    from .harness import Harness
 
-    harness = bench.Harness(args.layers, 1 if prefill else args.batch)
+    harness = Harness(args.layers, 1 if prefill else args.batch)
     if prefill:
         def once():
             for request_id in list(harness.step_function.computed):

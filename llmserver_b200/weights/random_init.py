@@ -48,21 +48,42 @@ class RandomSource:
         return tensor if declaration.kind == TABLE else tensor.to(self.dtype)
 
 
-def write_model_folder(config, folder: str, seed: int, dtype: torch.dtype = torch.bfloat16) -> str:
-    """Writes ``config.json`` and ``model.safetensors`` for the typed ``config`` (any registered
-    architecture's configuration class).  Values are drawn in float32 on the CPU and stored as ``dtype``."""
+def write_model_folder(config, folder: str, seed: int, dtype: torch.dtype = torch.bfloat16, device="cpu",
+                       shard_bytes: int = 4 << 30) -> str:
+    """Writes ``config.json`` and the weights for the typed ``config`` (any registered architecture's configuration
+    class): ``model.safetensors``, or, when the tensors exceed ``shard_bytes``, numbered shards with a
+    ``model.safetensors.index.json`` (so a large model never sits in host memory whole).  Values are drawn in float32
+    on ``device`` (the CPU by default; a GPU draws other values from the same seed, much faster) and stored as ``dtype``."""
     from safetensors.torch import save_file
 
     from ..config.registry import architecture_of
 
     raw = config.to_dict()
     spec = architecture_of(raw).build_spec(config)
-    tensors = {}
-    for name, declaration in declared_weights(spec).items():
-        tensor = random_tensor(name, declaration, seed, "cpu")
-        tensors[name] = tensor if declaration.kind == TABLE else tensor.to(dtype).contiguous()
     os.makedirs(folder, exist_ok=True)
     with open(os.path.join(folder, "config.json"), "w") as handle:
         json.dump(raw, handle, indent=2)
-    save_file(tensors, os.path.join(folder, "model.safetensors"))
+    wanted = declared_weights(spec)
+    sizes = {name: int(torch.tensor(declaration.shape).prod()) * (4 if declaration.kind == TABLE else torch.empty(0, dtype=dtype).element_size())
+             for name, declaration in wanted.items()}
+    shards, current, held = [], [], 0
+    for name in wanted:
+        if current and held + sizes[name] > shard_bytes:
+            shards.append(current)
+            current, held = [], 0
+        current.append(name)
+        held += sizes[name]
+    shards.append(current)
+    weight_map = {}
+    for index, names in enumerate(shards):
+        tensors = {}
+        for name in names:
+            tensor = random_tensor(name, wanted[name], seed, device)
+            tensors[name] = (tensor if wanted[name].kind == TABLE else tensor.to(dtype)).cpu().contiguous()
+        file_name = "model.safetensors" if len(shards) == 1 else f"model-{index + 1:05d}-of-{len(shards):05d}.safetensors"
+        save_file(tensors, os.path.join(folder, file_name))
+        weight_map.update({name: file_name for name in names})
+    if len(shards) > 1:
+        with open(os.path.join(folder, "model.safetensors.index.json"), "w") as handle:
+            json.dump({"metadata": {"total_size": sum(sizes.values())}, "weight_map": weight_map}, handle)
     return folder

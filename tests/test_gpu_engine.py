@@ -322,3 +322,27 @@ def test_warmup_leaves_nothing_to_tune_or_capture_and_the_step_profile_adds_up(t
     with pytest.raises(RuntimeError):
         engine.add_request(prompt_token_ids=[1, 2, 3])
         engine.warmup()
+
+
+def test_the_generate_command_prints_the_ids_the_engine_generates(tiny_folders):
+    import json
+    import os
+    import subprocess
+    import sys
+    folder = tiny_folders["a"]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    prompts = [tokens_for(256, 6, 21), tokens_for(256, 11, 22)]
+    command = [sys.executable, "-m", "llmserver_b200.cli.generate", "--model", folder, "--dtype", "float32", "--block-size", "4",
+               "--max-new-tokens", "7", "--ignore-eos"]
+    for prompt in prompts:
+        command += ["--prompt-ids", ",".join(str(token) for token in prompt)]
+    done = subprocess.run(command, capture_output=True, text=True, cwd=root, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    lines = done.stdout.strip().splitlines()
+    assert [[int(token) for token in line.split(",")] for line in lines] == [plain_greedy(folder, prompt, 7) for prompt in prompts]
+    done = subprocess.run(command + ["--json", "--temperature", "0.7", "--seed", "5"], capture_output=True, text=True, cwd=root, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    report = json.loads(done.stdout.strip().splitlines()[-1])
+    assert [len(tokens) for tokens in report["generated"]] == [7, 7] and report["finish_reasons"] == ["length", "length"]
+    for index, (prompt, tokens) in enumerate(zip(prompts, report["generated"])):
+        assert_tokens_are_argmax_of_plain(folder, prompt, tokens, "float32", 0.7, 5 + index)
