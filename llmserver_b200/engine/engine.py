@@ -76,6 +76,9 @@ class Engine:
         self.cuda_graphs = (self.device.type == "cuda") if cuda_graphs is None else bool(cuda_graphs)
         if self.cuda_graphs and self.step_function.graphs is None:
             self.step_function.enable_graphs(min(max_context, self.num_blocks * self.block_size), max_batch_size)
+        # with ``record_steps`` set, every step leaves (decode rows, prompt tokens, logits rows, cached tokens the step
+        # reads, (query, key) pairs its attention covers) in ``step_log``: what a benchmark needs to count bytes and FLOPs
+        self.record_steps, self.step_log = False, []
         self.stats = {"steps": 0, "preemptions": 0, "tokens": 0, "prefill_tokens": 0, "decode_tokens": 0, "prefix_tokens": 0,
                       "schedule_s": 0.0, "pack_copy_s": 0.0, "launch_s": 0.0, "read_back_s": 0.0, "accept_s": 0.0, "step_s": 0.0}
 
@@ -194,6 +197,11 @@ class Engine:
             if wants:
                 sampled.append(request)
         rows = [SamplingRow(request.temperature, request.seed, len(request.generated_token_ids)) for request in sampled]
+        if self.record_steps:
+            held = [(share.request.num_computed_tokens, share.tokens) for share in plan.shares]
+            self.step_log.append((len(plan.decoding), sum(share.tokens for share in plan.prompts), len(sampled),
+                                  sum(start + count for start, count in held),
+                                  sum(count * start + count * (count + 1) // 2 for start, count in held)))
         planned = clock()
         tokens = self.step_function.run_and_sample(entries, rows, self.sampler)
         ran = clock()
