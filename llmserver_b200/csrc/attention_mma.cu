@@ -22,6 +22,7 @@
 #include "common.cuh"
 #include "tma.cuh"
 #include "tcgen05.cuh"
+#include <stdlib.h>
 #include <type_traits>
 
 namespace {
@@ -50,6 +51,8 @@ struct AttnParams {
     int max_splits;
     float* partial_out;      // [N, Hq, max_splits, D]
     float* partial_ml;       // [N, Hq, max_splits, 2]
+    int cluster_merge;       // TMA decode kernel: the splits of a sequence form a thread-block cluster and merge their
+                             // partial results through distributed shared memory (no scratch, no merge kernel)
     int slot_by_seq;         // scratch slots are counted by sequence instead of by the sequence's token index
     int* error_flag;         // 3: a bounded wait of the TMA decode kernel ran out; 5: a block-table entry names no page
                              // of the pool; 6: a context needs more splits than max_splits (may be null)
@@ -108,6 +111,19 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
 __device__ __forceinline__ uint32_t pack_bf16(float low, float high) {
     __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
     return *reinterpret_cast<uint32_t*>(&pair);
+}
+
+// Thread-block cluster: a barrier over the threads of the cluster that have not exited, and a load from the shared
+// memory of another block of the cluster.
+__device__ __forceinline__ void cluster_arrive_wait() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float load_cluster(uint32_t local_address, uint32_t rank) {
+    uint32_t remote;
+    float value;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote) : "memory");
+    return value;
 }
 
 // Element offset of (row, 16-byte chunk) in a swizzled tile whose rows hold D bfloat16.
@@ -567,7 +583,16 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
     const int n_splits = (context - first_key + split_len - 1) / split_len;
     if (n_splits > p.max_splits && split == 0 && kv_head == 0 && threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 6);
     if (context <= 0 && split == 0) zero_output<D>(p, token, kv_head, group);     // nothing to attend to
-    if (split >= n_splits) return;
+    // every thread of a cluster whose splits merge in shared memory meets at the same two cluster barriers, also the
+    // blocks beyond the sequence's last split and the producer warps, which have nothing to add
+    const bool meets_cluster = p.cluster_merge && n_splits > 1;
+    if (split >= n_splits) {
+        if (meets_cluster) {
+            cluster_arrive_wait();
+            cluster_arrive_wait();
+        }
+        return;
+    }
     const int split_begin = first_key + split * split_len;
     const int split_end = min(split_begin + split_len, context);
     const int n_tiles = (split_end - split_begin + kTileKeys - 1) / kTileKeys;
@@ -620,6 +645,10 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
                     tma::load_2d(dst, my_v ? &map_v : &map_k, bar, my_half * 64, y);
                 }
             }
+        }
+        if (meets_cluster) {
+            cluster_arrive_wait();
+            cluster_arrive_wait();
         }
         return;
     }
@@ -696,6 +725,10 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
         }
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
+    // this split's result per head of the group: [16][D + 2] floats (normalised output, maximum, sum) behind the
+    // four warps' rows, for the splits that merge inside a cluster
+    float* mine = merge + (size_t)4 * 16 * (D + 2);
+    const bool in_cluster = meets_cluster;
     for (int index = threadIdx.x; index < group * D; index += kThreads) {
         const int r = index / D, d = index % D;
         float best = -INFINITY;
@@ -712,6 +745,12 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
         const int head = kv_head * group + r;
         if (n_splits == 1) {
             p.out[(size_t)token * p.n_q_heads * D + (size_t)head * D + d] = __float2bfloat16_rn(numerator / denominator);
+        } else if (in_cluster) {
+            mine[r * (D + 2) + d] = numerator / denominator;
+            if (d == 0) {
+                mine[r * (D + 2) + D] = best;
+                mine[r * (D + 2) + D + 1] = denominator;
+            }
         } else {
             const size_t slot = ((size_t)(p.slot_by_seq ? seq : token) * p.n_q_heads + head) * p.max_splits + split;
             p.partial_out[slot * D + d] = numerator / denominator;
@@ -720,6 +759,28 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
                 p.partial_ml[slot * 2 + 1] = denominator;
             }
         }
+    }
+    if (in_cluster) {
+        // The splits of this (sequence, kv head) are the ranks 0 .. n_splits - 1 of one cluster (ranks beyond have left
+        // already; a cluster barrier waits for threads that have not exited).  Every rank takes a share of the group's
+        // output elements and adds the splits' results in the order of the ranks, with the arithmetic of the merge
+        // kernel below, reading the other ranks' shared memory.
+        cluster_arrive_wait();
+        const uint32_t mine_address = smem_address(mine);
+        for (int index = split * kThreads + threadIdx.x; index < group * D; index += n_splits * kThreads) {
+            const int r = index / D, d = index % D;
+            float best = -INFINITY;
+            for (int s = 0; s < n_splits; ++s) best = fmaxf(best, load_cluster(mine_address + (uint32_t)(r * (D + 2) + D) * 4u, (uint32_t)s));
+            float numerator = 0.0f, denominator = 0.0f;
+            for (int s = 0; s < n_splits; ++s) {
+                const float weight = load_cluster(mine_address + (uint32_t)(r * (D + 2) + D + 1) * 4u, (uint32_t)s) *
+                                     exp2f(load_cluster(mine_address + (uint32_t)(r * (D + 2) + D) * 4u, (uint32_t)s) - best);
+                numerator += load_cluster(mine_address + (uint32_t)(r * (D + 2) + d) * 4u, (uint32_t)s) * weight;
+                denominator += weight;
+            }
+            p.out[(size_t)token * p.n_q_heads * D + (size_t)(kv_head * group + r) * D + d] = __float2bfloat16_rn(numerator / denominator);
+        }
+        cluster_arrive_wait();      // nobody leaves while another rank may still read its shared memory
     }
 }
 
@@ -790,19 +851,65 @@ int launch_decode_tma(const AttnParams& p, cudaStream_t stream) {
     const size_t shared = (size_t)kDecodeStages * 2 * kTileKeys * D * 2 + (size_t)16 * D * 2 + 1024;
     if (int limit_status = llm_raise_shared_limit(reinterpret_cast<const void*>(attention_decode_tma_kernel<D>), shared, "attention_decode_tma")) return limit_status;
     dim3 grid(p.max_splits, p.n_kv_heads, p.n_seqs);
-    llm_launch(attention_decode_tma_kernel<D>, grid, kDecodeThreads, shared, stream, map_k, map_v, p);
+    if (!p.cluster_merge) {
+        llm_launch(attention_decode_tma_kernel<D>, grid, kDecodeThreads, shared, stream, map_k, map_v, p);
+        return llm_check_launch("attention_decode_tma");
+    }
+    // the splits of a (sequence, kv head) pair as one cluster along x
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = dim3(kDecodeThreads, 1, 1);
+    config.dynamicSmemBytes = shared;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[2];
+    int count = 0;
+    if (llm_pdl_enabled()) {
+        attribute[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute[count].val.programmaticStreamSerializationAllowed = 1;
+        ++count;
+    }
+    attribute[count].id = cudaLaunchAttributeClusterDimension;
+    attribute[count].val.clusterDim.x = (unsigned)p.max_splits;
+    attribute[count].val.clusterDim.y = 1;
+    attribute[count].val.clusterDim.z = 1;
+    ++count;
+    config.attrs = attribute;
+    config.numAttrs = count;
+    cudaError_t status = cudaLaunchKernelEx(&config, attention_decode_tma_kernel<D>, map_k, map_v, p);
+    if (status != cudaSuccess) {
+        llm_set_error("attention_decode_tma (cluster of %d): %s", p.max_splits, cudaGetErrorString(status));
+        return (int)status;
+    }
     return llm_check_launch("attention_decode_tma");
 }
 
 template <int D>
 int launch_decode(const AttnParams& p, cudaStream_t stream) {
     const bool whole_pages = p.page_size >= 8 && p.page_size <= kTileKeys && kTileKeys % p.page_size == 0 && p.page_size % 8 == 0;
-    int status = (whole_pages && aligned16(p.k_pages) && aligned16(p.v_pages)) ? launch_decode_tma<D>(p, stream)
-                                                                                : launch_decode_cp_async<D>(p, stream);
-    if (status != LLM_OK || p.max_splits <= 1) return status;
+    const bool by_tma = whole_pages && aligned16(p.k_pages) && aligned16(p.v_pages);
+    AttnParams q = p;
+    // up to 8 splits (the portable cluster size) merge inside the kernel; more, or the cp.async kernel, go through the
+    // scratch buffers and the merge kernel
+    q.cluster_merge = by_tma && p.cluster_merge && p.max_splits > 1 && p.max_splits <= 8;
+    if (p.max_splits > 1 && !q.cluster_merge && (p.partial_out == nullptr || p.partial_ml == nullptr)) {
+        llm_set_error("attention_decode: %d splits need the scratch buffers for partial results", p.max_splits);
+        return LLM_REFUSED;
+    }
+    int status = by_tma ? launch_decode_tma<D>(q, stream) : launch_decode_cp_async<D>(q, stream);
+    if (status != LLM_OK || p.max_splits <= 1 || q.cluster_merge) return status;
     dim3 merge_grid(p.n_q_heads, p.n_seqs);
     llm_launch(attention_decode_merge_kernel<D>, merge_grid, D < 128 ? D : 128, 0, stream, p);
     return llm_check_launch("attention_decode_merge");
+}
+
+// LLMSERVER_B200_DECODE_MERGE=kernel sends every split decode through scratch memory and the merge kernel.
+bool decode_cluster_merge_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* value = getenv("LLMSERVER_B200_DECODE_MERGE");
+        enabled = (value != nullptr && value[0] == 'k') ? 0 : 1;
+    }
+    return enabled == 1;
 }
 
 }  // namespace
@@ -849,6 +956,7 @@ LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, const void* k_page
     p.max_blocks = max_blocks;
     p.num_pages = num_pages;
     p.slot_by_seq = 0;
+    p.cluster_merge = decode_cluster_merge_enabled() ? 1 : 0;
     p.q_start = q_start;
     p.context_len = context_len;
     p.out = (__nv_bfloat16*)out;
@@ -961,6 +1069,7 @@ LLM_EXPORT int llm_attention_decode_noalloc(const void* q, int q_stride, const v
     p.max_blocks = max_blocks;
     p.num_pages = num_pages;
     p.slot_by_seq = 1;      // the size check above counts sequences, whatever q_start holds
+    p.cluster_merge = 0;    // this entry is the one that merges through the fixed scratch array
     p.q_start = q_start;
     p.context_len = context_len;
     p.out = (__nv_bfloat16*)out;

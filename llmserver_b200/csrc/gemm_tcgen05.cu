@@ -146,6 +146,16 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
         }
         mbar_init(smem_u32(&accum_bar), 1);
         tma::mbar_fence_init();
+        // The weights do not depend on the kernel before this one: the W tiles of the first ring of stages are
+        // requested at once, before the block has even met at its first barrier and long before pdl_wait().
+        const int first = n_kb < p.stages ? n_kb : p.stages;
+        for (int i = 0; i < first; ++i) {
+            const uint32_t bar = smem_u32(&full_bar[i]);
+            mbar_expect_tx(bar, kAtoms * (a_bytes + b_bytes));
+#pragma unroll
+            for (int atom = 0; atom < kAtoms; ++atom)
+                tma_load_2d(base + i * stage_bytes + atom * a_bytes, &map_w, bar, (kb_begin + i) * kBlockK + atom * kAtomK, n0);
+        }
     }
     if (warp == 1) {   // this warp owns the tensor-memory allocation (64 columns: up to 64 token columns of float)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(64));
@@ -157,17 +167,10 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
     const uint32_t tmem_base = tmem_base_slot;
 
     if (warp == 0 && lane == 0) {
-        // ---- producer: TMA copies of the W tile and the token tile of each K block.  The weights do not
-        // depend on the kernel before this one, so the W tiles of the first ring of stages are requested
-        // before pdl_wait(); the token tiles, which that kernel may just have written, after it.
+        // ---- producer: TMA copies of the W tile and the token tile of each K block.  The W tiles of the first
+        // ring are on their way already (see above); the token tiles, which the kernel before this one may just
+        // have written, follow after pdl_wait().
         const int first = n_kb < p.stages ? n_kb : p.stages;
-        for (int i = 0; i < first; ++i) {
-            const uint32_t bar = smem_u32(&full_bar[i]);
-            mbar_expect_tx(bar, kAtoms * (a_bytes + b_bytes));
-#pragma unroll
-            for (int atom = 0; atom < kAtoms; ++atom)
-                tma_load_2d(base + i * stage_bytes + atom * a_bytes, &map_w, bar, (kb_begin + i) * kBlockK + atom * kAtomK, n0);
-        }
         pdl_wait();
         for (int i = 0; i < first; ++i)
 #pragma unroll

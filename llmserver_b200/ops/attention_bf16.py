@@ -13,6 +13,10 @@ from .library import call, check, library, stream_handle, wait_error_flag
 TILE = 64          # rows per block of the portions kernel, keys per tile of both kernels
 MIN_SPLIT = 192    # fewest keys one decode block walks
 DECODE_BLOCKS_PER_SM = 2    # blocks of the decode kernel an SM holds at a time (shared memory)
+# Up to this many splits of a sequence form a thread-block cluster and merge their results in shared memory; more go
+# through scratch memory and a merge kernel (as do all, with LLMSERVER_B200_DECODE_MERGE=kernel).
+CLUSTER_MERGE = os.environ.get("LLMSERVER_B200_DECODE_MERGE", "cluster") != "kernel"
+MAX_CLUSTER_SPLITS = 8
 
 
 # "tcgen05": the 256-row kernel for long portions and the 128-row kernel otherwise; "tcgen05-128" / "tcgen05-256":
@@ -85,6 +89,8 @@ def plan(batch, group: int, n_kv_heads: int, device=None):
         # equal splits beat ragged ones, and one wave beats one and a half.
         pairs = singles * n_kv_heads
         splits = max(1, min(wave_blocks // pairs, -(-longest // MIN_SPLIT)))
+        if CLUSTER_MERGE:
+            splits = min(splits, MAX_CLUSTER_SPLITS)
         if pairs > wave_blocks:
             # More than a wave of whole contexts: when the last wave would leave most SMs idle (40 sequences x 8 kv
             # heads = 1.08 waves take as long as 2), the contexts are split after all.  Measured on the 8B head shape at
