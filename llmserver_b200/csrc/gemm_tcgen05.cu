@@ -33,6 +33,28 @@ constexpr int kThreads = 128;
 constexpr int kMaxStages = 12;
 constexpr int kMaxSplit = 8;
 
+// Optional epilogue of the fused q/k/v projection of a decode step (head_dim 128: the 128 rows of W a CTA owns are
+// exactly one head): per-head RMSNorm of Q and K, rotation by the token's position, Q written to the output, K and V
+// written straight into the token's slot of the cache pages.  Same arithmetic as the stand-alone kernel of rope_kv.cu,
+// but on the 32-bit sums of the product instead of their bfloat16 roundings.
+struct RopeEpilogue {
+    int on;
+    const void* q_weight;      // [128] norm weights (null: no norm), bfloat16 or float
+    const void* k_weight;
+    int weight_is_f32;
+    const float* inv_freq;     // [64] (null: no rotation)
+    const int* positions;      // [m]
+    const int* seq_of_token;   // [m]
+    const int* block_tables;   // [sequences][max_blocks]
+    int max_blocks;
+    __nv_bfloat16* k_pages;    // [pages][kv heads][page_size][128]
+    __nv_bfloat16* v_pages;
+    int n_q_heads, n_kv_heads, page_size, num_pages;
+    float eps;
+    int write_cache;
+    int* page_error;           // set to 1 + token when a token's page is outside the pool
+};
+
 struct GemmParams {
     void* out;
     int out_is_f32;
@@ -42,6 +64,7 @@ struct GemmParams {
     int stages;
     int split;          // cluster size along K
     int* error_flag;
+    RopeEpilogue rope;
 };
 
 using tma::mbar_expect_tx;
@@ -108,6 +131,49 @@ __device__ __forceinline__ float load_peer(uint32_t local_address, uint32_t rank
     return value;
 }
 
+// One finished element of the q/k/v projection: token m, element `row` of head `tile`.  Called by all 128 threads of
+// the block with the same m (it meets at block barriers).
+__device__ __forceinline__ void rope_finish(const GemmParams& p, int m, int row, int tile, float value, float* exchange) {
+    const RopeEpilogue& e = p.rope;
+    const int warp = row >> 5, lane = row & 31;
+    const bool is_q = tile < e.n_q_heads;
+    const bool is_k = !is_q && tile < e.n_q_heads + e.n_kv_heads;
+    const int position = e.positions[m];
+    if (is_q || is_k) {
+        const void* weight = is_q ? e.q_weight : e.k_weight;
+        if (weight != nullptr) {
+            const float squares = warp_sum(value * value);
+            if (lane == 0) exchange[kBlockRows + warp] = squares;
+            __syncthreads();
+            const float total = exchange[kBlockRows] + exchange[kBlockRows + 1] + exchange[kBlockRows + 2] + exchange[kBlockRows + 3];
+            const float w = e.weight_is_f32 ? reinterpret_cast<const float*>(weight)[row]
+                                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(weight)[row]);
+            value = value * rsqrtf(total / (float)kBlockRows + e.eps) * w;
+        }
+        if (e.inv_freq != nullptr) {
+            exchange[row] = value;
+            __syncthreads();
+            const float partner = exchange[row ^ (kBlockRows / 2)];
+            const float angle = (float)position * e.inv_freq[row & (kBlockRows / 2 - 1)];
+            const float c = cosf(angle), sn = sinf(angle);
+            value = row < kBlockRows / 2 ? value * c - partner * sn : value * c + partner * sn;
+        }
+        __syncthreads();      // the exchange buffer is free for the next token
+    }
+    if (is_q) {
+        reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldc + (size_t)tile * kBlockRows + row] = __float2bfloat16_rn(value);
+    } else if (e.write_cache) {
+        const int kv_head = is_k ? tile - e.n_q_heads : tile - e.n_q_heads - e.n_kv_heads;
+        const int page = e.block_tables[(size_t)e.seq_of_token[m] * e.max_blocks + position / e.page_size];
+        if (page < 0 || page >= e.num_pages) {
+            if (row == 0) atomicExch(e.page_error, 1 + m);
+        } else {
+            __nv_bfloat16* pages = is_k ? e.k_pages : e.v_pages;
+            pages[(((size_t)page * e.n_kv_heads + kv_head) * e.page_size + position % e.page_size) * kBlockRows + row] = __float2bfloat16_rn(value);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x,
                                                                 const GemmParams p) {
@@ -117,6 +183,7 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
     __shared__ __align__(8) uint64_t accum_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed;
+    __shared__ float exchange[kBlockRows + 4];      // rope epilogue: a head's elements and its warps' sums
 
     // the dynamic region is aligned to 1024 bytes by hand (the swizzle atoms need it)
     const uint32_t raw = smem_u32(shared_raw);
@@ -248,6 +315,10 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
         if (p.split > 1) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) reduce[(c0 + i) * kBlockRows + row] = values[i];
+        } else if (p.rope.on) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if (c0 + i < p.m) rope_finish(p, c0 + i, row, tile, values[i], exchange);
         } else if (n < p.n) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
@@ -282,7 +353,9 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
                 float total = parts[j][0];
 #pragma unroll
                 for (int peer = 1; peer < kMaxSplit; ++peer) total += parts[j][peer];      // absent peers add 0
-                if (m < p.m && n < p.n) {
+                if (p.rope.on) {
+                    if (m < p.m) rope_finish(p, m, row, tile, total, exchange);
+                } else if (m < p.m && n < p.n) {
                     if (p.out_is_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldc + n] = total;
                     else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(total);
                 }
@@ -307,8 +380,8 @@ LLM_EXPORT int llm_gemm_small_m_supports(int m, int n, int k) {
     return m >= 1 && m <= 64 && n >= 1 && k >= 8 && k % 8 == 0;
 }
 
-LLM_EXPORT int llm_gemm_small_m(const void* x, const void* w, void* out, int m, int n, int k, int ldc, int out_is_f32,
-                                int requested_split, int* error_flag, cudaStream_t stream) {
+static int small_m_launch(const void* x, const void* w, void* out, int m, int n, int k, int ldc, int out_is_f32,
+                          int requested_split, int* error_flag, const RopeEpilogue* rope, cudaStream_t stream) {
     if (m == 0 || n == 0) return LLM_OK;
     if (!llm_gemm_small_m_supports(m, n, k) || !aligned16(x) || !aligned16(w)) {
         llm_set_error("gemm_small_m: takes 1..64 rows, K a multiple of 8 and 16-byte aligned operands (got m %d, n %d, k %d)", m, n, k);
@@ -323,6 +396,12 @@ LLM_EXPORT int llm_gemm_small_m(const void* x, const void* w, void* out, int m, 
     p.ldc = ldc;
     p.token_pad = ((m + 15) / 16) * 16;
     p.error_flag = error_flag;
+    if (rope != nullptr) {
+        p.rope = *rope;
+    } else {
+        p.rope = RopeEpilogue{};
+        p.rope.on = 0;
+    }
     const int tiles = (n + kBlockRows - 1) / kBlockRows;
     const int total_kb = (k + kBlockK - 1) / kBlockK;
     // K is split across a cluster so that the tiles fill the machine; each rank keeps >= 4 K blocks.  The
@@ -387,4 +466,57 @@ LLM_EXPORT int llm_gemm_small_m(const void* x, const void* w, void* out, int m, 
         return (int)status;
     }
     return llm_check_launch("gemm_small_m");
+}
+
+LLM_EXPORT int llm_gemm_small_m(const void* x, const void* w, void* out, int m, int n, int k, int ldc, int out_is_f32,
+                                int requested_split, int* error_flag, cudaStream_t stream) {
+    return small_m_launch(x, w, out, m, n, k, ldc, out_is_f32, requested_split, error_flag, nullptr, stream);
+}
+
+// 1 when the fused q/k/v projection takes the sizes: heads of 128 (a head is a tile of the product), few tokens (each
+// costs a block-wide reduction in the epilogue), and what llm_gemm_small_m itself needs.
+LLM_EXPORT int llm_gemm_qkv_rope_supports(int m, int n_q_heads, int n_kv_heads, int head_dim, int k) {
+    return head_dim == kBlockRows && m >= 1 && m <= 16 && n_q_heads >= 1 && n_kv_heads >= 1 &&
+           llm_gemm_small_m_supports(m, (n_q_heads + 2 * n_kv_heads) * head_dim, k);
+}
+
+// qkv[m, (Hq + 2 Hkv) 128] = x[m, k] W^T with the epilogue of RopeEpilogue: Q heads normalised, rotated and written
+// to `qkv` (bfloat16, row pitch ldc); K heads normalised, rotated and written to the K pages, V heads to the V pages
+// (when write_cache is set), nothing of K and V to `qkv`.  Arguments as llm_qk_norm_rope_kv_write and
+// llm_gemm_small_m; the whole head rotates, paired as halves.
+LLM_EXPORT int llm_gemm_qkv_rope(const void* x, const void* w, void* qkv, int m, int k, int ldc, int requested_split,
+                                 const void* q_weight, const void* k_weight, int weight_is_f32, const float* inv_freq,
+                                 const int* positions, const int* seq_of_token, const int* block_tables, int max_blocks,
+                                 void* k_pages, void* v_pages, int n_q_heads, int n_kv_heads, int head_dim, int page_size,
+                                 int num_pages, float eps, int write_cache, int* page_error, int* error_flag,
+                                 cudaStream_t stream) {
+    if (!llm_gemm_qkv_rope_supports(m, n_q_heads, n_kv_heads, head_dim, k)) {
+        llm_set_error("gemm_qkv_rope: takes heads of 128 and 1..16 tokens (got head_dim %d, m %d, k %d)", head_dim, m, k);
+        return LLM_REFUSED;
+    }
+    if (positions == nullptr || seq_of_token == nullptr || block_tables == nullptr || page_error == nullptr ||
+        (write_cache && (k_pages == nullptr || v_pages == nullptr)) || page_size <= 0 || num_pages <= 0) {
+        llm_set_error("gemm_qkv_rope: positions, tables, pages and the error flag must be given");
+        return LLM_REFUSED;
+    }
+    RopeEpilogue rope;
+    rope.on = 1;
+    rope.q_weight = q_weight;
+    rope.k_weight = k_weight;
+    rope.weight_is_f32 = weight_is_f32;
+    rope.inv_freq = inv_freq;
+    rope.positions = positions;
+    rope.seq_of_token = seq_of_token;
+    rope.block_tables = block_tables;
+    rope.max_blocks = max_blocks;
+    rope.k_pages = (__nv_bfloat16*)k_pages;
+    rope.v_pages = (__nv_bfloat16*)v_pages;
+    rope.n_q_heads = n_q_heads;
+    rope.n_kv_heads = n_kv_heads;
+    rope.page_size = page_size;
+    rope.num_pages = num_pages;
+    rope.eps = eps;
+    rope.write_cache = write_cache;
+    rope.page_error = page_error;
+    return small_m_launch(x, w, qkv, m, (n_q_heads + 2 * n_kv_heads) * head_dim, k, ldc, 0, requested_split, error_flag, &rope, stream);
 }

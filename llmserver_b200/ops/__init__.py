@@ -15,7 +15,7 @@ from .library import (KernelError, call, check, declare, dtype_code, launch_coun
                       require_device, stream_handle, wait_error_flag)
 
 __all__ = ["KernelError", "embedding", "add_rmsnorm", "rmsnorm", "silu_mul", "sample", "qk_norm_rope_kv_write",
-           "attention_generic", "gemm_f32", "linear", "require_device", "library", "launch_count"]
+           "attention_generic", "gemm_f32", "linear", "qkv_projection", "require_device", "library", "launch_count"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -209,6 +209,26 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
         return result
     from . import gemm_bf16
     return gemm_bf16.linear_bf16(x, weight, out=out, out_dtype=out_dtype)
+
+
+def qkv_projection(x: torch.Tensor, weight: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                   inv_freq: Optional[torch.Tensor], positions: torch.Tensor, seq_of_token: torch.Tensor,
+                   block_tables: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, n_q_heads: int, n_kv_heads: int,
+                   head_dim: int, eps: float, write_cache: bool, error_flag: torch.Tensor, rotary_dim: Optional[int] = None,
+                   interleaved: bool = False) -> torch.Tensor:
+    """qkv = x W^T followed by ``qk_norm_rope_kv_write``: as one kernel where the product kernel can finish heads in its
+    epilogue (bfloat16, heads of 128, up to 16 tokens, the whole head rotating in halves), else as two."""
+    whole_head = rotary_dim is None or rotary_dim == head_dim
+    if x.dtype == torch.bfloat16 and whole_head and not interleaved and x.shape[0] <= 16:
+        from . import gemm_bf16
+        fused = gemm_bf16.qkv_rope_fused(x, weight, q_weight, k_weight, inv_freq, positions, seq_of_token, block_tables,
+                                         k_pages, v_pages, n_q_heads, n_kv_heads, head_dim, eps, write_cache, error_flag)
+        if fused is not None:
+            return fused
+    qkv = linear(x, weight)
+    qk_norm_rope_kv_write(qkv, q_weight, k_weight, inv_freq, positions, seq_of_token, block_tables, k_pages, v_pages,
+                          n_q_heads, n_kv_heads, head_dim, eps, write_cache, error_flag, rotary_dim, interleaved)
+    return qkv
 
 
 def attention(qkv: torch.Tensor, batch, block_tables: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,

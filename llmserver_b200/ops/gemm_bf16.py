@@ -258,3 +258,37 @@ def _float32_by_library(x: torch.Tensor, weight: torch.Tensor, out: Optional[tor
         out.copy_(result)
         return out
     return result
+
+
+FUSE_QKV_ROPE = os.environ.get("LLMSERVER_B200_FUSE_QKV_ROPE", "1") != "0"
+
+
+def qkv_rope_fused(x: torch.Tensor, weight: torch.Tensor, q_weight, k_weight, inv_freq, positions, seq_of_token,
+                   block_tables, k_pages, v_pages, n_q_heads: int, n_kv_heads: int, head_dim: int, eps: float,
+                   write_cache: bool, page_error: torch.Tensor) -> Optional[torch.Tensor]:
+    """The fused q/k/v projection of a step with few tokens: x W^T, then, in the product kernel's epilogue, the per-head
+    norms, the rotation and the cache write (see ``ops.qk_norm_rope_kv_write`` for the arithmetic).  Returns the packed
+    [N, (Hq + 2 Hkv) D] tensor whose Q heads are finished (its K and V heads are not written: they went to the pages),
+    or None when the fused kernel does not take the case; the caller then runs the two kernels one after the other."""
+    rows, inner = x.shape
+    if not (FUSE_QKV_ROPE and _use_small_m and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and x.is_contiguous() and weight.is_contiguous() and k_pages.dtype == torch.bfloat16
+            and library().llm_gemm_qkv_rope_supports(rows, n_q_heads, n_kv_heads, head_dim, inner)):
+        return None
+    if weight.shape[0] != (n_q_heads + 2 * n_kv_heads) * head_dim:
+        return None
+    if (q_weight is None) != (k_weight is None) or (q_weight is not None and q_weight.dtype != k_weight.dtype):
+        return None
+    if inv_freq is not None and inv_freq.numel() * 2 != head_dim:
+        return None
+    split = _plan_for(x, weight, torch.bfloat16)
+    if split == 0:          # the library's product won the measurement for this shape: no epilogue to fuse into
+        return None
+    out = torch.empty((rows, weight.shape[0]), dtype=torch.bfloat16, device=x.device)
+    call("llm_gemm_qkv_rope", x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, inner, weight.shape[0], max(split, 0),
+         0 if q_weight is None else q_weight.data_ptr(), 0 if k_weight is None else k_weight.data_ptr(),
+         int(q_weight is not None and q_weight.dtype == torch.float32), 0 if inv_freq is None else inv_freq.data_ptr(),
+         positions.data_ptr(), seq_of_token.data_ptr(), block_tables.data_ptr(), block_tables.shape[-1],
+         k_pages.data_ptr(), v_pages.data_ptr(), n_q_heads, n_kv_heads, head_dim, k_pages.shape[2], k_pages.shape[0],
+         float(eps), int(write_cache), page_error.data_ptr(), error_flag(x.device).data_ptr(), stream_handle())
+    return out

@@ -32,6 +32,8 @@ SIGNATURES = {
     "llm_attention_prefill_wide": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _S],
     "llm_gemm_small_m_supports": [_I, _I, _I],
     "llm_gemm_small_m": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _S],
+    "llm_gemm_qkv_rope_supports": [_I, _I, _I, _I, _I],
+    "llm_gemm_qkv_rope": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _S],
     "llm_attention_mma": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _I, _I, _P, _P, _P, _S],
 }
 

@@ -91,11 +91,10 @@ class GQAttention(Mixer):
         self.inv_freq, self.rotary_dim, self.interleaved = inv_freq, rotary_dim, pairing == "interleaved"
 
     def forward(self, x, batch, cache):
-        qkv = ops.linear(x, self.qkv)
         tables = batch.block_tables[cache.group]
-        ops.qk_norm_rope_kv_write(qkv, self.q_norm, self.k_norm, self.inv_freq, batch.positions, batch.seq_of_token,
-                                  tables, cache.k_pages, cache.v_pages, self.heads, self.kv_heads, self.head_dim,
-                                  self.eps, cache.writes, batch.error_flag, self.rotary_dim, self.interleaved)
+        qkv = ops.qkv_projection(x, self.qkv, self.q_norm, self.k_norm, self.inv_freq, batch.positions, batch.seq_of_token,
+                                 tables, cache.k_pages, cache.v_pages, self.heads, self.kv_heads, self.head_dim, self.eps,
+                                 cache.writes, batch.error_flag, self.rotary_dim, self.interleaved)
         attended = ops.attention(qkv, batch, tables, cache.k_pages, cache.v_pages, self.heads, self.kv_heads,
                                  self.head_dim, self.scale, self.window)
         return ops.linear(attended, self.out)

@@ -218,6 +218,62 @@ def test_attention_finds_a_far_key_and_respects_the_window_edge(dtype):
     assert not torch.allclose(out[1], v[context - window - 1, 0], atol=0.2)
 
 
+@pytest.mark.parametrize("tokens,heads,kv_heads,hidden,qk_norm,weight_dtype", [
+    (1, 8, 2, 256, True, torch.bfloat16), (5, 4, 4, 1024, True, torch.float32), (16, 32, 8, 4096, True, torch.bfloat16),
+    (8, 6, 1, 512, False, torch.bfloat16)])
+def test_qkv_projection_with_the_rotation_in_its_epilogue(tokens, heads, kv_heads, hidden, qk_norm, weight_dtype):
+    """Heads of 128 and few tokens: the product kernel finishes each head itself (norm, rotation, cache write).  Against
+    plain arithmetic in float64 and against the two separate kernels."""
+    from llmserver_b200 import ops
+    from llmserver_b200.ops import gemm_bf16
+    dim, page_size, theta, eps, dtype = 128, 16, 1000000.0, 1e-6, torch.bfloat16
+    width = (heads + 2 * kv_heads) * dim
+    x = rand((tokens, hidden), dtype, 70)
+    weight = (rand((width, hidden), dtype, 71).float() * hidden ** -0.5 * 4).to(dtype)
+    q_weight = (rand((dim,), torch.float32, 72) + 1).to(weight_dtype) if qk_norm else None
+    k_weight = (rand((dim,), torch.float32, 73) + 1).to(weight_dtype) if qk_norm else None
+    positions = torch.tensor([(37 * i * i + 5) % 3000 for i in range(tokens)], dtype=torch.int32)
+    seq_of_token = torch.arange(tokens, dtype=torch.int32)
+    n_pages = tokens * (3000 // page_size + 1) + 1
+    tables = torch.randperm(n_pages - 1, generator=torch.Generator().manual_seed(9)).to(torch.int32).reshape(tokens, -1).contiguous()
+    inv_freq = (1.0 / (theta ** (torch.arange(0, dim, 2).float() / dim))).to(DEVICE)
+    results = {}
+    # this package's kernel for the shape, with K divided into 1, 2 or 4 parts (a measurement may prefer the library's
+    # product, which has no epilogue to fuse into)
+    gemm_bf16._choice[(gemm_bf16._row_bucket(tokens), width, hidden, torch.bfloat16)] = {1: 1, 5: 2, 8: 3, 16: 4}[tokens]
+    for fused in (True, False):
+        gemm_bf16.FUSE_QKV_ROPE = fused
+        k_pages = torch.zeros((n_pages, kv_heads, page_size, dim), dtype=dtype, device=DEVICE)
+        v_pages = torch.zeros_like(k_pages)
+        flag = torch.zeros(1, dtype=torch.int32, device=DEVICE)
+        launches = ops.launch_count()
+        qkv = ops.qkv_projection(x, weight, q_weight, k_weight, inv_freq, positions.to(DEVICE), seq_of_token.to(DEVICE),
+                                 tables.to(DEVICE), k_pages, v_pages, heads, kv_heads, dim, eps, True, flag)
+        torch.cuda.synchronize()
+        gemm_bf16.check_errors()
+        assert flag.item() == 0
+        results[fused] = (qkv[:, :heads * dim].float().cpu(), k_pages.float().cpu(), v_pages.float().cpu(), ops.launch_count() - launches)
+    gemm_bf16.FUSE_QKV_ROPE = True
+    assert results[True][3] < results[False][3], "the fused path was meant to launch fewer kernels"
+    product = x.double().cpu() @ weight.double().cpu().T
+    q = product[:, :heads * dim].view(tokens, heads, dim)
+    k = product[:, heads * dim:(heads + kv_heads) * dim].view(tokens, kv_heads, dim)
+    v = product[:, (heads + kv_heads) * dim:].view(tokens, kv_heads, dim)
+    if qk_norm:
+        q, k = plain_model.rms_norm(q, q_weight.double().cpu(), eps), plain_model.rms_norm(k, k_weight.double().cpu(), eps)
+    cosine, sine = plain_model.rope_tables(positions, dim, theta, torch.float64)
+    q, k = plain_model.apply_rope(q, cosine, sine), plain_model.apply_rope(k, cosine, sine)
+    for fused in (True, False):
+        got_q, got_k_pages, got_v_pages, _ = results[fused]
+        close(got_q, q.reshape(tokens, -1), dtype, f"q (fused {fused})")
+        got_k = torch.stack([got_k_pages[tables[t, p // page_size].item(), :, p % page_size] for t, p in enumerate(positions.tolist())])
+        got_v = torch.stack([got_v_pages[tables[t, p // page_size].item(), :, p % page_size] for t, p in enumerate(positions.tolist())])
+        close(got_k, k, dtype, f"cached k (fused {fused})")
+        close(got_v, v, dtype, f"cached v (fused {fused})")
+        written = (got_k_pages.abs().sum(dim=(1, 3)) > 0).sum().item()
+        assert written == tokens, "slots other than the tokens' own were written"
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("dim,rotary,interleaved,qk_norm", [(48, 24, True, True), (128, 64, False, True), (128, 128, True, False),
                                                             (80, 2, False, True), (64, 0, False, True)])
