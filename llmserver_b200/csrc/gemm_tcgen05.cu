@@ -65,6 +65,8 @@ struct GemmParams {
     int split;          // cluster size along K
     int* error_flag;
     RopeEpilogue rope;
+    int silu_gate;      // 1: rows 0..63 of a tile are gate rows and rows 64..127 their up rows; the epilogue writes
+                        // silu(gate) * up into an output of n / 2 columns
 };
 
 using tma::mbar_expect_tx;
@@ -172,6 +174,22 @@ __device__ __forceinline__ void rope_finish(const GemmParams& p, int m, int row,
             pages[(((size_t)page * e.n_kv_heads + kv_head) * e.page_size + position % e.page_size) * kBlockRows + row] = __float2bfloat16_rn(value);
         }
     }
+}
+
+// One finished element of the fused gate/up projection: rows 0..63 of the tile hold gate values, rows 64..127 the up
+// values of the same outputs.  Called by all 128 threads of the block with the same m.  The arithmetic is that of the
+// stand-alone kernel of activation.cu for 16-bit activations, on the 32-bit sums of the product.
+__device__ __forceinline__ void silu_finish(const GemmParams& p, int m, int row, int tile, float value, float* exchange) {
+    constexpr int kHalf = kBlockRows / 2;
+    if (row >= kHalf) exchange[row - kHalf] = value;
+    __syncthreads();
+    if (row < kHalf) {
+        const int column = tile * kHalf + row;
+        if (column < p.n / 2)
+            reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldc + column] =
+                __float2bfloat16_rn(__fdividef(value, 1.0f + __expf(-value)) * exchange[row]);
+    }
+    __syncthreads();
 }
 
 __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_constant__ CUtensorMap map_w,
@@ -319,6 +337,10 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
 #pragma unroll
             for (int i = 0; i < 16; ++i)
                 if (c0 + i < p.m) rope_finish(p, c0 + i, row, tile, values[i], exchange);
+        } else if (p.silu_gate) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if (c0 + i < p.m) silu_finish(p, c0 + i, row, tile, values[i], exchange);
         } else if (n < p.n) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
@@ -355,6 +377,8 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
                 for (int peer = 1; peer < kMaxSplit; ++peer) total += parts[j][peer];      // absent peers add 0
                 if (p.rope.on) {
                     if (m < p.m) rope_finish(p, m, row, tile, total, exchange);
+                } else if (p.silu_gate) {
+                    if (m < p.m) silu_finish(p, m, row, tile, total, exchange);
                 } else if (m < p.m && n < p.n) {
                     if (p.out_is_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldc + n] = total;
                     else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(total);
@@ -381,7 +405,8 @@ LLM_EXPORT int llm_gemm_small_m_supports(int m, int n, int k) {
 }
 
 static int small_m_launch(const void* x, const void* w, void* out, int m, int n, int k, int ldc, int out_is_f32,
-                          int requested_split, int* error_flag, const RopeEpilogue* rope, cudaStream_t stream) {
+                          int requested_split, int* error_flag, const RopeEpilogue* rope, cudaStream_t stream,
+                          int silu_gate = 0) {
     if (m == 0 || n == 0) return LLM_OK;
     if (!llm_gemm_small_m_supports(m, n, k) || !aligned16(x) || !aligned16(w)) {
         llm_set_error("gemm_small_m: takes 1..64 rows, K a multiple of 8 and 16-byte aligned operands (got m %d, n %d, k %d)", m, n, k);
@@ -402,6 +427,7 @@ static int small_m_launch(const void* x, const void* w, void* out, int m, int n,
         p.rope = RopeEpilogue{};
         p.rope.on = 0;
     }
+    p.silu_gate = silu_gate;
     const int tiles = (n + kBlockRows - 1) / kBlockRows;
     const int total_kb = (k + kBlockK - 1) / kBlockK;
     // K is split across a cluster so that the tiles fill the machine; each rank keeps >= 4 K blocks.  The
@@ -519,4 +545,16 @@ LLM_EXPORT int llm_gemm_qkv_rope(const void* x, const void* w, void* qkv, int m,
     rope.write_cache = write_cache;
     rope.page_error = page_error;
     return small_m_launch(x, w, qkv, m, (n_q_heads + 2 * n_kv_heads) * head_dim, k, ldc, 0, requested_split, error_flag, &rope, stream);
+}
+
+// out[m, n / 2] = silu(gate) * up of the fused gate/up projection x W^T, W [n, k] with gate and up rows interleaved in
+// groups of 64 (rows [128 b, 128 b + 64) are gate rows of outputs [64 b, 64 b + 64), the next 64 rows their up rows);
+// n must be a multiple of 128.  bfloat16 in and out; ldc is the row pitch of `out`.
+LLM_EXPORT int llm_gemm_gate_up_silu(const void* x, const void* w, void* out, int m, int n, int k, int ldc,
+                                     int requested_split, int* error_flag, cudaStream_t stream) {
+    if (n % kBlockRows) {
+        llm_set_error("gemm_gate_up_silu: %d rows of the fused weight are no multiple of %d", n, kBlockRows);
+        return LLM_REFUSED;
+    }
+    return small_m_launch(x, w, out, m, n, k, ldc, 0, requested_split, error_flag, nullptr, stream, 1);
 }

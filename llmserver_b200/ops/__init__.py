@@ -15,7 +15,7 @@ from .library import (KernelError, call, check, declare, dtype_code, launch_coun
                       require_device, stream_handle, wait_error_flag)
 
 __all__ = ["KernelError", "embedding", "add_rmsnorm", "rmsnorm", "silu_mul", "sample", "qk_norm_rope_kv_write",
-           "attention_generic", "gemm_f32", "linear", "qkv_projection", "require_device", "library", "launch_count"]
+           "attention_generic", "gemm_f32", "linear", "qkv_projection", "gate_up_silu", "interleave_gate_up", "require_device", "library", "launch_count"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -74,8 +74,10 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[tor
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[n, i] = silu(gate_up[n, i]) * gate_up[n, I + i]; gate_up is [N, 2 I], gate half first."""
+def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, group: int = 0) -> torch.Tensor:
+    """out[n, i] = silu(gate_up[n, i]) * gate_up[n, I + i]; gate_up is [N, 2 I], gate half first.  With ``group`` > 0
+    gate and up columns are interleaved in groups of that many: output i finds its gate value at column
+    (i // group) * 2 * group + i % group and its up value ``group`` columns further."""
     check(gate_up, "gate_up")
     rows, doubled = gate_up.shape
     if doubled % 2:
@@ -83,9 +85,34 @@ def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch
     if out is None:
         out = torch.empty((rows, doubled // 2), dtype=gate_up.dtype, device=gate_up.device)
     check(out, "silu_mul output", gate_up.dtype, doubled // 2)
-    call("llm_silu_mul", gate_up.data_ptr(), out.data_ptr(), rows, doubled // 2, dtype_code(gate_up.dtype),
+    call("llm_silu_mul", gate_up.data_ptr(), out.data_ptr(), rows, doubled // 2, int(group), dtype_code(gate_up.dtype),
          stream_handle())
     return out
+
+
+GATE_UP_GROUP = 64      # rows of gate and of up that share a 128-row tile of the fused weight
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int = GATE_UP_GROUP) -> torch.Tensor:
+    """The fused [2 I, H] weight with gate and up rows interleaved in groups (see ``silu_mul``): a 128-row tile then
+    holds 64 gate rows and their 64 up rows, so the product kernel can apply the gate in its epilogue."""
+    inter, hidden = gate.shape
+    if inter % group:
+        raise KernelError(f"the intermediate size {inter} is no multiple of {group}")
+    return torch.stack([gate.reshape(inter // group, group, hidden), up.reshape(inter // group, group, hidden)],
+                       dim=1).reshape(2 * inter, hidden).contiguous()
+
+
+def gate_up_silu(x: torch.Tensor, weight: torch.Tensor, group: int = 0) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) for the fused weight ``weight`` [2 I, H] (halves when ``group`` is 0, else interleaved in
+    groups): as one kernel where the product kernel can apply the gate in its epilogue (bfloat16, groups of 64, few
+    rows), else as the product followed by ``silu_mul``."""
+    if x.dtype == torch.bfloat16 and group == GATE_UP_GROUP:
+        from . import gemm_bf16
+        fused = gemm_bf16.gate_up_silu_fused(x, weight)
+        if fused is not None:
+            return fused
+    return silu_mul(linear(x, weight), group=group)
 
 
 def sample(logits: torch.Tensor, temperatures: Optional[torch.Tensor] = None, seeds: Optional[torch.Tensor] = None,

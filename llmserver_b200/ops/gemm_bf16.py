@@ -292,3 +292,24 @@ def qkv_rope_fused(x: torch.Tensor, weight: torch.Tensor, q_weight, k_weight, in
          k_pages.data_ptr(), v_pages.data_ptr(), n_q_heads, n_kv_heads, head_dim, k_pages.shape[2], k_pages.shape[0],
          float(eps), int(write_cache), page_error.data_ptr(), error_flag(x.device).data_ptr(), stream_handle())
     return out
+
+
+FUSE_GATE_UP_SILU = os.environ.get("LLMSERVER_B200_FUSE_GATE_UP_SILU", "1") != "0"
+
+
+def gate_up_silu_fused(x: torch.Tensor, weight: torch.Tensor) -> Optional[torch.Tensor]:
+    """silu(gate) * up in the epilogue of the product for few rows; ``weight`` is the fused [2 I, H] matrix with gate
+    and up rows interleaved in groups of 64.  None when the product kernel does not take the case (the caller then
+    runs the product and the activation kernel)."""
+    rows, inner = x.shape
+    cols = weight.shape[0]
+    if not (FUSE_GATE_UP_SILU and rows <= SMALL_M and cols % 128 == 0 and x.is_contiguous() and weight.is_contiguous()
+            and weight.dtype == torch.bfloat16 and small_m_supported(rows, cols, inner)):
+        return None
+    split = _plan_for(x, weight, torch.bfloat16)
+    if split == 0:
+        return None
+    out = torch.empty((rows, cols // 2), dtype=torch.bfloat16, device=x.device)
+    call("llm_gemm_gate_up_silu", x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, cols, inner, cols // 2, max(split, 0),
+         error_flag(x.device).data_ptr(), stream_handle())
+    return out

@@ -19,7 +19,7 @@ SIGNATURES = {
     "llm_embedding_gather": [_P, _P, _P, _I, _I, _I, _I, _S],
     "llm_add_rmsnorm": [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _S],
     "llm_rmsnorm": [_P, _P, _P, _I, _I, _F, _I, _I, _S],
-    "llm_silu_mul": [_P, _P, _I, _I, _I, _S],
+    "llm_silu_mul": [_P, _P, _I, _I, _I, _I, _S],
     "llm_sample": [_P, _P, _P, _P, _P, _I, _I, _P, _P, _S],
     "llm_sample_slices": [_I, _I],
     "llm_qk_norm_rope_kv_write": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _I, _I, _I, _S],
@@ -32,6 +32,7 @@ SIGNATURES = {
     "llm_attention_prefill_wide": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _S],
     "llm_gemm_small_m_supports": [_I, _I, _I],
     "llm_gemm_small_m": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _S],
+    "llm_gemm_gate_up_silu": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _S],
     "llm_gemm_qkv_rope_supports": [_I, _I, _I, _I, _I],
     "llm_gemm_qkv_rope": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _S],
     "llm_attention_mma": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _I, _I, _P, _P, _P, _S],

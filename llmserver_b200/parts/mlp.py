@@ -35,8 +35,12 @@ class SwiGLU(FeedForward):
 
     def __init__(self, params, weights, runtime):
         super().__init__(params, weights, runtime)
-        self.gate_up = torch.cat([weights["gate_proj.weight"], weights["up_proj.weight"]], dim=0).contiguous()
+        gate, up = weights["gate_proj.weight"], weights["up_proj.weight"]
+        # bfloat16: gate and up rows interleaved in groups of 64, the layout in which the product kernel for few rows
+        # can apply the gate itself; the 32-bit path keeps gate rows first
+        self.group = ops.GATE_UP_GROUP if gate.dtype == torch.bfloat16 and gate.shape[0] % ops.GATE_UP_GROUP == 0 else 0
+        self.gate_up = ops.interleave_gate_up(gate, up) if self.group else torch.cat([gate, up], dim=0).contiguous()
         self.down = weights["down_proj.weight"].contiguous()
 
     def forward(self, x):
-        return ops.linear(ops.silu_mul(ops.linear(x, self.gate_up)), self.down)
+        return ops.linear(ops.gate_up_silu(x, self.gate_up, self.group), self.down)

@@ -83,6 +83,40 @@ def test_rmsnorm_and_silu_mul(dtype):
     gate_up = rand((9, 2 * 1111), dtype, 7, 3.0)
     gate, up = gate_up.double()[:, :1111], gate_up.double()[:, 1111:]
     close(ops.silu_mul(gate_up), torch.nn.functional.silu(gate) * up, dtype, "silu_mul")
+    # gate and up columns interleaved in groups of 64 (vector form) and of 5 (element-wise form)
+    for inter, group in ((1152, 64), (1115, 5)):
+        gate_up = rand((7, 2 * inter), dtype, 8, 3.0)
+        blocks = gate_up.double().reshape(7, inter // group, 2, group)
+        want = (torch.nn.functional.silu(blocks[:, :, 0]) * blocks[:, :, 1]).reshape(7, inter)
+        close(ops.silu_mul(gate_up, group=group), want, dtype, f"silu_mul in groups of {group}")
+
+
+@pytest.mark.parametrize("rows,hidden,inter,split", [(1, 256, 128, 1), (8, 4096, 12288, 2), (37, 512, 1088, 3), (64, 1024, 2112, 4)])
+def test_gate_up_product_with_the_gate_in_its_epilogue(rows, hidden, inter, split):
+    """silu(x Wg^T) * (x Wu^T) from one kernel (gate and up rows interleaved in groups of 64 in the fused weight),
+    against float64 and against the product followed by the activation kernel."""
+    from llmserver_b200 import ops
+    from llmserver_b200.ops import gemm_bf16
+    dtype = torch.bfloat16
+    x = rand((rows, hidden), dtype, 90)
+    gate = (rand((inter, hidden), dtype, 91).float() * hidden ** -0.5 * 3).to(dtype)
+    up = (rand((inter, hidden), dtype, 92).float() * hidden ** -0.5 * 3).to(dtype)
+    weight = ops.interleave_gate_up(gate, up)
+    assert torch.equal(weight[64:128], up[:64]) and torch.equal(weight[128:192], gate[64:128])
+    gemm_bf16._choice[(gemm_bf16._row_bucket(rows), 2 * inter, hidden, torch.bfloat16)] = split
+    want = torch.nn.functional.silu(x.double() @ gate.double().T) * (x.double() @ up.double().T)
+    launches = ops.launch_count()
+    fused = ops.gate_up_silu(x, weight, ops.GATE_UP_GROUP)
+    assert ops.launch_count() - launches == 1
+    gemm_bf16.FUSE_GATE_UP_SILU = False
+    try:
+        apart = ops.gate_up_silu(x, weight, ops.GATE_UP_GROUP)
+    finally:
+        gemm_bf16.FUSE_GATE_UP_SILU = True
+    torch.cuda.synchronize()
+    gemm_bf16.check_errors()
+    close(fused, want, dtype, "fused gate/up")
+    close(apart, want, dtype, "gate/up product, then the activation kernel")
 
 
 @pytest.mark.parametrize("shape", [(1, 7, 5), (33, 100, 77), (130, 257, 1000), (2, 509, 96), (64, 64, 16)])
