@@ -255,6 +255,7 @@ class Harness:
             engine.step()
         torch.cuda.synchronize()
         before = sum(len(request.generated_token_ids) for request in requests)
+        stats_before = dict(engine.stats)
         started = time.perf_counter()
         for _ in range(steps):
             engine.step()
@@ -266,7 +267,11 @@ class Harness:
         h2d = engine.step_function.last_batch_bytes
         for request in requests:
             engine.cancel_request(request.request_id)
+        # where a step's host time goes (mean over the engine's steps; read_back is the wait for the device)
+        phases = {name: 1e3 * (engine.stats[name + "_s"] - stats_before[name + "_s"]) / steps
+                  for name in ("schedule", "pack_copy", "launch", "read_back", "accept")}
         return {"value": batch * steps / elapsed, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": batch * 4, "ms_per_step": elapsed * 1e3 / steps}
+                "d2h_bytes_per_step": batch * 4, "ms_per_step": elapsed * 1e3 / steps,
+                "host_phases_ms": ", ".join(f"{name} {phases[name]:.3f}" for name in ("schedule", "pack_copy", "launch", "read_back", "accept"))}
 
 

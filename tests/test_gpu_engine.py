@@ -346,3 +346,44 @@ def test_the_generate_command_prints_the_ids_the_engine_generates(tiny_folders):
     assert [len(tokens) for tokens in report["generated"]] == [7, 7] and report["finish_reasons"] == ["length", "length"]
     for index, (prompt, tokens) in enumerate(zip(prompts, report["generated"])):
         assert_tokens_are_argmax_of_plain(folder, prompt, tokens, "float32", 0.7, 5 + index)
+
+
+def test_two_processes_with_the_same_plan_file_give_the_same_bfloat16_logits(tiny_folders, tmp_path):
+    """The choice among the variants of a matrix product (which fixes the order of its partial sums) is measured per
+    process unless it is read from a file: the first process measures and writes the file, two more read it and must
+    agree bit for bit."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    folder = tiny_folders["e"]
+    plan = str(tmp_path / "gemm_plan.txt")
+    script = (
+        "import sys, hashlib, torch\n"
+        "from llmserver_b200.models import load_model\n"
+        "from llmserver_b200.cache import CacheManager\n"
+        "from llmserver_b200.engine.step import StepFunction\n"
+        "from llmserver_b200.ops import gemm_bf16\n"
+        "model = load_model(sys.argv[1], 'bfloat16', 'cuda:0')\n"
+        "cache = CacheManager(model.cache_needs(), 16, 40, num_slots=4, prefix_sharing=False)\n"
+        "cache.materialize(model.runtime.device, model.runtime.dtype)\n"
+        "step = StepFunction(model, cache)\n"
+        "digest = hashlib.sha256()\n"
+        "for name, count in (('a', 37), ('b', 5), ('c', 64)):\n"
+        "    step.admit(name)\n"
+        "    logits = step.run([(name, [(7 * i + len(name)) % 333 for i in range(count)], list(range(count)))])\n"
+        "    digest.update(logits.cpu().numpy().tobytes())\n"
+        "for round_index in range(4):\n"
+        "    logits = step.run([(name, [round_index], [0]) for name in 'abc'])\n"
+        "    digest.update(logits.cpu().numpy().tobytes())\n"
+        "print('DIGEST', digest.hexdigest(), gemm_bf16.tunings())\n")
+    results = []
+    for _ in range(3):
+        done = subprocess.run([sys.executable, "-c", script, folder], capture_output=True, text=True, cwd=root, timeout=600,
+                              env=dict(os.environ, LLMSERVER_B200_GEMM_PLAN=plan, PYTHONPATH=root))
+        assert done.returncode == 0, done.stderr[-2000:]
+        line = [text for text in done.stdout.splitlines() if text.startswith("DIGEST")][-1].split()
+        results.append((line[1], int(line[2])))
+    assert os.path.isfile(plan) and results[0][1] > 0, "the first process was meant to measure and write the plan"
+    assert results[1][1] == 0 and results[2][1] == 0, "a process that reads the plan measured again"
+    assert results[1][0] == results[2][0] == results[0][0], "the same plan gave other logits"

@@ -436,7 +436,12 @@ def test_sampling_greedy_and_temperature():
             continue
         scores = plain_model.gumbel_scores(host[row], temperatures[row].item(), int(seeds[row]), int(steps[row]))
         assert scores[token] >= scores.max() - 1e-4, f"row {row}: token {token} is not the Gumbel-max choice"
-    assert drawn[0] != drawn[3] or True  # different steps usually differ; not required
+    # the noise depends on the step: the same row drawn at 64 different steps does not give one token 64 times
+    many = torch.arange(64, dtype=torch.int32, device=DEVICE)
+    row = 1 if temperatures[1].item() > 0 else int((temperatures > 0).nonzero()[0])
+    tokens = ops.sample(logits[row:row + 1].expand(64, -1).contiguous(), temperatures[row:row + 1].expand(64).contiguous(),
+                        seeds[row:row + 1].expand(64).contiguous(), many).cpu().tolist()
+    assert len(set(tokens)) > 1, "the draw does not depend on the step"
 
 
 def test_sampling_over_a_large_vocabulary():
@@ -600,3 +605,30 @@ def test_attention_prefill_tcgen05(heads, kv_heads, page_size, window):
             results[kernel] = out
     close(results["tcgen05-128"], results["mma"].double().cpu(), dtype, "the 128-row kernel against the mma.sync kernel")
     close(results["tcgen05-256"], results["mma"].double().cpu(), dtype, "the 256-row kernel against the mma.sync kernel")
+
+
+def test_float32_logits_are_32_bit_sums_whatever_the_number_of_rows():
+    """The output head's product: float32 results come from 32-bit accumulators for 64 rows, for 65 (two launches of
+    this package's kernel) and for a shape the kernel does not take (the library's product with a 32-bit result), never
+    from a bfloat16 product widened afterwards.  A row's logits do not depend on how many rows share the step beyond the
+    order of a 32-bit sum."""
+    from llmserver_b200 import ops
+    hidden, vocab = 512, 5003
+    x = rand((130, hidden), torch.bfloat16, 31)
+    head = rand((vocab, hidden), torch.bfloat16, 32, 0.05)
+    want = x.double() @ head.double().T
+    scale = want.abs().max().item()
+    by_rows = {}
+    for rows in (1, 64, 65, 130):
+        got = ops.linear(x[:rows].contiguous(), head, out_dtype=torch.float32)
+        assert got.dtype == torch.float32
+        assert (got.bfloat16().float() != got).float().mean().item() > 0.9, f"{rows} rows: the logits look rounded to bfloat16"
+        assert (got.double() - want[:rows]).abs().max().item() <= 2e-5 * scale, f"{rows} rows: not a 32-bit sum"
+        by_rows[rows] = got
+    assert (by_rows[65][:64] - by_rows[64]).abs().max().item() <= 2e-6 * scale
+    assert (by_rows[130][:1] - by_rows[1]).abs().max().item() <= 2e-6 * scale
+    odd = rand((70, 100), torch.bfloat16, 33)            # an inner size that is no multiple of 8: the library's product
+    odd_head = rand((300, 100), torch.bfloat16, 34)
+    got = ops.linear(odd, odd_head, out_dtype=torch.float32)
+    assert (got.double() - odd.double() @ odd_head.double().T).abs().max().item() <= 2e-5 * got.abs().max().item()
+    assert (got.bfloat16().float() != got).float().mean().item() > 0.9
