@@ -8,6 +8,7 @@ workloads are what ``ncu`` is pointed at for the summaries under ``profiles/``.
     python -m llmserver_b200.cli.microbench attention-prefill --tokens 2048 [--context 32768]
     python -m llmserver_b200.cli.microbench decode-step --batch 8 --layers 4 [--eager]
     python -m llmserver_b200.cli.microbench prefill-step --tokens 2048 --layers 4
+    python -m llmserver_b200.cli.microbench decode-timeline --batch 8 --layers 8
 
 Head sizes and counts default to the Qwen3-8B shape (32 / 8 heads of 128, pages of 16 tokens).
 ``--eager`` launches kernels one by one instead of replaying a graph (what a profiler wants to see);
@@ -193,6 +194,52 @@ def bench_step(args, prefill: bool) -> dict:
     return {"workload": "decode-step", "layers": args.layers, "batch": args.batch, "context": args.context, "mode": "eager"}
 
 
+def decode_timeline(args) -> dict:
+    """When every kernel of one replayed decode step starts and ends (CUPTI activity records through torch.profiler;
+    no profiler replay, kernels overlap as they do in serving).  ``after`` is how long after the kernel before it
+    ENDED a kernel ended: the step's time is the sum of that column, so it shows what each kernel adds to the step."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    from ..sampling import SamplingRow
+    from .harness import Harness
+
+    harness = Harness(args.layers, args.batch)
+    harness.time_decode(args.batch, 4, 3)
+    harness.time_decode(args.batch, 8, 3)        # the graph exists now; the requests sit near the mean context
+    ids = list(harness.step_function.computed)[:args.batch]
+    rows = [SamplingRow() for _ in ids]
+
+    def step():
+        return harness.step_function.run_and_sample([(request_id, [1], [0]) for request_id in ids], rows)
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as recorded:
+        step()
+        torch.cuda.synchronize()
+    events = sorted((event for event in recorded.events() if event.device_type == torch.autograd.DeviceType.CUDA),
+                    key=lambda event: event.time_range.start)
+    first = next(index for index, event in enumerate(events) if "Memcpy" not in event.name and "memcpy" not in event.name)
+    events = events[first:]
+    origin, last_end, lines = events[0].time_range.start, events[0].time_range.start, []
+    for event in events:
+        begin, end = event.time_range.start - origin, event.time_range.end - origin
+        name = event.name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0].split("<")[0]
+        lines.append({"kernel": name, "start_us": round(begin, 2), "end_us": round(end, 2),
+                      "after": round(max(0.0, event.time_range.end - last_end), 2)})
+        last_end = max(last_end, event.time_range.end)
+    if not args.json_only:
+        for line in lines:
+            print(f"{line['kernel']:44s} start {line['start_us']:9.2f}  end {line['end_us']:9.2f}  adds {line['after']:7.2f}", file=sys.stderr)
+    per_kernel = {}
+    for line in lines:
+        per_kernel[line["kernel"]] = round(per_kernel.get(line["kernel"], 0.0) + line["after"], 2)
+    return {"workload": "decode-timeline", "layers": args.layers, "batch": args.batch, "kernels": len(lines),
+            "step_us": round(last_end - origin, 2), "adds_us_by_kernel": per_kernel}
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = parser.add_subparsers(dest="workload", required=True)
@@ -225,6 +272,11 @@ def main(argv=None) -> int:
     step.add_argument("--batch", type=int, default=8)
     step.add_argument("--context", type=int, default=3072)
     step.add_argument("--layers", type=int, default=4)
+    timeline = sub.add_parser("decode-timeline")
+    common(timeline)
+    timeline.add_argument("--batch", type=int, default=8)
+    timeline.add_argument("--layers", type=int, default=8)
+    timeline.add_argument("--json-only", action="store_true", help="no line per kernel on standard error")
     prompt = sub.add_parser("prefill-step")
     common(prompt)
     prompt.add_argument("--tokens", type=int, default=2048)
@@ -237,6 +289,8 @@ def main(argv=None) -> int:
         result = bench_attention(args, prefill=False)
     elif args.workload == "attention-prefill":
         result = bench_attention(args, prefill=True)
+    elif args.workload == "decode-timeline":
+        result = decode_timeline(args)
     else:
         result = bench_step(args, prefill=args.workload == "prefill-step")
     print(json.dumps(result))
