@@ -54,9 +54,13 @@ PLAN_FILE = os.environ.get("LLMSERVER_B200_GEMM_PLAN")
 _plan_loaded = False
 
 
+OWN_KERNEL = "bf16-own"      # in place of the output type in a key: the choice among this package's variants only
+
+
 def _key_text(key) -> str:
     bucket, cols, inner, out_dtype = key
-    return f"{bucket},{cols},{inner},{'f32' if out_dtype == torch.float32 else 'bf16'}"
+    kind = out_dtype if isinstance(out_dtype, str) else ("f32" if out_dtype == torch.float32 else "bf16")
+    return f"{bucket},{cols},{inner},{kind}"
 
 
 def load_plan(path: Optional[str] = None) -> int:
@@ -74,7 +78,8 @@ def load_plan(path: Optional[str] = None) -> int:
                 continue
             try:
                 bucket, cols, inner, kind, split = line.split(",")
-                key = (int(bucket), int(cols), int(inner), torch.float32 if kind == "f32" else torch.bfloat16)
+                key = (int(bucket), int(cols), int(inner),
+                       {"f32": torch.float32, "bf16": torch.bfloat16}.get(kind, kind))
                 _choice.setdefault(key, int(split))
                 count += 1
             except ValueError as error:
@@ -157,8 +162,11 @@ def _small_m(x, weight, out, split: int) -> None:
          int(out.dtype == torch.float32), split, error_flag(x.device).data_ptr(), stream_handle())
 
 
-def _plan_for(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> int:
-    """Measures, once per (rows bucket, shape), this package's kernel with a few splits of K and the
+def _plan_for(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, own_kernel_only: bool = False) -> int:
+    """``own_kernel_only``: the best split of this package's kernel, the library's product not considered (for the
+    products that finish their result in the kernel's epilogue, which the library's cannot; kept under a key of its own).
+
+    Measures, once per (rows bucket, shape), this package's kernel with a few splits of K and the
     library product, each as a model step runs it, and remembers the fastest: a split (> 0) or 0 for the library.  All candidates read
     the same operands and give the same result up to rounding, so the choice changes speed only.
     While a CUDA graph is being captured nothing can be timed: an unknown shape then uses this
@@ -166,7 +174,7 @@ def _plan_for(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> 
     global _tunings
     rows, inner = x.shape
     cols = weight.shape[0]
-    key = (_row_bucket(rows), cols, inner, out_dtype)
+    key = (_row_bucket(rows), cols, inner, OWN_KERNEL if own_kernel_only else out_dtype)
     known = _choice.get(key)
     if known is not None:
         return known
@@ -176,7 +184,7 @@ def _plan_for(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> 
             return _choice[key]
     if torch.cuda.is_current_stream_capturing():
         return -1
-    if out_dtype == torch.float32:
+    if out_dtype == torch.float32 or own_kernel_only:
         # 32-bit results always come from this package's kernel, straight from its accumulators; only the split is
         # measured (the library's product would have to be rounded to bfloat16 on the way)
         out = torch.empty((rows, cols), dtype=out_dtype, device=x.device)
@@ -281,9 +289,7 @@ def qkv_rope_fused(x: torch.Tensor, weight: torch.Tensor, q_weight, k_weight, in
         return None
     if inv_freq is not None and inv_freq.numel() * 2 != head_dim:
         return None
-    split = _plan_for(x, weight, torch.bfloat16)
-    if split == 0:          # the library's product won the measurement for this shape: no epilogue to fuse into
-        return None
+    split = _plan_for(x, weight, torch.bfloat16, own_kernel_only=True)      # at most 16 rows: this package's kernel
     out = torch.empty((rows, weight.shape[0]), dtype=torch.bfloat16, device=x.device)
     call("llm_gemm_qkv_rope", x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, inner, weight.shape[0], max(split, 0),
          0 if q_weight is None else q_weight.data_ptr(), 0 if k_weight is None else k_weight.data_ptr(),
@@ -306,9 +312,14 @@ def gate_up_silu_fused(x: torch.Tensor, weight: torch.Tensor) -> Optional[torch.
     if not (FUSE_GATE_UP_SILU and rows <= SMALL_M and cols % 128 == 0 and x.is_contiguous() and weight.is_contiguous()
             and weight.dtype == torch.bfloat16 and small_m_supported(rows, cols, inner)):
         return None
-    split = _plan_for(x, weight, torch.bfloat16)
-    if split == 0:
-        return None
+    # up to 16 rows this package's kernel, whatever a measurement of the bare products says (whole steps are faster with
+    # it there, and the activation kernel goes away); with more rows the fused form only where the bare kernel wins
+    if rows <= 16:
+        split = _plan_for(x, weight, torch.bfloat16, own_kernel_only=True)
+    else:
+        split = _plan_for(x, weight, torch.bfloat16)
+        if split == 0:
+            return None
     out = torch.empty((rows, cols // 2), dtype=torch.bfloat16, device=x.device)
     call("llm_gemm_gate_up_silu", x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, cols, inner, cols // 2, max(split, 0),
          error_flag(x.device).data_ptr(), stream_handle())

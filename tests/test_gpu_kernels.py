@@ -103,6 +103,7 @@ def test_gate_up_product_with_the_gate_in_its_epilogue(rows, hidden, inter, spli
     up = (rand((inter, hidden), dtype, 92).float() * hidden ** -0.5 * 3).to(dtype)
     weight = ops.interleave_gate_up(gate, up)
     assert torch.equal(weight[64:128], up[:64]) and torch.equal(weight[128:192], gate[64:128])
+    gemm_bf16._choice[(gemm_bf16._row_bucket(rows), 2 * inter, hidden, gemm_bf16.OWN_KERNEL)] = split
     gemm_bf16._choice[(gemm_bf16._row_bucket(rows), 2 * inter, hidden, torch.bfloat16)] = split
     want = torch.nn.functional.silu(x.double() @ gate.double().T) * (x.double() @ up.double().T)
     launches = ops.launch_count()
@@ -274,7 +275,7 @@ def test_qkv_projection_with_the_rotation_in_its_epilogue(tokens, heads, kv_head
     results = {}
     # this package's kernel for the shape, with K divided into 1, 2 or 4 parts (a measurement may prefer the library's
     # product, which has no epilogue to fuse into)
-    gemm_bf16._choice[(gemm_bf16._row_bucket(tokens), width, hidden, torch.bfloat16)] = {1: 1, 5: 2, 8: 3, 16: 4}[tokens]
+    gemm_bf16._choice[(gemm_bf16._row_bucket(tokens), width, hidden, gemm_bf16.OWN_KERNEL)] = {1: 1, 5: 2, 8: 3, 16: 4}[tokens]
     for fused in (True, False):
         gemm_bf16.FUSE_QKV_ROPE = fused
         k_pages = torch.zeros((n_pages, kv_heads, page_size, dim), dtype=dtype, device=DEVICE)
