@@ -168,9 +168,10 @@ class DecodeGraphs:
         self.table_width = -(-max_context // cache.page_size)
         self.graphs: Dict[int, DecodeGraph] = {}
         self.seen: Dict[int, int] = {}
-        # a mixer that keeps state per request runs host code per row: nothing to capture, and padding rows
-        # would have to own a state slot
-        self.failed = bool(cache.state_entries)
+        # every mixer has to say that it can be captured; and rows that only pad a batch would have to own a state
+        # slot, which the slot allocator does not set aside
+        mixers = [getattr(layer, "mixer", None) for layer in getattr(model, "layers", [])]
+        self.failed = bool(cache.state_entries) or any(not getattr(mixer, "capturable", True) for mixer in mixers)
         self.null_pages = None
 
     def forget_rows(self) -> None:

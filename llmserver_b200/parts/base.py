@@ -54,6 +54,11 @@ class Part:
 
 
 class Mixer(Part):
+    # Whether ``forward`` can be captured in a CUDA graph and replayed: it must launch the same kernels whatever the
+    # batch holds and read nothing of the batch on the host.  A mixer that walks its rows in Python says False; decode
+    # steps of a model that has one run eagerly.
+    capturable = True
+
     @classmethod
     def cache_need(cls, params: dict):
         """``KVPagesNeed``, ``StateNeed`` or None: what one execution of this mixer keeps per request."""

@@ -21,6 +21,8 @@ def register_toy():
     class DecayingSum(Mixer):
         """state <- decay * state + x_t ; out_t = state W^T.  State: one float32 [hidden] row per request."""
 
+        capturable = False        # walks the batch's rows on the host
+
         @classmethod
         def declare_weights(cls, params):
             return {"mix.weight": WeightDecl((params["hidden"], params["hidden"]))}
