@@ -76,7 +76,7 @@ def plan(batch, group: int, n_kv_heads: int, device=None):
     cached = batch.scratch.get(key)
     if cached is not None:
         return cached
-    wave_blocks = DECODE_BLOCKS_PER_SM * _sm_count(device if device is not None else batch.token_ids.device)
+    wave_blocks = DECODE_BLOCKS_PER_SM * _sm_count(device if device is not None else batch.context_len.device)
     singles = sum(1 for length in batch.q_lens if length == 1)
     run_decode = singles > 0
     run_portions = singles < batch.n_seqs
