@@ -633,3 +633,16 @@ def test_float32_logits_are_32_bit_sums_whatever_the_number_of_rows():
     got = ops.linear(odd, odd_head, out_dtype=torch.float32)
     assert (got.double() - odd.double() @ odd_head.double().T).abs().max().item() <= 2e-5 * got.abs().max().item()
     assert (got.bfloat16().float() != got).float().mean().item() > 0.9
+
+
+def test_the_microbenchmarks_run(capsys):
+    """The workloads the profiler is pointed at, at small sizes: each must run and print its JSON line."""
+    import json
+    from llmserver_b200.cli import microbench
+    for arguments in (["gemm", "--rows", "8", "--out-features", "1024", "--in-features", "512"],
+                      ["attention-decode", "--batch", "3", "--context", "300"],
+                      ["attention-prefill", "--tokens", "300"],
+                      ["attention-prefill", "--tokens", "128", "--context", "700", "--shuffle-pages"]):
+        assert microbench.main(arguments) == 0
+        report = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+        assert report["workload"] == arguments[0] and report.get("us", report.get("tcgen05_us", 0)) > 0
