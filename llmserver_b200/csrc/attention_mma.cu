@@ -9,8 +9,10 @@
 //     from the first key the tile's window can see to the last token's own position (causal).
 //   * decode (q_len == 1): one block per (split of the keys, kv head, sequence).  The G heads are the
 //     rows (padded to 16); the four warps take 16 keys each of every 64-key tile, then merge.  With more
-//     than one split per sequence the partial results go to scratch memory and a second kernel merges
-//     them (split-KV, as the reference's paged decode: utils/paged_attention.py:168-237).
+//     than one split per sequence the splits' results are merged (split-KV, as the reference's paged
+//     decode: utils/paged_attention.py:168-237): up to 8 splits form a thread-block cluster and merge
+//     through distributed shared memory inside the TMA kernel; otherwise they go to scratch memory and a
+//     second kernel merges them.  Both add the splits in the same order with the same arithmetic.
 //
 // K and V tiles travel global -> shared with cp.async (16-byte chunks, two stages), each key's page
 // looked up in the block table, so a page size is only a divisor here.  Shared tiles are XOR-swizzled by

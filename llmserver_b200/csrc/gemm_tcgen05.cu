@@ -11,9 +11,16 @@
 // a fixed order (rank 0, 1, ...), so results do not depend on timing.
 //
 // One elected thread issues the TMA copies, one issues the MMAs; mbarriers carry "stage full" (TMA
-// transaction bytes), "stage free" and "accumulator ready" (tcgen05.commit).  Every wait is bounded: a
-// wait that runs out sets an error flag that the host reads, and the CTA still frees its tensor memory
-// and leaves in step with its cluster.
+// transaction bytes), "stage free" and "accumulator ready" (tcgen05.commit).  The thread that initialises the
+// barriers requests the weight tiles of the first ring of stages at once, before the block's first barrier and
+// before griddepcontrol.wait (weights do not depend on the kernel in front); the token tiles follow after the
+// wait.  Every wait is bounded: a wait that runs out sets an error flag that the host reads, and the CTA still
+// frees its tensor memory and leaves in step with its cluster.
+//
+// Two optional epilogues finish a decode step's results where they are, instead of in a kernel of their own:
+// the q/k/v projection with heads of 128 (the 128 rows of W a CTA owns are one head) normalises and rotates each
+// head and writes K and V into the cache pages (RopeEpilogue); the fused gate/up projection, whose weight holds
+// 64 gate rows and their 64 up rows per tile, writes silu(gate) * up (silu_gate).
 //
 // Out-of-range rows of W (N not a multiple of 128), token rows beyond M and a K that is no multiple of
 // 64 are zero-filled by TMA.  K must be a multiple of 8 (16-byte row pitch) and the pointers 16-byte
