@@ -53,6 +53,8 @@ struct AttnParams {
     int max_splits;
     float* partial_out;      // [N, Hq, max_splits, D]
     float* partial_ml;       // [N, Hq, max_splits, 2]
+    int old_keys_settled;    // TMA decode kernel: every key but each sequence's newest was written before the kernel in
+                             // front of this one started (by an earlier step), so their copies need not wait for it
     int cluster_merge;       // TMA decode kernel: the splits of a sequence form a thread-block cluster and merge their
                              // partial results through distributed shared memory (no scratch, no merge kernel)
     int slot_by_seq;         // scratch slots are counted by sequence instead of by the sequence's token index
@@ -558,7 +560,13 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
                                                                               const __grid_constant__ CUtensorMap map_v,
                                                                               const AttnParams p) {
     pdl_trigger();   // let the next kernel start launching
-    pdl_wait();      // everything before this kernel in the stream is complete and visible
+    // Normally everything before this kernel must be complete before it reads anything.  When the caller vouches that
+    // only each sequence's newest key is written by the kernel in front (a decode step: older keys come from earlier
+    // steps, behind the step's batch copy), the copies of older keys start at once and overlap that kernel's end; Q,
+    // the newest key's tile and every write wait.  Each block still waits before it leaves, so that this kernel never
+    // completes before the one in front has.
+    const bool early = p.old_keys_settled != 0;
+    if (!early) pdl_wait();
     extern __shared__ __align__(16) unsigned char shared_raw[];
     __shared__ __align__(8) uint64_t full_bar[kDecodeStages];
     __shared__ __align__(8) uint64_t empty_bar[kDecodeStages];
@@ -575,7 +583,10 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
 
     const int seq = blockIdx.z, kv_head = blockIdx.y, split = blockIdx.x;
     const int token = p.q_start[seq];
-    if (p.q_start[seq + 1] - token != 1) return;
+    if (p.q_start[seq + 1] - token != 1) {
+        if (early) pdl_wait();
+        return;
+    }
     const int group = p.n_q_heads / p.n_kv_heads;
     const int context = p.context_len[seq];
     const int position = context - 1;
@@ -584,11 +595,15 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
     const int split_len = split_length(p, context - first_key);
     const int n_splits = (context - first_key + split_len - 1) / split_len;
     if (n_splits > p.max_splits && split == 0 && kv_head == 0 && threadIdx.x == 0 && p.error_flag) atomicExch(p.error_flag, 6);
-    if (context <= 0 && split == 0) zero_output<D>(p, token, kv_head, group);     // nothing to attend to
+    if (context <= 0 && split == 0) {       // nothing to attend to
+        if (early) pdl_wait();
+        zero_output<D>(p, token, kv_head, group);
+    }
     // every thread of a cluster whose splits merge in shared memory meets at the same two cluster barriers, also the
     // blocks beyond the sequence's last split and the producer warps, which have nothing to add
     const bool meets_cluster = p.cluster_merge && n_splits > 1;
     if (split >= n_splits) {
+        if (early) pdl_wait();
         if (meets_cluster) {
             cluster_arrive_wait();
             cluster_arrive_wait();
@@ -621,8 +636,15 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
         const int pages_per_tile = kTileKeys / p.page_size;
         const int copies = pages_per_tile * kBoxesPerPage * 2;
         const int my_page = lane / (kBoxesPerPage * 2), my_half = (lane / 2) % kBoxesPerPage, my_v = lane & 1;
+        bool waited = !early;
         for (int t = 0; t < n_tiles; ++t) {
             const int s = t % kDecodeStages;
+            // the tile that may hold the sequence's newest key (the last tile of the last split) is written by the
+            // kernel in front of this one
+            if (!waited && split == n_splits - 1 && t == n_tiles - 1) {
+                pdl_wait();
+                waited = true;
+            }
             bool ok = true;
             if (t >= kDecodeStages) ok = tma::mbar_wait(tma::smem_u32(&empty_bar[s]), ((t / kDecodeStages) - 1) & 1);
             if (!ok) {
@@ -648,6 +670,7 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
                 }
             }
         }
+        if (!waited) pdl_wait();
         if (meets_cluster) {
             cluster_arrive_wait();
             cluster_arrive_wait();
@@ -656,6 +679,7 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
     }
 
     // ---- consumer warps: gather Q (plain loads into the XOR layout), then walk the tiles
+    if (early) pdl_wait();        // Q comes from the kernel in front
     {
         constexpr int kChunks = D / 8;
         for (int c = threadIdx.x; c < 16 * kChunks; c += kThreads) {
@@ -923,6 +947,9 @@ LLM_EXPORT int llm_attention_mma_supports(int head_dim, int n_q_heads, int n_kv_
     return n_q_heads / n_kv_heads <= 16;
 }
 
+// old_keys_settled: the caller vouches that, of the keys the decode rows read, only each sequence's newest was written
+// by the kernel launched just before this call (everything older by kernels that completed earlier, e.g. earlier
+// steps behind a copy): the decode kernel then starts copying older keys without waiting for that kernel.
 // run_portions / run_decode: which of the two kernels to launch (a mixed batch launches both; each
 // skips the other's sequences).  total_tiles: sum over sequences of ceil(q_len * group / 64), counting
 // sequences of one token only when the decode kernel is not run.
@@ -931,7 +958,7 @@ LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, const void* k_page
                                  void* out, int n_seqs, int n_q_heads, int n_kv_heads, int head_dim, int page_size,
                                  int num_pages, float scale, int window, int run_portions, int total_tiles, int run_decode,
                                  int split_len, int max_splits, float* partial_out, float* partial_ml,
-                                 int* error_flag, cudaStream_t stream) {
+                                 int old_keys_settled, int* error_flag, cudaStream_t stream) {
     if (!llm_attention_mma_supports(head_dim, n_q_heads, n_kv_heads)) {
         llm_set_error("attention_mma: head_dim %d with %d/%d heads is not supported (head_dim 64 or 128, group <= 16)",
                       head_dim, n_q_heads, n_kv_heads);
@@ -959,6 +986,7 @@ LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, const void* k_page
     p.num_pages = num_pages;
     p.slot_by_seq = 0;
     p.cluster_merge = decode_cluster_merge_enabled() ? 1 : 0;
+    p.old_keys_settled = old_keys_settled;
     p.q_start = q_start;
     p.context_len = context_len;
     p.out = (__nv_bfloat16*)out;
@@ -1072,6 +1100,7 @@ LLM_EXPORT int llm_attention_decode_noalloc(const void* q, int q_stride, const v
     p.num_pages = num_pages;
     p.slot_by_seq = 1;      // the size check above counts sequences, whatever q_start holds
     p.cluster_merge = 0;    // this entry is the one that merges through the fixed scratch array
+    p.old_keys_settled = 0;
     p.q_start = q_start;
     p.context_len = context_len;
     p.out = (__nv_bfloat16*)out;

@@ -92,6 +92,11 @@ class StepBatch:
     decode_only: bool = False
     host_bytes: int = 0
     scratch: dict = field(default_factory=dict)   # per-step data kernels' wrappers derive once
+    # A request's tokens before this step's were cached by earlier steps, and this step begins with the copy of its
+    # batch to the device, behind which those steps are complete: kernels may read such keys without waiting for the
+    # kernel launched just before them.  True for every batch packed here; a hand-made batch that fills the cache and
+    # reads it in the same breath must say False.
+    keys_settled: bool = True
 
 
 def layout_of(slices: List[SequenceSlice], n_groups: int, min_table_width: int = 1) -> BatchLayout:

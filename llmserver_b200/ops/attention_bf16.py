@@ -118,6 +118,12 @@ def plan(batch, group: int, n_kv_heads: int, device=None):
     return cached
 
 
+# A decode row's older keys were cached by earlier steps, which lie behind the step's batch copy; the decode kernel may
+# start copying them before the kernel in front of it (which writes the newest key) has ended.  Only batches that say
+# so (``keys_settled``, set where the engine packs a step) get this.
+EARLY_KEYS = os.environ.get("LLMSERVER_B200_DECODE_EARLY_KEYS", "1") != "0"
+
+
 def try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim, scale, window):
     if not supported(head_dim, n_q_heads, n_kv_heads):
         return None
@@ -166,5 +172,6 @@ def try_attention(qkv, q_stride, batch, block_tables, k_pages, v_pages, n_q_head
          block_tables.shape[-1], batch.q_start.data_ptr(), batch.context_len.data_ptr(), out.data_ptr(), batch.n_seqs,
          n_q_heads, n_kv_heads, head_dim, page_size, k_pages.shape[0], float(scale), int(window), int(run_portions), tiles,
          int(run_decode), split_len, max_splits, 0 if partial_out is None else partial_out.data_ptr(),
-         0 if partial_ml is None else partial_ml.data_ptr(), flag, stream_handle())
+         0 if partial_ml is None else partial_ml.data_ptr(), int(EARLY_KEYS and getattr(batch, "keys_settled", False)), flag,
+         stream_handle())
     return out

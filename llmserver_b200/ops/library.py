@@ -35,7 +35,7 @@ SIGNATURES = {
     "llm_gemm_gate_up_silu": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _S],
     "llm_gemm_qkv_rope_supports": [_I, _I, _I, _I, _I],
     "llm_gemm_qkv_rope": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _S],
-    "llm_attention_mma": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _I, _I, _P, _P, _P, _S],
+    "llm_attention_mma": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _S],
 }
 
 _lock = threading.Lock()
