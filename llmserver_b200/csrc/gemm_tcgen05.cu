@@ -506,10 +506,11 @@ LLM_EXPORT int llm_gemm_small_m(const void* x, const void* w, void* out, int m, 
     return small_m_launch(x, w, out, m, n, k, ldc, out_is_f32, requested_split, error_flag, nullptr, stream);
 }
 
-// 1 when the fused q/k/v projection takes the sizes: heads of 128 (a head is a tile of the product), few tokens (each
-// costs a block-wide reduction in the epilogue), and what llm_gemm_small_m itself needs.
+// 1 when the fused q/k/v projection takes the sizes: heads of 128 (a head is a tile of the product), up to 64 tokens
+// (each costs a block-wide reduction in the epilogue of the block that finishes it: with many tokens the caller
+// measures whether the fused form still wins), and what llm_gemm_small_m itself needs.
 LLM_EXPORT int llm_gemm_qkv_rope_supports(int m, int n_q_heads, int n_kv_heads, int head_dim, int k) {
-    return head_dim == kBlockRows && m >= 1 && m <= 16 && n_q_heads >= 1 && n_kv_heads >= 1 &&
+    return head_dim == kBlockRows && m >= 1 && m <= 64 && n_q_heads >= 1 && n_kv_heads >= 1 &&
            llm_gemm_small_m_supports(m, (n_q_heads + 2 * n_kv_heads) * head_dim, k);
 }
 
@@ -524,7 +525,7 @@ LLM_EXPORT int llm_gemm_qkv_rope(const void* x, const void* w, void* qkv, int m,
                                  int num_pages, float eps, int write_cache, int* page_error, int* error_flag,
                                  cudaStream_t stream) {
     if (!llm_gemm_qkv_rope_supports(m, n_q_heads, n_kv_heads, head_dim, k)) {
-        llm_set_error("gemm_qkv_rope: takes heads of 128 and 1..16 tokens (got head_dim %d, m %d, k %d)", head_dim, m, k);
+        llm_set_error("gemm_qkv_rope: takes heads of 128 and 1..64 tokens (got head_dim %d, m %d, k %d)", head_dim, m, k);
         return LLM_REFUSED;
     }
     if (positions == nullptr || seq_of_token == nullptr || block_tables == nullptr || page_error == nullptr ||

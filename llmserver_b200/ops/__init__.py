@@ -244,9 +244,10 @@ def qkv_projection(x: torch.Tensor, weight: torch.Tensor, q_weight: Optional[tor
                    head_dim: int, eps: float, write_cache: bool, error_flag: torch.Tensor, rotary_dim: Optional[int] = None,
                    interleaved: bool = False) -> torch.Tensor:
     """qkv = x W^T followed by ``qk_norm_rope_kv_write``: as one kernel where the product kernel can finish heads in its
-    epilogue (bfloat16, heads of 128, up to 16 tokens, the whole head rotating in halves), else as two."""
+    epilogue (bfloat16, heads of 128, up to 64 tokens, the whole head rotating in halves; from 17 tokens on only where
+    that is measured to be faster), else as two."""
     whole_head = rotary_dim is None or rotary_dim == head_dim
-    if x.dtype == torch.bfloat16 and whole_head and not interleaved and x.shape[0] <= 16:
+    if x.dtype == torch.bfloat16 and whole_head and not interleaved and x.shape[0] <= 64:
         from . import gemm_bf16
         fused = gemm_bf16.qkv_rope_fused(x, weight, q_weight, k_weight, inv_freq, positions, seq_of_token, block_tables,
                                          k_pages, v_pages, n_q_heads, n_kv_heads, head_dim, eps, write_cache, error_flag)

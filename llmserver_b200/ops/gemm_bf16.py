@@ -268,6 +268,37 @@ def _float32_by_library(x: torch.Tensor, weight: torch.Tensor, out: Optional[tor
     return result
 
 
+def _plan_fused(kind: str, rows: int, cols: int, inner: int, fused, apart, device) -> int:
+    """For 17 to 64 rows: the split with which the fused kernel ``fused(split)`` is fastest inside a step, or 0 when
+    the library's product followed by the kernel of its own (``apart()``) is faster.  Measured once per (kind, row
+    bucket, shape), kept with the other choices (and in the plan file).  While a graph is being captured nothing can
+    be measured: an unknown shape then runs apart."""
+    global _tunings
+    key = (_row_bucket(rows), cols, inner, kind)
+    known = _choice.get(key)
+    if known is not None:
+        return known
+    if not _plan_loaded:
+        load_plan()
+        if key in _choice:
+            return _choice[key]
+    if torch.cuda.is_current_stream_capturing():
+        return 0
+    best, best_time = 0, _time_in_step(apart, device)
+    tiles, k_blocks = -(-cols // 128), -(-inner // 128)
+    for split in SPLITS:
+        if split > 1 and (tiles * split > 600 or k_blocks // split < 2):
+            continue
+        elapsed = _time_in_step(lambda: fused(split), device)
+        if elapsed < best_time:
+            best_time, best = elapsed, split
+    _choice[key] = best
+    _tunings += 1
+    if PLAN_FILE:
+        save_plan()
+    return best
+
+
 FUSE_QKV_ROPE = os.environ.get("LLMSERVER_B200_FUSE_QKV_ROPE", "1") != "0"
 
 
@@ -289,14 +320,29 @@ def qkv_rope_fused(x: torch.Tensor, weight: torch.Tensor, q_weight, k_weight, in
         return None
     if inv_freq is not None and inv_freq.numel() * 2 != head_dim:
         return None
-    split = _plan_for(x, weight, torch.bfloat16, own_kernel_only=True)      # at most 16 rows: this package's kernel
     out = torch.empty((rows, weight.shape[0]), dtype=torch.bfloat16, device=x.device)
-    call("llm_gemm_qkv_rope", x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, inner, weight.shape[0], max(split, 0),
-         0 if q_weight is None else q_weight.data_ptr(), 0 if k_weight is None else k_weight.data_ptr(),
-         int(q_weight is not None and q_weight.dtype == torch.float32), 0 if inv_freq is None else inv_freq.data_ptr(),
-         positions.data_ptr(), seq_of_token.data_ptr(), block_tables.data_ptr(), block_tables.shape[-1],
-         k_pages.data_ptr(), v_pages.data_ptr(), n_q_heads, n_kv_heads, head_dim, k_pages.shape[2], k_pages.shape[0],
-         float(eps), int(write_cache), page_error.data_ptr(), error_flag(x.device).data_ptr(), stream_handle())
+
+    def fused(split: int) -> None:
+        call("llm_gemm_qkv_rope", x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, inner, weight.shape[0], split,
+             0 if q_weight is None else q_weight.data_ptr(), 0 if k_weight is None else k_weight.data_ptr(),
+             int(q_weight is not None and q_weight.dtype == torch.float32), 0 if inv_freq is None else inv_freq.data_ptr(),
+             positions.data_ptr(), seq_of_token.data_ptr(), block_tables.data_ptr(), block_tables.shape[-1],
+             k_pages.data_ptr(), v_pages.data_ptr(), n_q_heads, n_kv_heads, head_dim, k_pages.shape[2], k_pages.shape[0],
+             float(eps), int(write_cache), page_error.data_ptr(), error_flag(x.device).data_ptr(), stream_handle())
+
+    if rows <= 16:
+        split = _plan_for(x, weight, torch.bfloat16, own_kernel_only=True)      # few rows: always this package's kernel
+    else:
+        def apart() -> None:      # what the caller would run instead (it writes the same values to the same places)
+            from . import qk_norm_rope_kv_write
+            torch.matmul(x, weight.t(), out=out)
+            qk_norm_rope_kv_write(out, q_weight, k_weight, inv_freq, positions, seq_of_token, block_tables, k_pages, v_pages,
+                                  n_q_heads, n_kv_heads, head_dim, eps, write_cache, page_error)
+
+        split = _plan_fused("qkv-rope", rows, weight.shape[0], inner, fused, apart, x.device)
+        if split == 0:
+            return None
+    fused(max(split, 0))
     return out
 
 
@@ -312,15 +358,24 @@ def gate_up_silu_fused(x: torch.Tensor, weight: torch.Tensor) -> Optional[torch.
     if not (FUSE_GATE_UP_SILU and rows <= SMALL_M and cols % 128 == 0 and x.is_contiguous() and weight.is_contiguous()
             and weight.dtype == torch.bfloat16 and small_m_supported(rows, cols, inner)):
         return None
+    out = torch.empty((rows, cols // 2), dtype=torch.bfloat16, device=x.device)
+
+    def fused(split: int) -> None:
+        call("llm_gemm_gate_up_silu", x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, cols, inner, cols // 2, split,
+             error_flag(x.device).data_ptr(), stream_handle())
+
     # up to 16 rows this package's kernel, whatever a measurement of the bare products says (whole steps are faster with
-    # it there, and the activation kernel goes away); with more rows the fused form only where the bare kernel wins
+    # it there, and the activation kernel goes away); with more rows whichever is measured faster: the fused kernel, or
+    # the library's product followed by the activation kernel
     if rows <= 16:
         split = _plan_for(x, weight, torch.bfloat16, own_kernel_only=True)
     else:
-        split = _plan_for(x, weight, torch.bfloat16)
+        def apart() -> None:
+            from . import silu_mul
+            silu_mul(torch.matmul(x, weight.t()), out=out, group=64)
+
+        split = _plan_fused("gate-up-silu", rows, cols, inner, fused, apart, x.device)
         if split == 0:
             return None
-    out = torch.empty((rows, cols // 2), dtype=torch.bfloat16, device=x.device)
-    call("llm_gemm_gate_up_silu", x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, cols, inner, cols // 2, max(split, 0),
-         error_flag(x.device).data_ptr(), stream_handle())
+    fused(max(split, 0))
     return out

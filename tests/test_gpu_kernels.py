@@ -104,6 +104,7 @@ def test_gate_up_product_with_the_gate_in_its_epilogue(rows, hidden, inter, spli
     weight = ops.interleave_gate_up(gate, up)
     assert torch.equal(weight[64:128], up[:64]) and torch.equal(weight[128:192], gate[64:128])
     gemm_bf16._choice[(gemm_bf16._row_bucket(rows), 2 * inter, hidden, gemm_bf16.OWN_KERNEL)] = split
+    gemm_bf16._choice[(gemm_bf16._row_bucket(rows), 2 * inter, hidden, "gate-up-silu")] = split
     gemm_bf16._choice[(gemm_bf16._row_bucket(rows), 2 * inter, hidden, torch.bfloat16)] = split
     want = torch.nn.functional.silu(x.double() @ gate.double().T) * (x.double() @ up.double().T)
     launches = ops.launch_count()
@@ -255,7 +256,7 @@ def test_attention_finds_a_far_key_and_respects_the_window_edge(dtype):
 
 @pytest.mark.parametrize("tokens,heads,kv_heads,hidden,qk_norm,weight_dtype", [
     (1, 8, 2, 256, True, torch.bfloat16), (5, 4, 4, 1024, True, torch.float32), (16, 32, 8, 4096, True, torch.bfloat16),
-    (8, 6, 1, 512, False, torch.bfloat16)])
+    (8, 6, 1, 512, False, torch.bfloat16), (41, 8, 2, 1024, True, torch.bfloat16), (64, 4, 1, 512, True, torch.float32)])
 def test_qkv_projection_with_the_rotation_in_its_epilogue(tokens, heads, kv_heads, hidden, qk_norm, weight_dtype):
     """Heads of 128 and few tokens: the product kernel finishes each head itself (norm, rotation, cache write).  Against
     plain arithmetic in float64 and against the two separate kernels."""
@@ -275,7 +276,9 @@ def test_qkv_projection_with_the_rotation_in_its_epilogue(tokens, heads, kv_head
     results = {}
     # this package's kernel for the shape, with K divided into 1, 2 or 4 parts (a measurement may prefer the library's
     # product, which has no epilogue to fuse into)
-    gemm_bf16._choice[(gemm_bf16._row_bucket(tokens), width, hidden, gemm_bf16.OWN_KERNEL)] = {1: 1, 5: 2, 8: 3, 16: 4}[tokens]
+    split = {1: 1, 5: 2, 8: 3, 16: 4, 41: 2, 64: 1}[tokens]
+    gemm_bf16._choice[(gemm_bf16._row_bucket(tokens), width, hidden, gemm_bf16.OWN_KERNEL)] = split
+    gemm_bf16._choice[(gemm_bf16._row_bucket(tokens), width, hidden, "qkv-rope")] = split
     for fused in (True, False):
         gemm_bf16.FUSE_QKV_ROPE = fused
         k_pages = torch.zeros((n_pages, kv_heads, page_size, dim), dtype=dtype, device=DEVICE)
