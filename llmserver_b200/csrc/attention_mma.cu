@@ -793,16 +793,30 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
         // kernel below, reading the other ranks' shared memory.
         cluster_arrive_wait();
         const uint32_t mine_address = smem_address(mine);
+        constexpr int kMaxRanks = 8;      // the portable cluster size: the launcher merges more splits by the merge kernel
         for (int index = split * kThreads + threadIdx.x; index < group * D; index += n_splits * kThreads) {
             const int r = index / D, d = index % D;
+            // all ranks' values are asked for before the first is used: a load from another block's shared memory
+            // takes some hundred cycles, and one after the other they were most of this kernel's time with few keys
+            float maxima[kMaxRanks], sums[kMaxRanks], outputs[kMaxRanks];
+#pragma unroll
+            for (int s = 0; s < kMaxRanks; ++s) {
+                const bool present = s < n_splits;
+                maxima[s] = present ? load_cluster(mine_address + (uint32_t)(r * (D + 2) + D) * 4u, (uint32_t)s) : -INFINITY;
+                sums[s] = present ? load_cluster(mine_address + (uint32_t)(r * (D + 2) + D + 1) * 4u, (uint32_t)s) : 0.0f;
+                outputs[s] = present ? load_cluster(mine_address + (uint32_t)(r * (D + 2) + d) * 4u, (uint32_t)s) : 0.0f;
+            }
             float best = -INFINITY;
-            for (int s = 0; s < n_splits; ++s) best = fmaxf(best, load_cluster(mine_address + (uint32_t)(r * (D + 2) + D) * 4u, (uint32_t)s));
+#pragma unroll
+            for (int s = 0; s < kMaxRanks; ++s) best = fmaxf(best, maxima[s]);
             float numerator = 0.0f, denominator = 0.0f;
-            for (int s = 0; s < n_splits; ++s) {
-                const float weight = load_cluster(mine_address + (uint32_t)(r * (D + 2) + D + 1) * 4u, (uint32_t)s) *
-                                     exp2f(load_cluster(mine_address + (uint32_t)(r * (D + 2) + D) * 4u, (uint32_t)s) - best);
-                numerator += load_cluster(mine_address + (uint32_t)(r * (D + 2) + d) * 4u, (uint32_t)s) * weight;
-                denominator += weight;
+#pragma unroll
+            for (int s = 0; s < kMaxRanks; ++s) {
+                if (s < n_splits) {       // in the order of the ranks, with the merge kernel's arithmetic
+                    const float weight = sums[s] * exp2f(maxima[s] - best);
+                    numerator += outputs[s] * weight;
+                    denominator += weight;
+                }
             }
             p.out[(size_t)token * p.n_q_heads * D + (size_t)(kv_head * group + r) * D + d] = __float2bfloat16_rn(numerator / denominator);
         }
