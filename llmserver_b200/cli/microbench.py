@@ -75,7 +75,7 @@ def bench_gemm(args) -> dict:
     def ours():
         for weight, out in zip(weights, outs):
             call("llm_gemm_small_m", x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, cols, inner, cols, 0,
-                 args.split, flag.data_ptr(), stream_handle())
+                 args.split, *gemm_bf16.NO_SCALE, flag.data_ptr(), stream_handle())
 
     def library():
         for weight, out in zip(weights, outs):

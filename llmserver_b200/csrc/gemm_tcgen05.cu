@@ -22,6 +22,13 @@
 // head and writes K and V into the cache pages (RopeEpilogue); the fused gate/up projection, whose weight holds
 // 64 gate rows and their 64 up rows per tile, writes silu(gate) * up (silu_gate).
 //
+// Two more options take the stand-alone residual-add + RMSNorm kernels out of a decode step.  A product whose result
+// is added to the 32-bit residual stream does so in its epilogue (StreamEpilogue), and leaves for the RMSNorm that
+// follows the stream times the norm's weight, rounded to bfloat16, and the sums of squares of the updated stream per
+// token and per warp's 32 columns.  The product that consumes the norm's output takes those (RowScale): it adds the
+// partial sums in a fixed order, and multiplies its 32-bit accumulators token by token with 1 / rms, since
+// W (s w x) = s W (w x) for a scalar s per token.  Statistics, scale and residual sum stay 32-bit.
+//
 // Out-of-range rows of W (N not a multiple of 128), token rows beyond M and a K that is no multiple of
 // 64 are zero-filled by TMA.  K must be a multiple of 8 (16-byte row pitch) and the pointers 16-byte
 // aligned; otherwise the launcher refuses and the caller uses the library product.
@@ -62,6 +69,28 @@ struct RopeEpilogue {
     int* page_error;           // set to 1 + token when a token's page is outside the pool
 };
 
+// The input rows are a residual stream times a norm's weight, not yet divided by their root mean square: the sums of
+// squares of the stream rows lie in parts[i * stride + token], i < n_parts; the accumulators of token m are multiplied
+// with rsqrt(sum_i parts[i][m] / k + eps).  parts == null: no scaling.
+struct RowScale {
+    const float* parts;
+    int n_parts, stride;
+    float eps;
+};
+
+// The product is added to the residual stream [m, n] (32-bit, row pitch n) where it lies.  With next_weight, the
+// updated stream times next_weight [n] is written to `scaled` (bfloat16, row pitch n) and the sums of squares of
+// the updated stream to parts[(4 * tile + warp) * stride + token], for the RowScale of the next product.
+struct StreamEpilogue {
+    int on;
+    float* residual;
+    const void* next_weight;
+    int weight_is_f32;
+    __nv_bfloat16* scaled;
+    float* parts;
+    int stride;
+};
+
 struct GemmParams {
     void* out;
     int out_is_f32;
@@ -74,6 +103,8 @@ struct GemmParams {
     RopeEpilogue rope;
     int silu_gate;      // 1: rows 0..63 of a tile are gate rows and rows 64..127 their up rows; the epilogue writes
                         // silu(gate) * up into an output of n / 2 columns
+    RowScale scale;
+    StreamEpilogue stream;
 };
 
 using tma::mbar_expect_tx;
@@ -199,6 +230,27 @@ __device__ __forceinline__ void silu_finish(const GemmParams& p, int m, int row,
     __syncthreads();
 }
 
+// One finished element of a product that is added to the residual stream: token m, column tile * 128 + row; `before`
+// is the stream's value there (0 outside the matrix).  Called by whole warps with the same m.
+__device__ __forceinline__ void stream_finish(const GemmParams& p, int m, int row, int tile, float value, float before) {
+    const StreamEpilogue& e = p.stream;
+    const int n = tile * kBlockRows + row;
+    float updated = 0.0f;
+    if (n < p.n) {
+        updated = before + value;
+        e.residual[(size_t)m * p.n + n] = updated;
+        if (e.next_weight != nullptr) {
+            const float w = e.weight_is_f32 ? reinterpret_cast<const float*>(e.next_weight)[n]
+                                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(e.next_weight)[n]);
+            e.scaled[(size_t)m * p.n + n] = __float2bfloat16_rn(updated * w);
+        }
+    }
+    if (e.next_weight != nullptr) {
+        const float squares = warp_sum(updated * updated);
+        if ((row & 31) == 0) e.parts[(size_t)(tile * 4 + (row >> 5)) * e.stride + m] = squares;
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x,
                                                                 const GemmParams p) {
@@ -209,6 +261,7 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed;
     __shared__ float exchange[kBlockRows + 4];      // rope epilogue: a head's elements and its warps' sums
+    __shared__ float row_scale[64];                 // RowScale: 1 / rms of each token's stream row
 
     // the dynamic region is aligned to 1024 bytes by hand (the swizzle atoms need it)
     const uint32_t raw = smem_u32(shared_raw);
@@ -308,6 +361,16 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
             umma_commit(smem_u32(&empty_bar[s]));     // the stage is free once these MMAs have read it
         }
         umma_commit(smem_u32(&accum_bar));            // the accumulator is complete once all MMAs are done
+    } else if (warp >= 2 && p.scale.parts != nullptr) {
+        // ---- the two warps without a role in the main loop add the sums of squares, in an order that depends on
+        // the number of parts only, and leave 1 / rms per token for the epilogue
+        pdl_wait();
+        for (int m = warp - 2; m < p.m; m += 2) {
+            float squares = 0.0f;
+            for (int i = lane; i < p.scale.n_parts; i += 32) squares += p.scale.parts[(size_t)i * p.scale.stride + m];
+            squares = warp_sum(squares);
+            if (lane == 0) row_scale[m] = rsqrtf(squares / (float)p.k + p.scale.eps);
+        }
     }
 
     // ---- epilogue: all four warps; warp w reads tensor-memory lanes 32 w .. 32 w + 31 = rows of the tile
@@ -329,6 +392,7 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
     const int row = warp * 32 + lane;                 // row of the W tile
     float* reduce = reinterpret_cast<float*>(aligned);   // [token_pad][128], reuses the stage memory
     const int n = n0 + row;
+    const bool scaled = p.scale.parts != nullptr;
     for (int c0 = 0; c0 < p.token_pad; c0 += 16) {
         float values[16];
         if (n_kb > 0 && !bad) {
@@ -340,6 +404,17 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
         if (p.split > 1) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) reduce[(c0 + i) * kBlockRows + row] = values[i];
+            continue;
+        }
+        if (scaled) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) values[i] *= c0 + i < p.m ? row_scale[c0 + i] : 0.0f;
+        }
+        if (p.stream.on) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if (c0 + i < p.m)
+                    stream_finish(p, c0 + i, row, tile, values[i], n < p.n ? p.stream.residual[(size_t)(c0 + i) * p.n + n] : 0.0f);
         } else if (p.rope.on) {
 #pragma unroll
             for (int i = 0; i < 16; ++i)
@@ -368,6 +443,12 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
         constexpr int kRowsAtOnce = 4;
         for (int m0 = (int)rank; m0 < p.m; m0 += kRowsAtOnce * p.split) {
             float parts[kRowsAtOnce][kMaxSplit];
+            float before[kRowsAtOnce];      // the stream's values, asked for together with the peers' parts
+#pragma unroll
+            for (int j = 0; j < kRowsAtOnce; ++j) {
+                const int m = m0 + j * p.split;
+                before[j] = (p.stream.on && m < p.m && n < p.n) ? p.stream.residual[(size_t)m * p.n + n] : 0.0f;
+            }
 #pragma unroll
             for (int j = 0; j < kRowsAtOnce; ++j) {
                 const int m = m0 + j * p.split;
@@ -382,7 +463,10 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
                 float total = parts[j][0];
 #pragma unroll
                 for (int peer = 1; peer < kMaxSplit; ++peer) total += parts[j][peer];      // absent peers add 0
-                if (p.rope.on) {
+                if (scaled && m < p.m) total *= row_scale[m];
+                if (p.stream.on) {
+                    if (m < p.m) stream_finish(p, m, row, tile, total, before[j]);
+                } else if (p.rope.on) {
                     if (m < p.m) rope_finish(p, m, row, tile, total, exchange);
                 } else if (p.silu_gate) {
                     if (m < p.m) silu_finish(p, m, row, tile, total, exchange);
@@ -411,9 +495,18 @@ LLM_EXPORT int llm_gemm_small_m_supports(int m, int n, int k) {
     return m >= 1 && m <= 64 && n >= 1 && k >= 8 && k % 8 == 0;
 }
 
+static RowScale row_scale_of(const float* parts, int n_parts, int stride, float eps) {
+    RowScale scale;
+    scale.parts = n_parts > 0 ? parts : nullptr;
+    scale.n_parts = n_parts;
+    scale.stride = stride;
+    scale.eps = eps;
+    return scale;
+}
+
 static int small_m_launch(const void* x, const void* w, void* out, int m, int n, int k, int ldc, int out_is_f32,
                           int requested_split, int* error_flag, const RopeEpilogue* rope, cudaStream_t stream,
-                          int silu_gate = 0) {
+                          int silu_gate, const RowScale& scale, const StreamEpilogue* stream_out = nullptr) {
     if (m == 0 || n == 0) return LLM_OK;
     if (!llm_gemm_small_m_supports(m, n, k) || !aligned16(x) || !aligned16(w)) {
         llm_set_error("gemm_small_m: takes 1..64 rows, K a multiple of 8 and 16-byte aligned operands (got m %d, n %d, k %d)", m, n, k);
@@ -435,6 +528,17 @@ static int small_m_launch(const void* x, const void* w, void* out, int m, int n,
         p.rope.on = 0;
     }
     p.silu_gate = silu_gate;
+    p.scale = scale;
+    if (scale.parts != nullptr && (scale.stride < m || m > 64)) {
+        llm_set_error("gemm_small_m: the sums of squares have room for %d tokens, the product has %d", scale.stride, m);
+        return LLM_REFUSED;
+    }
+    if (stream_out != nullptr) {
+        p.stream = *stream_out;
+    } else {
+        p.stream = StreamEpilogue{};
+        p.stream.on = 0;
+    }
     const int tiles = (n + kBlockRows - 1) / kBlockRows;
     const int total_kb = (k + kBlockK - 1) / kBlockK;
     // K is split across a cluster so that the tiles fill the machine; each rank keeps >= 4 K blocks.  The
@@ -501,9 +605,38 @@ static int small_m_launch(const void* x, const void* w, void* out, int m, int n,
     return llm_check_launch("gemm_small_m");
 }
 
+// scale_parts .. scale_eps: the RowScale of the input rows (scale_n_parts 0: none), here and in the products below.
 LLM_EXPORT int llm_gemm_small_m(const void* x, const void* w, void* out, int m, int n, int k, int ldc, int out_is_f32,
-                                int requested_split, int* error_flag, cudaStream_t stream) {
-    return small_m_launch(x, w, out, m, n, k, ldc, out_is_f32, requested_split, error_flag, nullptr, stream);
+                                int requested_split, const float* scale_parts, int scale_n_parts, int scale_stride,
+                                float scale_eps, int* error_flag, cudaStream_t stream) {
+    return small_m_launch(x, w, out, m, n, k, ldc, out_is_f32, requested_split, error_flag, nullptr, stream, 0,
+                          row_scale_of(scale_parts, scale_n_parts, scale_stride, scale_eps));
+}
+
+// How many partial sums of squares per token llm_gemm_into_stream leaves for a stream of n columns.
+LLM_EXPORT int llm_gemm_into_stream_parts(int n) { return 4 * ((n + kBlockRows - 1) / kBlockRows); }
+
+// residual[m, n] += x[m, k] W^T (32-bit stream, contiguous).  With next_weight [n] (bfloat16, or float when
+// weight_is_f32): scaled[m, n] = bfloat16(residual * next_weight) and parts[i * parts_stride + token], i <
+// llm_gemm_into_stream_parts(n), the partial sums of squares of the updated rows: the input and the RowScale of the
+// product that consumes the RMSNorm with that weight.  Without next_weight only the stream is updated.
+LLM_EXPORT int llm_gemm_into_stream(const void* x, const void* w, float* residual, int m, int n, int k, int requested_split,
+                                    const void* next_weight, int weight_is_f32, void* scaled, float* parts, int parts_stride,
+                                    int* error_flag, cudaStream_t stream) {
+    if (residual == nullptr || (next_weight != nullptr && (scaled == nullptr || parts == nullptr || parts_stride < m))) {
+        llm_set_error("gemm_into_stream: the stream, and with a norm weight its two outputs (room for %d tokens), must be given", m);
+        return LLM_REFUSED;
+    }
+    StreamEpilogue e;
+    e.on = 1;
+    e.residual = residual;
+    e.next_weight = next_weight;
+    e.weight_is_f32 = weight_is_f32;
+    e.scaled = (__nv_bfloat16*)scaled;
+    e.parts = parts;
+    e.stride = parts_stride;
+    return small_m_launch(x, w, nullptr, m, n, k, n, 1, requested_split, error_flag, nullptr, stream, 0,
+                          row_scale_of(nullptr, 0, 0, 0.0f), &e);
 }
 
 // 1 when the fused q/k/v projection takes the sizes: heads of 128 (a head is a tile of the product), up to 64 tokens
@@ -522,7 +655,8 @@ LLM_EXPORT int llm_gemm_qkv_rope(const void* x, const void* w, void* qkv, int m,
                                  const void* q_weight, const void* k_weight, int weight_is_f32, const float* inv_freq,
                                  const int* positions, const int* seq_of_token, const int* block_tables, int max_blocks,
                                  void* k_pages, void* v_pages, int n_q_heads, int n_kv_heads, int head_dim, int page_size,
-                                 int num_pages, float eps, int write_cache, int* page_error, int* error_flag,
+                                 int num_pages, float eps, int write_cache, int* page_error, const float* scale_parts,
+                                 int scale_n_parts, int scale_stride, float scale_eps, int* error_flag,
                                  cudaStream_t stream) {
     if (!llm_gemm_qkv_rope_supports(m, n_q_heads, n_kv_heads, head_dim, k)) {
         llm_set_error("gemm_qkv_rope: takes heads of 128 and 1..64 tokens (got head_dim %d, m %d, k %d)", head_dim, m, k);
@@ -552,17 +686,20 @@ LLM_EXPORT int llm_gemm_qkv_rope(const void* x, const void* w, void* qkv, int m,
     rope.eps = eps;
     rope.write_cache = write_cache;
     rope.page_error = page_error;
-    return small_m_launch(x, w, qkv, m, (n_q_heads + 2 * n_kv_heads) * head_dim, k, ldc, 0, requested_split, error_flag, &rope, stream);
+    return small_m_launch(x, w, qkv, m, (n_q_heads + 2 * n_kv_heads) * head_dim, k, ldc, 0, requested_split, error_flag, &rope, stream,
+                          0, row_scale_of(scale_parts, scale_n_parts, scale_stride, scale_eps));
 }
 
 // out[m, n / 2] = silu(gate) * up of the fused gate/up projection x W^T, W [n, k] with gate and up rows interleaved in
 // groups of 64 (rows [128 b, 128 b + 64) are gate rows of outputs [64 b, 64 b + 64), the next 64 rows their up rows);
 // n must be a multiple of 128.  bfloat16 in and out; ldc is the row pitch of `out`.
 LLM_EXPORT int llm_gemm_gate_up_silu(const void* x, const void* w, void* out, int m, int n, int k, int ldc,
-                                     int requested_split, int* error_flag, cudaStream_t stream) {
+                                     int requested_split, const float* scale_parts, int scale_n_parts, int scale_stride,
+                                     float scale_eps, int* error_flag, cudaStream_t stream) {
     if (n % kBlockRows) {
         llm_set_error("gemm_gate_up_silu: %d rows of the fused weight are no multiple of %d", n, kBlockRows);
         return LLM_REFUSED;
     }
-    return small_m_launch(x, w, out, m, n, k, ldc, 0, requested_split, error_flag, nullptr, stream, 1);
+    return small_m_launch(x, w, out, m, n, k, ldc, 0, requested_split, error_flag, nullptr, stream, 1,
+                          row_scale_of(scale_parts, scale_n_parts, scale_stride, scale_eps));
 }

@@ -8,6 +8,8 @@
 // the residual sum to the activation type first; keeping the stream in 32-bit is more exact.
 // `rows` (optional) selects the source rows: output row o reads row rows[o]; used for the final
 // norm, which runs only where logits are wanted (utils/model.py:147-157).
+// With `squares_out` the division by the root mean square is left to the consumer: out = residual * weight, and
+// squares_out[o] = sum(residual[r]^2), for a product kernel that scales its accumulators row by row.
 //
 // Two forms of the same arithmetic: a vector form (16-byte accesses, the row held in registers between
 // the two passes) for widths that are a multiple of 8 and at most 16384, and a scalar form for the rest.
@@ -23,7 +25,8 @@ constexpr int kMaxChunks = 4;    // per thread
 template <typename T, typename W>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                        const W* __restrict__ weight, T* __restrict__ out,
-                                       const int* __restrict__ rows, int width, float eps, int write_residual) {
+                                       const int* __restrict__ rows, int width, float eps, int write_residual,
+                                       float* __restrict__ squares_out) {
     pdl_trigger();   // let the next kernel start launching
     pdl_wait();      // everything before this kernel in the stream is complete and visible
     __shared__ float scratch[33];
@@ -51,7 +54,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
         }
     }
     const float total = block_sum(sum_squares, scratch);
-    const float inverse = rsqrtf(total / (float)width + eps);
+    const float inverse = squares_out ? 1.0f : rsqrtf(total / (float)width + eps);
+    if (squares_out && threadIdx.x == 0) squares_out[o] = total;
     T* dst = out + (size_t)o * width;
 #pragma unroll
     for (int i = 0; i < kMaxChunks; ++i) {
@@ -69,7 +73,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
 template <typename T, typename W>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                    const W* __restrict__ weight, T* __restrict__ out,
-                                   const int* __restrict__ rows, int width, float eps, int write_residual) {
+                                   const int* __restrict__ rows, int width, float eps, int write_residual,
+                                       float* __restrict__ squares_out) {
     pdl_trigger();   // let the next kernel start launching
     pdl_wait();      // everything before this kernel in the stream is complete and visible
     __shared__ float scratch[33];
@@ -87,7 +92,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
         sum_squares += v * v;
     }
     const float total = block_sum(sum_squares, scratch);
-    const float inverse = rsqrtf(total / (float)width + eps);
+    const float inverse = squares_out ? 1.0f : rsqrtf(total / (float)width + eps);
+    if (squares_out && threadIdx.x == 0) squares_out[o] = total;
     T* dst = out + (size_t)o * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float v = res[i];
@@ -121,7 +127,7 @@ static int norm_threads(int width) { return width >= 2048 ? 512 : (width >= 512 
 
 LLM_EXPORT int llm_add_rmsnorm(float* residual, const void* delta, const void* weight, void* out, const int* rows,
                                int n_rows, int width, float eps, int write_residual, int dtype,
-                               int weight_dtype, cudaStream_t stream) {
+                               int weight_dtype, float* squares_out, cudaStream_t stream) {
     if (n_rows == 0) return LLM_OK;
     const int chunks = width / kChunk;
     // the block size depends on the width only, so a row is summed in the same order in every call
@@ -133,13 +139,13 @@ LLM_EXPORT int llm_add_rmsnorm(float* residual, const void* delta, const void* w
         LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype,
                                   (llm_launch(add_rmsnorm_vec_kernel<T, W>, n_rows, threads, 0, stream, 
                                       residual, (const T*)delta, (const W*)weight, (T*)out, rows, width, eps,
-                                      write_residual)));
+                                      write_residual, squares_out)));
         return llm_check_launch("add_rmsnorm");
     }
     LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype,
                               (llm_launch(add_rmsnorm_kernel<T, W>, n_rows, norm_threads(width), 0, stream, 
                                   residual, (const T*)delta, (const W*)weight, (T*)out, rows, width, eps,
-                                  write_residual)));
+                                  write_residual, squares_out)));
     return llm_check_launch("add_rmsnorm");
 }
 

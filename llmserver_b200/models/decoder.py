@@ -79,8 +79,15 @@ class DecoderModel:
         for position in self.positions.values():
             position.on_embedding(residual, batch)
         delta = None
-        for index, entry in enumerate(self.spec.schedule):
-            residual, delta = self.layers[entry.layer].forward(residual, delta, batch, self.entry_caches[index])
+        schedule = self.spec.schedule
+        for index, entry in enumerate(schedule):
+            block = self.layers[entry.layer]
+            if block.passes_stream:
+                # what runs next, for a block whose last part can prepare that norm's input
+                after = self.layers[schedule[index + 1].layer].entry() if index + 1 < len(schedule) else (self.final_norm, None)
+                residual, delta = block.forward(residual, delta, batch, self.entry_caches[index], after=after)
+            else:
+                residual, delta = block.forward(residual, delta, batch, self.entry_caches[index])
         if batch.n_logits == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=residual.device)
         # final norm only where logits are wanted (utils/model.py:147-157)

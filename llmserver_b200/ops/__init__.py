@@ -13,9 +13,11 @@ import torch
 
 from .library import (KernelError, call, check, declare, dtype_code, launch_count, library, pointer,
                       require_device, stream_handle, wait_error_flag)
+from .stream import STREAM_ROWS, RowScaled, StreamSink
 
 __all__ = ["KernelError", "embedding", "add_rmsnorm", "rmsnorm", "silu_mul", "sample", "qk_norm_rope_kv_write",
-           "attention_generic", "gemm_f32", "linear", "qkv_projection", "gate_up_silu", "interleave_gate_up", "require_device", "library", "launch_count"]
+           "attention_generic", "gemm_f32", "linear", "qkv_projection", "gate_up_silu", "interleave_gate_up", "require_device", "library", "launch_count",
+           "RowScaled", "StreamSink", "STREAM_ROWS", "unscaled_rows_supported"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -34,12 +36,13 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
-                write_residual: bool = True, act_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                write_residual: bool = True, act_dtype: Optional[torch.dtype] = None, unscaled: bool = False):
     """residual += delta (in place, 32-bit), then out = rmsnorm(residual) * weight in the activation
     type ``act_dtype`` (default: weight's dtype; the weight may be float32 beside bfloat16 activations).
 
     ``rows`` (int32) selects source rows: output row o comes from row rows[o]; then the residual is
-    left untouched and ``delta`` is added on the fly."""
+    left untouched and ``delta`` is added on the fly.  ``unscaled``: the division by the root mean square is left to
+    the product that consumes the result; returns a ``RowScaled`` (residual * weight and the rows' sums of squares)."""
     check(residual, "residual", torch.float32)
     width = residual.shape[-1]
     check(weight, "norm weight", last_dim=width)
@@ -56,9 +59,11 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: t
     if out is None:
         out = torch.empty((n_rows, width), dtype=act, device=residual.device)
     check(out, "norm output", act, width)
+    squares = torch.empty((1, max(n_rows, 1)), dtype=torch.float32, device=residual.device) if unscaled else None
     call("llm_add_rmsnorm", residual.data_ptr(), pointer(delta), weight.data_ptr(), out.data_ptr(), pointer(rows),
-         n_rows, width, float(eps), int(write_residual), dtype_code(act), dtype_code(weight.dtype), stream_handle())
-    return out
+         n_rows, width, float(eps), int(write_residual), dtype_code(act), dtype_code(weight.dtype), pointer(squares),
+         stream_handle())
+    return RowScaled(out, squares, eps) if unscaled else out
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -103,10 +108,10 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int = GATE_U
                        dim=1).reshape(2 * inter, hidden).contiguous()
 
 
-def gate_up_silu(x: torch.Tensor, weight: torch.Tensor, group: int = 0) -> torch.Tensor:
+def gate_up_silu(x, weight: torch.Tensor, group: int = 0) -> torch.Tensor:
     """silu(x Wg^T) * (x Wu^T) for the fused weight ``weight`` [2 I, H] (halves when ``group`` is 0, else interleaved in
     groups): as one kernel where the product kernel can apply the gate in its epilogue (bfloat16, groups of 64, few
-    rows), else as the product followed by ``silu_mul``."""
+    rows), else as the product followed by ``silu_mul``.  ``x`` may be a ``RowScaled``."""
     if x.dtype == torch.bfloat16 and group == GATE_UP_GROUP:
         from . import gemm_bf16
         fused = gemm_bf16.gate_up_silu_fused(x, weight)
@@ -222,30 +227,40 @@ def gemm_f32(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] 
     return out
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
-           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+def linear(x, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None, sink: Optional[StreamSink] = None) -> Optional[torch.Tensor]:
     """y = x W^T for W stored [out, in] (utils/attention.py:119-124 uses nn.Linear for the same).
 
     float32: this package's FMA kernel.  bfloat16: the library matrix product (cuBLAS through
     PyTorch) where the reference's engine uses a library too, or this package's own kernels where
-    they apply (see ``gemm_bf16``)."""
-    if not x.is_cuda:
+    they apply (see ``gemm_bf16``).  ``x`` may be a ``RowScaled``.  With a ``sink`` the product is added to the sink's
+    residual stream by the product kernel itself where that kernel takes the case (``sink.added`` then says so and
+    nothing is returned); otherwise the sink is left alone and the product is returned as usual."""
+    if x.device.type != "cuda":
         raise KernelError("linear: there is no CPU path")
     if x.dtype == torch.float32:
         result = gemm_f32(x, weight, out)
         return result
     from . import gemm_bf16
+    if sink is not None and out is None and not isinstance(x, RowScaled) and gemm_bf16.linear_into_stream(x, weight, sink):
+        return None
     return gemm_bf16.linear_bf16(x, weight, out=out, out_dtype=out_dtype)
 
 
-def qkv_projection(x: torch.Tensor, weight: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+def unscaled_rows_supported(weight: torch.Tensor) -> bool:
+    """Whether products with ``weight`` take ``RowScaled`` rows."""
+    from . import gemm_bf16
+    return gemm_bf16.unscaled_rows_supported(weight)
+
+
+def qkv_projection(x, weight: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
                    inv_freq: Optional[torch.Tensor], positions: torch.Tensor, seq_of_token: torch.Tensor,
                    block_tables: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, n_q_heads: int, n_kv_heads: int,
                    head_dim: int, eps: float, write_cache: bool, error_flag: torch.Tensor, rotary_dim: Optional[int] = None,
                    interleaved: bool = False) -> torch.Tensor:
     """qkv = x W^T followed by ``qk_norm_rope_kv_write``: as one kernel where the product kernel can finish heads in its
     epilogue (bfloat16, heads of 128, up to 64 tokens, the whole head rotating in halves; from 17 tokens on only where
-    that is measured to be faster), else as two."""
+    that is measured to be faster), else as two.  ``x`` may be a ``RowScaled``."""
     whole_head = rotary_dim is None or rotary_dim == head_dim
     if x.dtype == torch.bfloat16 and whole_head and not interleaved and x.shape[0] <= 64:
         from . import gemm_bf16

@@ -16,6 +16,7 @@ from typing import Optional
 import torch
 
 from .library import KernelError, call, check_wait_errors, library, stream_handle, wait_error_flag
+from .stream import NO_SCALE, STREAM_ROWS, RowScaled, StreamSink, rows_of, scale_args_of
 
 SMALL_M = 64
 _use_small_m = os.environ.get("LLMSERVER_B200_SMALL_M_GEMM", "1") != "0"
@@ -155,11 +156,11 @@ def _time_in_step(run, device, repeats: int = 3) -> float:
     return measure(run) - _empty_round[device]
 
 
-def _small_m(x, weight, out, split: int) -> None:
+def _small_m(x, weight, out, split: int, scale: tuple = NO_SCALE) -> None:
     rows, inner = x.shape
     cols = weight.shape[0]
     call("llm_gemm_small_m", x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, cols, inner, cols,
-         int(out.dtype == torch.float32), split, error_flag(x.device).data_ptr(), stream_handle())
+         int(out.dtype == torch.float32), split, *scale, error_flag(x.device).data_ptr(), stream_handle())
 
 
 def _plan_for(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, own_kernel_only: bool = False) -> int:
@@ -223,8 +224,55 @@ def _plan_for(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, own
     return best
 
 
-def linear_bf16(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
+def unscaled_rows_supported(weight: torch.Tensor) -> bool:
+    """Whether products with ``weight`` [N, K] take ``RowScaled`` input (this package's kernel has to take the shape)."""
+    return (weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.is_contiguous()
+            and small_m_supported(STREAM_ROWS, weight.shape[0], weight.shape[1]))
+
+
+def linear_into_stream(x: torch.Tensor, weight: torch.Tensor, sink: StreamSink) -> bool:
+    """sink.residual += x W^T in the product kernel's epilogue and, when the sink names a norm weight, the input of
+    that norm (``sink.scaled``).  False, with nothing done, when the kernel does not take the case."""
+    rows, inner = x.shape
+    cols = weight.shape[0]
+    residual = sink.residual
+    if not (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.is_contiguous() and weight.is_contiguous()
+            and rows <= STREAM_ROWS and small_m_supported(rows, cols, inner) and residual.dtype == torch.float32
+            and residual.is_contiguous() and tuple(residual.shape) == (rows, cols)):
+        return False
+    norm_weight = sink.norm_weight
+    if norm_weight is not None and (norm_weight.dtype not in (torch.bfloat16, torch.float32) or norm_weight.numel() != cols
+                                    or not norm_weight.is_contiguous()):
+        return False
+    split = max(_plan_for(x, weight, torch.bfloat16, own_kernel_only=True), 0)
+    scaled = parts = None
+    if norm_weight is not None:
+        scaled = torch.empty((rows, cols), dtype=torch.bfloat16, device=x.device)
+        parts = torch.empty((library().llm_gemm_into_stream_parts(cols), STREAM_ROWS), dtype=torch.float32, device=x.device)
+    call("llm_gemm_into_stream", x.data_ptr(), weight.data_ptr(), residual.data_ptr(), rows, cols, inner, split,
+         0 if norm_weight is None else norm_weight.data_ptr(), int(norm_weight is not None and norm_weight.dtype == torch.float32),
+         0 if scaled is None else scaled.data_ptr(), 0 if parts is None else parts.data_ptr(), STREAM_ROWS,
+         error_flag(x.device).data_ptr(), stream_handle())
+    sink.added = True
+    if norm_weight is not None:
+        sink.scaled = RowScaled(scaled, parts, sink.eps)
+    return True
+
+
+def linear_bf16(x, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
                 out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    if isinstance(x, RowScaled):
+        # rows that still have to be divided by their root mean square: only this package's kernel can do that
+        rows, inner = x.shape
+        cols = weight.shape[0]
+        out_dtype = out_dtype or torch.bfloat16
+        if not (rows <= SMALL_M and unscaled_rows_supported(weight) and x.x.is_contiguous()):
+            raise KernelError(f"linear_bf16: no product kernel takes unscaled rows for {rows} rows and a weight {tuple(weight.shape)}")
+        if out is None:
+            out = torch.empty((rows, cols), dtype=out_dtype, device=x.device)
+        own_only = out_dtype != torch.float32
+        _small_m(x.x, weight, out, max(_plan_for(x.x, weight, out_dtype, own_kernel_only=own_only), 0), x.scale_args())
+        return out
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
         raise KernelError(f"linear_bf16 takes bfloat16 operands, got {x.dtype} and {weight.dtype}")
     out_dtype = out_dtype or torch.bfloat16
@@ -309,6 +357,7 @@ def qkv_rope_fused(x: torch.Tensor, weight: torch.Tensor, q_weight, k_weight, in
     norms, the rotation and the cache write (see ``ops.qk_norm_rope_kv_write`` for the arithmetic).  Returns the packed
     [N, (Hq + 2 Hkv) D] tensor whose Q heads are finished (its K and V heads are not written: they went to the pages),
     or None when the fused kernel does not take the case; the caller then runs the two kernels one after the other."""
+    scale, x = scale_args_of(x), rows_of(x)
     rows, inner = x.shape
     if not (FUSE_QKV_ROPE and _use_small_m and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
             and x.is_contiguous() and weight.is_contiguous() and k_pages.dtype == torch.bfloat16
@@ -328,7 +377,7 @@ def qkv_rope_fused(x: torch.Tensor, weight: torch.Tensor, q_weight, k_weight, in
              int(q_weight is not None and q_weight.dtype == torch.float32), 0 if inv_freq is None else inv_freq.data_ptr(),
              positions.data_ptr(), seq_of_token.data_ptr(), block_tables.data_ptr(), block_tables.shape[-1],
              k_pages.data_ptr(), v_pages.data_ptr(), n_q_heads, n_kv_heads, head_dim, k_pages.shape[2], k_pages.shape[0],
-             float(eps), int(write_cache), page_error.data_ptr(), error_flag(x.device).data_ptr(), stream_handle())
+             float(eps), int(write_cache), page_error.data_ptr(), *scale, error_flag(x.device).data_ptr(), stream_handle())
 
     if rows <= 16:
         split = _plan_for(x, weight, torch.bfloat16, own_kernel_only=True)      # few rows: always this package's kernel
@@ -353,6 +402,7 @@ def gate_up_silu_fused(x: torch.Tensor, weight: torch.Tensor) -> Optional[torch.
     """silu(gate) * up in the epilogue of the product for few rows; ``weight`` is the fused [2 I, H] matrix with gate
     and up rows interleaved in groups of 64.  None when the product kernel does not take the case (the caller then
     runs the product and the activation kernel)."""
+    scale, x = scale_args_of(x), rows_of(x)
     rows, inner = x.shape
     cols = weight.shape[0]
     if not (FUSE_GATE_UP_SILU and rows <= SMALL_M and cols % 128 == 0 and x.is_contiguous() and weight.is_contiguous()
@@ -362,7 +412,7 @@ def gate_up_silu_fused(x: torch.Tensor, weight: torch.Tensor) -> Optional[torch.
 
     def fused(split: int) -> None:
         call("llm_gemm_gate_up_silu", x.data_ptr(), weight.data_ptr(), out.data_ptr(), rows, cols, inner, cols // 2, split,
-             error_flag(x.device).data_ptr(), stream_handle())
+             *scale, error_flag(x.device).data_ptr(), stream_handle())
 
     # up to 16 rows this package's kernel, whatever a measurement of the bare products says (whole steps are faster with
     # it there, and the activation kernel goes away); with more rows whichever is measured faster: the fused kernel, or

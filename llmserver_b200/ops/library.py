@@ -17,7 +17,7 @@ _P, _I, _F, _S = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 # name -> argument types (every launcher returns an int status; the stream comes last)
 SIGNATURES = {
     "llm_embedding_gather": [_P, _P, _P, _I, _I, _I, _I, _S],
-    "llm_add_rmsnorm": [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _S],
+    "llm_add_rmsnorm": [_P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _P, _S],
     "llm_rmsnorm": [_P, _P, _P, _I, _I, _F, _I, _I, _S],
     "llm_silu_mul": [_P, _P, _I, _I, _I, _I, _S],
     "llm_sample": [_P, _P, _P, _P, _P, _I, _I, _P, _P, _S],
@@ -31,10 +31,13 @@ SIGNATURES = {
     "llm_attention_prefill_wide_supports": [_I, _I, _I, _I],
     "llm_attention_prefill_wide": [_P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _S],
     "llm_gemm_small_m_supports": [_I, _I, _I],
-    "llm_gemm_small_m": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _S],
-    "llm_gemm_gate_up_silu": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _S],
+    "llm_gemm_small_m": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _I, _F, _P, _S],
+    "llm_gemm_into_stream_parts": [_I],
+    "llm_gemm_into_stream": [_P, _P, _P, _I, _I, _I, _I, _P, _I, _P, _P, _I, _P, _S],
+    "llm_gemm_gate_up_silu": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _F, _P, _S],
     "llm_gemm_qkv_rope_supports": [_I, _I, _I, _I, _I],
-    "llm_gemm_qkv_rope": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _S],
+    "llm_gemm_qkv_rope": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P,
+                          _P, _I, _I, _F, _P, _S],
     "llm_attention_mma": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _S],
 }
 

@@ -90,11 +90,17 @@ class GQAttention(Mixer):
                              f"attention_factor is {position.attention_factor}, only 1 is supported")
         self.inv_freq, self.rotary_dim, self.interleaved = inv_freq, rotary_dim, pairing == "interleaved"
 
-    def forward(self, x, batch, cache):
+    feeds_stream = True
+
+    @property
+    def takes_unscaled(self):
+        return ops.unscaled_rows_supported(self.qkv)
+
+    def forward(self, x, batch, cache, sink=None):
         tables = batch.block_tables[cache.group]
         qkv = ops.qkv_projection(x, self.qkv, self.q_norm, self.k_norm, self.inv_freq, batch.positions, batch.seq_of_token,
                                  tables, cache.k_pages, cache.v_pages, self.heads, self.kv_heads, self.head_dim, self.eps,
                                  cache.writes, batch.error_flag, self.rotary_dim, self.interleaved)
         attended = ops.attention(qkv, batch, tables, cache.k_pages, cache.v_pages, self.heads, self.kv_heads,
                                  self.head_dim, self.scale, self.window)
-        return ops.linear(attended, self.out)
+        return ops.linear(attended, self.out, sink=sink)

@@ -58,6 +58,13 @@ class Mixer(Part):
     # batch holds and read nothing of the batch on the host.  A mixer that walks its rows in Python says False; decode
     # steps of a model that has one run eagerly.
     capturable = True
+    # Two optional abilities, with which a step of few rows runs without stand-alone residual-add + norm kernels (see
+    # ``ops.stream``).  ``takes_unscaled``: ``forward`` accepts an ``ops.RowScaled`` in place of the normalised rows.
+    # ``feeds_stream``: ``forward`` takes a keyword ``sink`` (an ``ops.StreamSink``), may add its result to the sink's
+    # stream itself (it then returns None and the sink says ``added``) and otherwise ignores it.  A part that leaves
+    # both False is called exactly as before.
+    takes_unscaled = False
+    feeds_stream = False
 
     @classmethod
     def cache_need(cls, params: dict):
@@ -72,6 +79,9 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_unscaled = False      # as for a mixer
+    feeds_stream = False
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
@@ -81,6 +91,13 @@ class Norm(Part):
                  rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """residual += delta (when delta is given), then the normalised stream in the activation type."""
         raise NotImplementedError
+
+    def sink(self, residual: torch.Tensor, consumer):
+        """An ``ops.StreamSink`` through which the part in front may add its result to ``residual`` and prepare this
+        norm's input for ``consumer`` (the part that reads the norm's output; None: nobody needs it prepared, the
+        result is only added), or None when this norm cannot work that way.  A norm that gives out sinks accepts a
+        used one as ``delta`` of ``add_norm``, and a keyword ``unscaled`` there (leave the division to the consumer)."""
+        return None
 
     def norm(self, x: torch.Tensor) -> torch.Tensor:
         """Normalises activations that are not the stream (a sub-layer's output, in blocks that do so)."""
@@ -119,6 +136,15 @@ class Block(Part):
         self.params, self.parts = params, dict(parts)
         for role, part in parts.items():
             setattr(self, role, part)
+
+    def entry(self):
+        """(norm, consumer): the norm that this block applies to the stream first and the part that reads its output,
+        for a block in front that can prepare that norm's input; None when the block does not start that way."""
+        return None
+
+    # True: ``forward`` takes a keyword ``after``, the ``entry()`` of what runs next (the next block, or the final
+    # norm with no consumer), and may return a used ``ops.StreamSink`` in place of its not yet added output.
+    passes_stream = False
 
     def forward(self, residual, delta, batch, cache):
         raise NotImplementedError

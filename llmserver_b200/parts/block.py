@@ -16,8 +16,25 @@ class PreNormBlock(Block):
 
     KNOWN_PARAMS = ("mixer_prefix", "feed_forward_prefix", "mixer_norm_prefix", "feed_forward_norm_prefix")
 
-    def forward(self, residual, delta, batch, cache):
-        normed = self.mixer_norm.add_norm(residual, delta)
-        mixed = self.mixer.forward(normed, batch, cache)
-        normed = self.feed_forward_norm.add_norm(residual, mixed)
-        return residual, self.feed_forward.forward(normed)
+    passes_stream = True
+
+    def entry(self):
+        return self.mixer_norm, self.mixer
+
+    def forward(self, residual, delta, batch, cache, after=None):
+        # With few rows, parts that can do so add their results to the stream themselves and prepare the next norm's
+        # input (``sink``), and take a norm's output before its division (``unscaled``); see ``ops.stream``.  Parts
+        # and norms that cannot are called as ever.
+        normed = _add_norm(self.mixer_norm, residual, delta, self.mixer)
+        sink = self.feed_forward_norm.sink(residual, self.feed_forward) if self.mixer.feeds_stream else None
+        mixed = self.mixer.forward(normed, batch, cache, sink=sink) if sink is not None else self.mixer.forward(normed, batch, cache)
+        normed = _add_norm(self.feed_forward_norm, residual, sink if sink is not None and sink.added else mixed, self.feed_forward)
+        sink = after[0].sink(residual, after[1]) if after is not None and self.feed_forward.feeds_stream else None
+        out = self.feed_forward.forward(normed, sink=sink) if sink is not None else self.feed_forward.forward(normed)
+        return residual, (sink if sink is not None and sink.added else out)
+
+
+def _add_norm(norm, residual, delta, consumer):
+    if getattr(consumer, "takes_unscaled", False) and norm.sink(residual, consumer) is not None:
+        return norm.add_norm(residual, delta, unscaled=True)
+    return norm.add_norm(residual, delta)

@@ -42,5 +42,11 @@ class SwiGLU(FeedForward):
         self.gate_up = ops.interleave_gate_up(gate, up) if self.group else torch.cat([gate, up], dim=0).contiguous()
         self.down = weights["down_proj.weight"].contiguous()
 
-    def forward(self, x):
-        return ops.linear(ops.gate_up_silu(x, self.gate_up, self.group), self.down)
+    feeds_stream = True
+
+    @property
+    def takes_unscaled(self):
+        return ops.unscaled_rows_supported(self.gate_up)
+
+    def forward(self, x, sink=None):
+        return ops.linear(ops.gate_up_silu(x, self.gate_up, self.group), self.down, sink=sink)

@@ -1,6 +1,8 @@
 """RMSNorm over the residual stream."""
 from __future__ import annotations
 
+import torch
+
 from .. import ops
 from ..weights.declare import NORM, WeightDecl
 from .base import Norm
@@ -24,8 +26,27 @@ class RMSNorm(Norm):
         self.weight = weights["weight"].contiguous()
         self.eps = float(params["eps"])
 
-    def add_norm(self, residual, delta, rows=None):
-        return ops.add_rmsnorm(residual, delta, self.weight, self.eps, rows=rows, act_dtype=self.runtime.dtype)
+    def add_norm(self, residual, delta, rows=None, unscaled=False):
+        if isinstance(delta, ops.StreamSink):
+            # the part in front added its result to the stream itself and, if asked, prepared this norm's input
+            if delta.owner is not self or not delta.added:
+                raise RuntimeError("a stream sink reached a norm that did not make it, or was never used")
+            if delta.scaled is not None and rows is None:
+                return delta.scaled
+            delta = None
+        unscaled = unscaled and rows is None and self._few_rows(residual)
+        return ops.add_rmsnorm(residual, delta, self.weight, self.eps, rows=rows, act_dtype=self.runtime.dtype,
+                               unscaled=unscaled)
+
+    def _few_rows(self, residual) -> bool:
+        return self.runtime.dtype == torch.bfloat16 and residual.shape[0] <= ops.STREAM_ROWS
+
+    def sink(self, residual, consumer):
+        if not self._few_rows(residual) or (consumer is not None and not getattr(consumer, "takes_unscaled", False)):
+            return None
+        if consumer is None:
+            return ops.StreamSink(residual, owner=self)
+        return ops.StreamSink(residual, self.weight, self.eps, owner=self)
 
     def norm(self, x):
         return ops.rmsnorm(x, self.weight, self.eps)

@@ -158,7 +158,7 @@ def test_gemm_small_m_tcgen05(shape):
     for out_dtype, split in ((torch.float32, 0), (torch.bfloat16, 0), (torch.float32, 3), (torch.bfloat16, 8)):
         out = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEVICE)
         call("llm_gemm_small_m", x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, n, int(out_dtype == torch.float32),
-             split, gemm_bf16.error_flag(DEVICE).data_ptr(), stream_handle())
+             split, *gemm_bf16.NO_SCALE, gemm_bf16.error_flag(DEVICE).data_ptr(), stream_handle())
         torch.cuda.synchronize()
         gemm_bf16.check_errors()
         close(out, want, out_dtype, f"small-M product {shape} -> {out_dtype}", factor=4.0 if out_dtype == torch.float32 else 1.0)
@@ -649,3 +649,104 @@ def test_the_microbenchmarks_run(capsys):
         assert microbench.main(arguments) == 0
         report = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
         assert report["workload"] == arguments[0] and report.get("us", report.get("tcgen05_us", 0)) > 0
+
+
+@pytest.mark.parametrize("rows,cols,inner,split,weight_dtype,with_norm", [
+    (1, 4096, 12288, 0, torch.bfloat16, True), (8, 4096, 4096, 4, torch.bfloat16, True), (16, 200, 136, 1, torch.float32, True),
+    (5, 1000, 512, 2, torch.bfloat16, True), (3, 328, 264, 0, torch.bfloat16, False)])
+def test_product_added_to_the_stream_in_its_epilogue(rows, cols, inner, split, weight_dtype, with_norm):
+    """residual += x W^T inside the product kernel, with the next norm's input prepared: the stream times the norm's
+    weight and, in parts, the rows' sums of squares."""
+    from llmserver_b200 import ops
+    from llmserver_b200.ops import gemm_bf16
+    x, w = rand((rows, inner), torch.bfloat16, 31), rand((cols, inner), torch.bfloat16, 32, 0.05)
+    residual = rand((rows, cols), torch.float32, 33)
+    norm_weight = (rand((cols,), weight_dtype, 34) + 1) if with_norm else None
+    want = residual.double() + x.double() @ w.double().T
+    if split:
+        gemm_bf16._choice[(gemm_bf16._row_bucket(rows), cols, inner, gemm_bf16.OWN_KERNEL)] = split
+    sink = ops.StreamSink(residual, norm_weight, 1e-5)
+    assert ops.linear(x, w, sink=sink) is None and sink.added
+    torch.cuda.synchronize()
+    gemm_bf16.check_errors()
+    close(residual, want, torch.float32, "stream after the product", factor=8.0)      # 32-bit sums of bfloat16 products
+    if not with_norm:
+        assert sink.scaled is None
+        return
+    scaled = sink.scaled
+    assert scaled.x.dtype == torch.bfloat16 and scaled.eps == 1e-5
+    close(scaled.x, residual.double() * norm_weight.double(), torch.bfloat16, "stream times the norm's weight")
+    squares = scaled.parts.double().sum(0)[:rows]
+    close(squares, (residual.double() ** 2).sum(1), torch.float32, "sums of squares", factor=4.0)
+
+
+@pytest.mark.parametrize("rows,width,cols", [(1, 4096, 6144), (8, 4096, 1000), (16, 264, 328), (5, 5120, 512)])
+def test_products_divide_unscaled_rows_by_their_root_mean_square(rows, width, cols):
+    """A product given the stream times the norm's weight and the sums of squares equals the product of the
+    normalised rows: from the stand-alone norm kernel and from a product's stream epilogue, in one part or many."""
+    from llmserver_b200 import ops
+    from llmserver_b200.ops import gemm_bf16
+    eps = 1e-6
+    residual = rand((rows, width), torch.float32, 41, 3.0)
+    norm_weight = rand((width,), torch.bfloat16, 42) + 1
+    w = rand((cols, width), torch.bfloat16, 43, 0.05)
+    normed = plain_model.rms_norm(residual.double(), norm_weight.double(), eps)
+    want = normed @ w.double().T
+    unscaled = ops.add_rmsnorm(residual.clone(), None, norm_weight, eps, act_dtype=torch.bfloat16, unscaled=True)
+    assert isinstance(unscaled, ops.RowScaled) and unscaled.parts.shape[0] == 1
+    for out_dtype in (torch.bfloat16, torch.float32):
+        got = ops.linear(unscaled, w, out_dtype=out_dtype)
+        torch.cuda.synchronize()
+        gemm_bf16.check_errors()
+        close(got, want, torch.bfloat16, f"product of unscaled rows -> {out_dtype}")
+    # the same rows prepared by a product's epilogue (many parts): stream = 0 + previous product
+    previous_x, previous_w = rand((rows, 136), torch.bfloat16, 44), rand((width, 136), torch.bfloat16, 45, 0.3)
+    stream = torch.zeros((rows, width), dtype=torch.float32, device=DEVICE)
+    sink = ops.StreamSink(stream, norm_weight, eps)
+    assert ops.linear(previous_x, previous_w, sink=sink) is None
+    assert sink.scaled.parts.shape[0] == 4 * -(-width // 128)
+    got = ops.linear(sink.scaled, w)
+    torch.cuda.synchronize()
+    gemm_bf16.check_errors()
+    want = plain_model.rms_norm(stream.double(), norm_weight.double(), eps) @ w.double().T
+    close(got, want, torch.bfloat16, "product of rows prepared by a product")
+
+
+def test_gate_up_and_qkv_products_take_unscaled_rows():
+    from llmserver_b200 import ops
+    from llmserver_b200.ops import gemm_bf16
+    rows, hidden, inter, eps = 6, 1024, 640, 1e-6
+    residual = rand((rows, hidden), torch.float32, 51, 2.0)
+    norm_weight = rand((hidden,), torch.bfloat16, 52) + 1
+    gate, up = rand((inter, hidden), torch.bfloat16, 53, 0.05), rand((inter, hidden), torch.bfloat16, 54, 0.05)
+    normed = ops.add_rmsnorm(residual.clone(), None, norm_weight, eps, act_dtype=torch.bfloat16)
+    unscaled = ops.add_rmsnorm(residual.clone(), None, norm_weight, eps, act_dtype=torch.bfloat16, unscaled=True)
+    fused_weight = ops.interleave_gate_up(gate, up)
+    before = ops.launch_count()
+    got = ops.gate_up_silu(unscaled, fused_weight, ops.GATE_UP_GROUP)
+    assert ops.launch_count() - before == 1 or gemm_bf16.tunings() > 0
+    want = ops.gate_up_silu(normed, fused_weight, ops.GATE_UP_GROUP)
+    torch.cuda.synchronize()
+    gemm_bf16.check_errors()
+    close(got, want.double(), torch.bfloat16, "gate/up product of unscaled rows")
+    # q/k/v projection with the rotation in its epilogue
+    heads, kv_heads, dim, page_size = 4, 2, 128, 16
+    qkv_weight = rand(((heads + 2 * kv_heads) * dim, hidden), torch.bfloat16, 55, 0.05)
+    q_norm, k_norm = rand((dim,), torch.bfloat16, 56) + 1, rand((dim,), torch.bfloat16, 57) + 1
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))).to(DEVICE)
+    positions = torch.arange(3, 3 + rows, dtype=torch.int32, device=DEVICE)
+    seq_of_token = torch.zeros(rows, dtype=torch.int32, device=DEVICE)
+    tables = torch.tensor([[2, 1, 0, 3]], dtype=torch.int32, device=DEVICE)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEVICE)
+    results = []
+    for x in (unscaled, normed):
+        k_pages = torch.zeros((4, kv_heads, page_size, dim), dtype=torch.bfloat16, device=DEVICE)
+        v_pages = torch.zeros_like(k_pages)
+        qkv = ops.qkv_projection(x, qkv_weight, q_norm, k_norm, inv_freq, positions, seq_of_token, tables, k_pages, v_pages,
+                                 heads, kv_heads, dim, eps, True, flag)
+        results.append((qkv[:, :heads * dim].clone(), k_pages, v_pages))
+    torch.cuda.synchronize()
+    gemm_bf16.check_errors()
+    assert flag.item() == 0
+    for got, want, what in zip(results[0], results[1], ("q", "k pages", "v pages")):
+        close(got, want.double(), torch.bfloat16, f"q/k/v projection of unscaled rows: {what}", factor=2.0)
