@@ -739,12 +739,11 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
         float total = row_sum[h];
         total += __shfl_xor_sync(0xffffffffu, total, 1);
         total += __shfl_xor_sync(0xffffffffu, total, 2);
+        if (g + 8 * h >= group) continue;       // rows beyond the group hold nothing and are not read below
         float* row = merge + ((size_t)warp * 16 + g + 8 * h) * (D + 2);
 #pragma unroll
-        for (int n = 0; n < D / 8; ++n) {
-            row[n * 8 + 2 * t] = o_acc[n][2 * h];
-            row[n * 8 + 2 * t + 1] = o_acc[n][2 * h + 1];
-        }
+        for (int n = 0; n < D / 8; ++n)
+            *reinterpret_cast<float2*>(row + n * 8 + 2 * t) = make_float2(o_acc[n][2 * h], o_acc[n][2 * h + 1]);
         if (t == 0) {
             row[D] = row_max[h];
             row[D + 1] = total;

@@ -112,9 +112,20 @@ _empty_round = {}
 # early), from 32 rows on with the library's.  So a candidate of the other kind has to win by this much.
 _CLOSE_FEW_ROWS = 0.10
 _CLOSE_MANY_ROWS = 0.05
+# Among the splits of this package's kernel, the ones within this much of the fastest count as equal, and the largest
+# of them is taken: measured one product at a time, 6 and 8 parts of the 8B shape's q/k/v and output projections lie
+# within 1 to 3.5 % of each other and the choice went either way from process to process, while whole steps are 1 to
+# 2 % faster with 8 (more blocks keep more bytes in flight where one kernel hands over to the next).
+_CLOSE_SPLITS = 0.04
 
 
-def _time_in_step(run, device, repeats: int = 3) -> float:
+def _fastest_split(timed: list) -> int:
+    """``timed``: (split, milliseconds) of this package's kernel; the largest split among the (nearly) fastest."""
+    fastest = min(elapsed for _, elapsed in timed)
+    return max(split for split, elapsed in timed if elapsed <= fastest * (1.0 + _CLOSE_SPLITS))
+
+
+def _time_in_step(run, device, repeats: int = 10) -> float:
     """Time of ``run`` as a model step sees it: replayed from a CUDA graph between two small kernels of this package
     (so that a product which starts its weight stream while its predecessor still runs, and lets its successor
     launch early, gets the credit), with the weights coming from HBM (a buffer larger than L2 is overwritten before
@@ -189,14 +200,13 @@ def _plan_for(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, own
         # 32-bit results always come from this package's kernel, straight from its accumulators; only the split is
         # measured (the library's product would have to be rounded to bfloat16 on the way)
         out = torch.empty((rows, cols), dtype=out_dtype, device=x.device)
-        best, best_time = 1, float("inf")
+        timed = []
         tiles, k_blocks = -(-cols // 128), -(-inner // 128)
         for split in SPLITS:
             if split > 1 and (tiles * split > 600 or k_blocks // split < 2):
                 continue
-            elapsed = _time_in_step(lambda: _small_m(x, weight, out, split), x.device)
-            if elapsed < best_time:
-                best_time, best = elapsed, split
+            timed.append((split, _time_in_step(lambda: _small_m(x, weight, out, split), x.device)))
+        best = _fastest_split(timed)
         _choice[key] = best
         _tunings += 1
         if PLAN_FILE:
@@ -209,14 +219,13 @@ def _plan_for(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, own
 
     favour_library = key[0] > 16
     best_time = _time_in_step(library_product, x.device) * ((1.0 - _CLOSE_MANY_ROWS) if favour_library else (1.0 + _CLOSE_FEW_ROWS))
-    best = 0
+    timed = []
     tiles, k_blocks = -(-cols // 128), -(-inner // 128)
     for split in SPLITS:
         if split > 1 and (tiles * split > 600 or k_blocks // split < 2):
             continue
-        elapsed = _time_in_step(lambda: _small_m(x, weight, out, split), x.device)
-        if elapsed < best_time:
-            best_time, best = elapsed, split
+        timed.append((split, _time_in_step(lambda: _small_m(x, weight, out, split), x.device)))
+    best = _fastest_split(timed) if min(elapsed for _, elapsed in timed) < best_time else 0
     _choice[key] = best
     _tunings += 1
     if PLAN_FILE:
@@ -332,14 +341,14 @@ def _plan_fused(kind: str, rows: int, cols: int, inner: int, fused, apart, devic
             return _choice[key]
     if torch.cuda.is_current_stream_capturing():
         return 0
-    best, best_time = 0, _time_in_step(apart, device)
+    apart_time = _time_in_step(apart, device)
+    timed = []
     tiles, k_blocks = -(-cols // 128), -(-inner // 128)
     for split in SPLITS:
         if split > 1 and (tiles * split > 600 or k_blocks // split < 2):
             continue
-        elapsed = _time_in_step(lambda: fused(split), device)
-        if elapsed < best_time:
-            best_time, best = elapsed, split
+        timed.append((split, _time_in_step(lambda: fused(split), device)))
+    best = _fastest_split(timed) if min(elapsed for _, elapsed in timed) < apart_time else 0
     _choice[key] = best
     _tunings += 1
     if PLAN_FILE:
