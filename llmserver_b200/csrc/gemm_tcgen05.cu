@@ -254,6 +254,10 @@ __device__ __forceinline__ void stream_finish(const GemmParams& p, int m, int ro
 __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x,
                                                                 const GemmParams p) {
+    // Static shared memory has to stay within 1 KiB.  Up to 16 tokens a block takes 72 KiB of stages + 1 KiB to align
+    // them + this + 1 KiB that the system reserves = 75 KiB, and three blocks share an SM (225 of 227 KiB): two of this
+    // kernel and one of the next, whose weights are then on their way while this kernel still runs.  With 2 KiB more
+    // only two fit: a decode step of the 8B shape then took 4.23 ms instead of 3.67.
     extern __shared__ __align__(1024) unsigned char shared_raw[];
     __shared__ __align__(8) uint64_t full_bar[kMaxStages];
     __shared__ __align__(8) uint64_t empty_bar[kMaxStages];

@@ -750,3 +750,4 @@ def test_gate_up_and_qkv_products_take_unscaled_rows():
     assert flag.item() == 0
     for got, want, what in zip(results[0], results[1], ("q", "k pages", "v pages")):
         close(got, want.double(), torch.bfloat16, f"q/k/v projection of unscaled rows: {what}", factor=2.0)
+
