@@ -235,7 +235,7 @@ def _plan_for(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, own
 
 def unscaled_rows_supported(weight: torch.Tensor) -> bool:
     """Whether products with ``weight`` [N, K] take ``RowScaled`` input (this package's kernel has to take the shape)."""
-    return (weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.is_contiguous()
+    return (STREAM_ROWS > 0 and weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.is_contiguous()
             and small_m_supported(STREAM_ROWS, weight.shape[0], weight.shape[1]))
 
 
@@ -257,10 +257,10 @@ def linear_into_stream(x: torch.Tensor, weight: torch.Tensor, sink: StreamSink) 
     scaled = parts = None
     if norm_weight is not None:
         scaled = torch.empty((rows, cols), dtype=torch.bfloat16, device=x.device)
-        parts = torch.empty((library().llm_gemm_into_stream_parts(cols), STREAM_ROWS), dtype=torch.float32, device=x.device)
+        parts = torch.empty((library().llm_gemm_into_stream_parts(cols), max(STREAM_ROWS, rows)), dtype=torch.float32, device=x.device)
     call("llm_gemm_into_stream", x.data_ptr(), weight.data_ptr(), residual.data_ptr(), rows, cols, inner, split,
          0 if norm_weight is None else norm_weight.data_ptr(), int(norm_weight is not None and norm_weight.dtype == torch.float32),
-         0 if scaled is None else scaled.data_ptr(), 0 if parts is None else parts.data_ptr(), STREAM_ROWS,
+         0 if scaled is None else scaled.data_ptr(), 0 if parts is None else parts.data_ptr(), 0 if parts is None else parts.shape[1],
          error_flag(x.device).data_ptr(), stream_handle())
     sink.added = True
     if norm_weight is not None:

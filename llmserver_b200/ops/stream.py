@@ -8,11 +8,14 @@ only the place where bfloat16 rounding happens moves (before the division instea
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
 
-STREAM_ROWS = 16        # up to this many rows a step runs this way (the rows this package's product kernel is used for)
+# up to this many rows a step runs this way (the rows this package's product kernel is used for);
+# LLMSERVER_B200_STREAM_EPILOGUES=0 switches it off (the stand-alone add + norm kernel then runs at every row count)
+STREAM_ROWS = 16 if os.environ.get("LLMSERVER_B200_STREAM_EPILOGUES", "1") != "0" else 0
 NO_SCALE = (0, 0, 0, 0.0)
 
 

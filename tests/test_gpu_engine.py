@@ -387,3 +387,46 @@ def test_two_processes_with_the_same_plan_file_give_the_same_bfloat16_logits(tin
     assert os.path.isfile(plan) and results[0][1] > 0, "the first process was meant to measure and write the plan"
     assert results[1][1] == 0 and results[2][1] == 0, "a process that reads the plan measured again"
     assert results[1][0] == results[2][0] == results[0][0], "the same plan gave other logits"
+
+
+@pytest.mark.parametrize("name", ["a", "c", "e"])
+def test_few_rows_run_without_norm_kernels_and_agree_with_the_stand_alone_norms(tiny_folders, monkeypatch, name):
+    """Up to 16 rows in bfloat16 the residual add and the norms run inside the products (two launches fewer per layer
+    and per sub-layer boundary); the same step with the stand-alone kernels gives the same logits up to bfloat16
+    rounding, and both match the plain implementation."""
+    from helpers import assert_close, plain_logits, tokens_for
+    from llmserver_b200 import ops
+    from llmserver_b200.cache import CacheManager
+    from llmserver_b200.engine.step import StepFunction
+    from llmserver_b200.models import load_model
+    folder = tiny_folders[name]
+    model = load_model(folder, "bfloat16", "cuda:0")
+    cache = CacheManager(model.cache_needs(), 8, 24, num_slots=2, prefix_sharing=False)
+    cache.materialize(model.runtime.device, model.runtime.dtype)
+    step = StepFunction(model, cache)
+    tokens = tokens_for(model.spec.vocab_size, 13, 77)
+    results, norm_calls = {}, {}
+    real_add_rmsnorm = ops.add_rmsnorm
+    calls = []
+
+    def counted(*args, **kwargs):
+        calls.append(1)
+        return real_add_rmsnorm(*args, **kwargs)
+
+    monkeypatch.setattr(ops, "add_rmsnorm", counted)
+    for rows in (ops.STREAM_ROWS, 0):
+        monkeypatch.setattr(ops, "STREAM_ROWS", rows)
+        step.admit("r")
+        step.run([("r", tokens[:9], [8])])
+        del calls[:]
+        logits = step.run([("r", tokens[9:], [0, 1, 2, 3])])
+        norm_calls[rows] = len(calls)
+        results[rows] = logits.float().cpu().numpy()
+        step.release("r")
+    layers = len(model.spec.schedule)
+    # stand-alone: two per layer and the final norm; inside the products: the first layer's input and the final norm
+    assert norm_calls == {16: 2, 0: 2 * layers + 1}, norm_calls
+    want = plain_logits(folder, tokens)[9:]
+    assert_close(results[16], want, "bfloat16", "norms inside the products")
+    assert_close(results[0], want, "bfloat16", "stand-alone norms")
+    assert_close(results[16], results[0], "bfloat16", "the two against each other")
