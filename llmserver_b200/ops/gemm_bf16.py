@@ -116,7 +116,7 @@ _CLOSE_MANY_ROWS = 0.05
 # of them is taken: measured one product at a time, 6 and 8 parts of the 8B shape's q/k/v and output projections lie
 # within 1 to 3.5 % of each other and the choice went either way from process to process, while whole steps are 1 to
 # 2 % faster with 8 (more blocks keep more bytes in flight where one kernel hands over to the next).
-_CLOSE_SPLITS = 0.04
+_CLOSE_SPLITS = float(os.environ.get("LLMSERVER_B200_GEMM_CLOSE_SPLITS", "0.04"))
 
 
 def _fastest_split(timed: list) -> int:
