@@ -2,6 +2,8 @@
 positions and a sliding window."""
 from __future__ import annotations
 
+import functools
+
 import torch
 
 from .. import ops
@@ -92,7 +94,7 @@ class GQAttention(Mixer):
 
     feeds_stream = True
 
-    @property
+    @functools.cached_property
     def takes_unscaled(self):
         return ops.unscaled_rows_supported(self.qkv)
 

@@ -1,6 +1,8 @@
 """SwiGLU feed-forward."""
 from __future__ import annotations
 
+import functools
+
 import torch
 
 from .. import ops
@@ -44,7 +46,7 @@ class SwiGLU(FeedForward):
 
     feeds_stream = True
 
-    @property
+    @functools.cached_property
     def takes_unscaled(self):
         return ops.unscaled_rows_supported(self.gate_up)
 
