@@ -792,7 +792,7 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
         // kernel below, reading the other ranks' shared memory.
         cluster_arrive_wait();
         const uint32_t mine_address = smem_address(mine);
-        constexpr int kMaxRanks = 8;      // the portable cluster size: the launcher merges more splits by the merge kernel
+        constexpr int kMaxRanks = 16;     // the largest cluster the launcher forms: it merges more splits by the merge kernel
         for (int index = split * kThreads + threadIdx.x; index < group * D; index += n_splits * kThreads) {
             const int r = index / D, d = index % D;
             // all ranks' values are asked for before the first is used: a load from another block's shared memory
@@ -895,6 +895,17 @@ int launch_decode_tma(const AttnParams& p, cudaStream_t stream) {
         return llm_check_launch("attention_decode_tma");
     }
     // the splits of a (sequence, kv head) pair as one cluster along x
+    if (p.max_splits > 8) {
+        static bool allowed = false;
+        if (!allowed) {
+            cudaError_t status = cudaFuncSetAttribute(attention_decode_tma_kernel<D>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            if (status != cudaSuccess) {
+                llm_set_error("attention_decode_tma: clusters of %d are not allowed: %s", p.max_splits, cudaGetErrorString(status));
+                return (int)status;
+            }
+            allowed = true;
+        }
+    }
     cudaLaunchConfig_t config = {};
     config.gridDim = grid;
     config.blockDim = dim3(kDecodeThreads, 1, 1);
@@ -927,9 +938,9 @@ int launch_decode(const AttnParams& p, cudaStream_t stream) {
     const bool whole_pages = p.page_size >= 8 && p.page_size <= kTileKeys && kTileKeys % p.page_size == 0 && p.page_size % 8 == 0;
     const bool by_tma = whole_pages && aligned16(p.k_pages) && aligned16(p.v_pages);
     AttnParams q = p;
-    // up to 8 splits (the portable cluster size) merge inside the kernel; more, or the cp.async kernel, go through the
+    // up to 8 splits (the portable cluster size) or exactly 16 (allowed on request) merge inside the kernel; others, or the cp.async kernel, go through the
     // scratch buffers and the merge kernel
-    q.cluster_merge = by_tma && p.cluster_merge && p.max_splits > 1 && p.max_splits <= 8;
+    q.cluster_merge = by_tma && p.cluster_merge && p.max_splits > 1 && (p.max_splits <= 8 || p.max_splits == 16);
     if (p.max_splits > 1 && !q.cluster_merge && (p.partial_out == nullptr || p.partial_ml == nullptr)) {
         llm_set_error("attention_decode: %d splits need the scratch buffers for partial results", p.max_splits);
         return LLM_REFUSED;

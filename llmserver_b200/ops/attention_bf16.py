@@ -17,6 +17,10 @@ DECODE_BLOCKS_PER_SM = 2    # blocks of the decode kernel an SM holds at a time 
 # through scratch memory and a merge kernel (as do all, with LLMSERVER_B200_DECODE_MERGE=kernel).
 CLUSTER_MERGE = os.environ.get("LLMSERVER_B200_DECODE_MERGE", "cluster") != "kernel"
 MAX_CLUSTER_SPLITS = 8
+# With so few (sequence, kv head) pairs that 16 blocks each still leave every block an SM of its own (batch 1 of the
+# 8B shape), clusters of 16 (beyond the portable size, which the hardware allows on request) get each block's keys in
+# flight at once: 3.21 against 3.25 ms per batch-1 step.  With more pairs they are slower (batch 2: 3.49 against 3.30).
+WIDE_CLUSTER_SPLITS = 16
 
 
 # "tcgen05": the 256-row kernel for long portions and the 128-row kernel otherwise; "tcgen05-128" / "tcgen05-256":
@@ -90,7 +94,9 @@ def plan(batch, group: int, n_kv_heads: int, device=None):
         pairs = singles * n_kv_heads
         splits = max(1, min(wave_blocks // pairs, -(-longest // MIN_SPLIT)))
         if CLUSTER_MERGE:
-            splits = min(splits, MAX_CLUSTER_SPLITS)
+            lone_blocks = pairs * WIDE_CLUSTER_SPLITS <= wave_blocks // DECODE_BLOCKS_PER_SM
+            # a cluster has up to 8 blocks, or exactly 16
+            splits = WIDE_CLUSTER_SPLITS if lone_blocks and splits > 12 else min(splits, MAX_CLUSTER_SPLITS)
         if pairs > wave_blocks:
             # More than a wave of whole contexts: when the last wave would leave most SMs idle (40 sequences x 8 kv
             # heads = 1.08 waves take as long as 2), the contexts are split after all.  Measured on the 8B head shape at

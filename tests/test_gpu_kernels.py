@@ -751,3 +751,33 @@ def test_gate_up_and_qkv_products_take_unscaled_rows():
     for got, want, what in zip(results[0], results[1], ("q", "k pages", "v pages")):
         close(got, want.double(), torch.bfloat16, f"q/k/v projection of unscaled rows: {what}", factor=2.0)
 
+
+@pytest.mark.parametrize("contexts,heads,kv_heads,splits", [([3000], 8, 2, 16), ([2900, 1300], 12, 4, 16), ([2000], 8, 2, 8), ([3000] * 5, 8, 2, 8)])
+def test_decode_attention_in_clusters_of_sixteen(contexts, heads, kv_heads, splits):
+    """With so few (sequence, kv head) pairs that sixteen blocks each still have an SM of their own, long contexts are
+    split sixteen ways and merged inside a cluster of sixteen blocks; with more pairs or shorter contexts up to eight."""
+    from llmserver_b200.ops import attention_bf16
+    dim, page_size, dtype = 128, 16, torch.bfloat16
+    q_lens = [1] * len(contexts)
+    scale = dim ** -0.5
+    dense_k = [rand((c, kv_heads, dim), dtype, 220 + i).cpu() for i, c in enumerate(contexts)]
+    dense_v = [rand((c, kv_heads, dim), dtype, 230 + i).cpu() for i, c in enumerate(contexts)]
+    # one far key per sequence that a lost split would lose: it takes most of the weight of head 0
+    queries = [rand((1, heads, dim), dtype, 240 + i).cpu() for i in range(len(contexts))]
+    for i, c in enumerate(contexts):
+        far = (c * (i + 3)) // 9
+        dense_k[i][far, 0] = queries[i][0, 0] * 3.0
+    k_pages, v_pages, tables = paged(dense_k, dense_v, page_size, 5, dtype)
+    q_stride = (heads + 2 * kv_heads) * dim
+    packed = torch.zeros((len(contexts), q_stride), dtype=dtype)
+    packed[:, :heads * dim] = torch.cat(queries).reshape(-1, heads * dim)
+    batch = FakeBatch(contexts, q_lens)
+    planned = attention_bf16.plan(batch, heads // kv_heads, kv_heads, torch.device(DEVICE))
+    assert planned[4] == splits, planned
+    out = attention_bf16.try_attention(packed.to(DEVICE), q_stride, batch, tables, k_pages, v_pages, heads, kv_heads, dim, scale, 0)
+    torch.cuda.synchronize()
+    from llmserver_b200.ops import gemm_bf16
+    gemm_bf16.check_errors()
+    want = torch.cat([plain_attention_rows(q.double(), k.double(), v.double(), scale, None, c - 1)
+                      for q, k, v, c in zip(queries, dense_k, dense_v, contexts)])
+    close(out, want, dtype, f"decode attention split {splits} ways")
