@@ -10,6 +10,11 @@
 // split across a thread-block cluster; the partial tiles are added through distributed shared memory in
 // a fixed order (rank 0, 1, ...), so results do not depend on timing.
 //
+// The epilogue moves the tile through shared memory as [token][128 rows] and hands whole token rows to warps: a
+// token's 128 elements are four per lane, so per-head and per-row reductions are warp reductions, rotation partners
+// and gate/up pairs a shuffle away, stores 8 or 16 bytes per lane, and the four warps work on different tokens
+// without a block barrier (per-token block barriers cost 9 to 14 us of a q/k/v product at 32 to 64 tokens).
+//
 // One elected thread issues the TMA copies, one issues the MMAs; mbarriers carry "stage full" (TMA
 // transaction bytes), "stage free" and "accumulator ready" (tcgen05.commit).  The thread that initialises the
 // barriers requests the weight tiles of the first ring of stages at once, before the block's first barrier and
@@ -80,7 +85,7 @@ struct RowScale {
 
 // The product is added to the residual stream [m, n] (32-bit, row pitch n) where it lies.  With next_weight, the
 // updated stream times next_weight [n] is written to `scaled` (bfloat16, row pitch n) and the sums of squares of
-// the updated stream to parts[(4 * tile + warp) * stride + token], for the RowScale of the next product.
+// the updated stream over each tile's 128 columns to parts[tile * stride + token], for the RowScale of the next product.
 struct StreamEpilogue {
     int on;
     float* residual;
@@ -105,6 +110,8 @@ struct GemmParams {
                         // silu(gate) * up into an output of n / 2 columns
     RowScale scale;
     StreamEpilogue stream;
+    int vector_out;     // the output (and the cache pages of the q/k/v epilogue) take 8- and 16-byte stores of four results
+    int vector_stream;  // so do the stream and the next norm's input
 };
 
 using tma::mbar_expect_tx;
@@ -163,91 +170,149 @@ __device__ __forceinline__ uint32_t cluster_rank() {
 __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float load_peer(uint32_t local_address, uint32_t rank) {
+// ---- The epilogues.  A finished token row of a tile is handled by ONE WARP: lane i holds the four elements
+// 4 i .. 4 i + 3 of the tile's 128, so a head's sum of squares or a stream row's is one warp reduction, the partner of
+// a rotation (64 elements further) and the up value of a gate sit in lane i ^ 16, and every store is 8 or 16 bytes per
+// lane and 256 or 512 contiguous bytes per warp.  The four warps of a block take different tokens at the same time
+// and never meet at a block barrier; what a token needs beside the sums (its position, its page, the stream's values)
+// is asked for together with the sums' parts.
+
+__device__ __forceinline__ float4 load_peer4(uint32_t local_address, uint32_t rank) {
     uint32_t remote;
-    float value;
+    float4 value;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote) : "memory");
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(value.x), "=f"(value.y), "=f"(value.z), "=f"(value.w) : "r"(remote) : "memory");
     return value;
 }
 
-// One finished element of the q/k/v projection: token m, element `row` of head `tile`.  Called by all 128 threads of
-// the block with the same m (it meets at block barriers).
-__device__ __forceinline__ void rope_finish(const GemmParams& p, int m, int row, int tile, float value, float* exchange) {
+__device__ __forceinline__ void load_weights4(const void* weight, int is_f32, int first, int limit, float (&w)[4]) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        w[c] = 1.0f;
+        if (weight != nullptr && first + c < limit)
+            w[c] = is_f32 ? reinterpret_cast<const float*>(weight)[first + c]
+                          : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(weight)[first + c]);
+    }
+}
+
+// Four consecutive results as bfloat16 (8 bytes at once where `vector` says the place is aligned) or float (16 bytes);
+// `valid`: how many of the four exist.
+__device__ __forceinline__ void store4_bf16(__nv_bfloat16* dst, const float (&v)[4], int valid, bool vector) {
+    if (valid >= 4 && vector) {
+        __nv_bfloat162 low = __floats2bfloat162_rn(v[0], v[1]), high = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&low);
+        packed.y = *reinterpret_cast<uint32_t*>(&high);
+        *reinterpret_cast<uint2*>(dst) = packed;
+    } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            if (c < valid) dst[c] = __float2bfloat16_rn(v[c]);
+    }
+}
+__device__ __forceinline__ void store4_f32(float* dst, const float (&v)[4], int valid, bool vector) {
+    if (valid >= 4 && vector) {
+        *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            if (c < valid) dst[c] = v[c];
+    }
+}
+
+// What the q/k/v epilogue needs of a token beside the product.
+struct RopeRow {
+    int position;
+    int page;       // of the K and V heads' token slot; -1 outside the pool
+};
+__device__ __forceinline__ RopeRow rope_row(const GemmParams& p, int m, int tile) {
     const RopeEpilogue& e = p.rope;
-    const int warp = row >> 5, lane = row & 31;
+    RopeRow r;
+    r.position = e.positions[m];
+    r.page = 0;
+    if (tile >= e.n_q_heads && e.write_cache) {
+        r.page = e.block_tables[(size_t)e.seq_of_token[m] * e.max_blocks + r.position / e.page_size];
+        if (r.page < 0 || r.page >= e.num_pages) r.page = -1;
+    }
+    return r;
+}
+
+// Token m of head `tile` of the q/k/v projection: per-head norm, rotation, Q to the output, K and V into the cache.
+// `weight`: the head norm's weights of this lane's elements, `frequency`: the rotation's of elements 4 lane + c mod 64.
+__device__ __forceinline__ void rope_finish(const GemmParams& p, int m, int lane, int tile, float (&value)[4],
+                                            const float (&weight)[4], const float (&frequency)[4], RopeRow info) {
+    const RopeEpilogue& e = p.rope;
     const bool is_q = tile < e.n_q_heads;
     const bool is_k = !is_q && tile < e.n_q_heads + e.n_kv_heads;
-    const int position = e.positions[m];
     if (is_q || is_k) {
-        const void* weight = is_q ? e.q_weight : e.k_weight;
-        if (weight != nullptr) {
-            const float squares = warp_sum(value * value);
-            if (lane == 0) exchange[kBlockRows + warp] = squares;
-            __syncthreads();
-            const float total = exchange[kBlockRows] + exchange[kBlockRows + 1] + exchange[kBlockRows + 2] + exchange[kBlockRows + 3];
-            const float w = e.weight_is_f32 ? reinterpret_cast<const float*>(weight)[row]
-                                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(weight)[row]);
-            value = value * rsqrtf(total / (float)kBlockRows + e.eps) * w;
+        if ((is_q ? e.q_weight : e.k_weight) != nullptr) {
+            const float squares = warp_sum(value[0] * value[0] + value[1] * value[1] + value[2] * value[2] + value[3] * value[3]);
+            const float inverse = rsqrtf(squares / (float)kBlockRows + e.eps);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) value[c] = value[c] * inverse * weight[c];
         }
         if (e.inv_freq != nullptr) {
-            exchange[row] = value;
-            __syncthreads();
-            const float partner = exchange[row ^ (kBlockRows / 2)];
-            const float angle = (float)position * e.inv_freq[row & (kBlockRows / 2 - 1)];
-            const float c = cosf(angle), sn = sinf(angle);
-            value = row < kBlockRows / 2 ? value * c - partner * sn : value * c + partner * sn;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float partner = __shfl_xor_sync(0xffffffffu, value[c], 16);      // the element 64 further or back
+                const float angle = (float)info.position * frequency[c];
+                const float cs = cosf(angle), sn = sinf(angle);
+                value[c] = lane < 16 ? value[c] * cs - partner * sn : value[c] * cs + partner * sn;
+            }
         }
-        __syncthreads();      // the exchange buffer is free for the next token
     }
     if (is_q) {
-        reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldc + (size_t)tile * kBlockRows + row] = __float2bfloat16_rn(value);
+        store4_bf16(reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldc + (size_t)tile * kBlockRows + 4 * lane, value, 4, p.vector_out != 0);
     } else if (e.write_cache) {
         const int kv_head = is_k ? tile - e.n_q_heads : tile - e.n_q_heads - e.n_kv_heads;
-        const int page = e.block_tables[(size_t)e.seq_of_token[m] * e.max_blocks + position / e.page_size];
-        if (page < 0 || page >= e.num_pages) {
-            if (row == 0) atomicExch(e.page_error, 1 + m);
+        if (info.page < 0) {
+            if (lane == 0) atomicExch(e.page_error, 1 + m);
         } else {
             __nv_bfloat16* pages = is_k ? e.k_pages : e.v_pages;
-            pages[(((size_t)page * e.n_kv_heads + kv_head) * e.page_size + position % e.page_size) * kBlockRows + row] = __float2bfloat16_rn(value);
+            store4_bf16(pages + (((size_t)info.page * e.n_kv_heads + kv_head) * e.page_size + info.position % e.page_size) * kBlockRows + 4 * lane,
+                        value, 4, p.vector_out != 0);
         }
     }
 }
 
-// One finished element of the fused gate/up projection: rows 0..63 of the tile hold gate values, rows 64..127 the up
-// values of the same outputs.  Called by all 128 threads of the block with the same m.  The arithmetic is that of the
-// stand-alone kernel of activation.cu for 16-bit activations, on the 32-bit sums of the product.
-__device__ __forceinline__ void silu_finish(const GemmParams& p, int m, int row, int tile, float value, float* exchange) {
+// Token m of a tile of the fused gate/up projection: elements 0..63 of the tile are gate values, 64..127 the up values
+// of the same outputs, so lane i < 16 finds its up values in lane i + 16.  The arithmetic is that of the stand-alone
+// kernel of activation.cu for 16-bit activations, on the 32-bit sums of the product.
+__device__ __forceinline__ void silu_finish(const GemmParams& p, int m, int lane, int tile, const float (&value)[4]) {
     constexpr int kHalf = kBlockRows / 2;
-    if (row >= kHalf) exchange[row - kHalf] = value;
-    __syncthreads();
-    if (row < kHalf) {
-        const int column = tile * kHalf + row;
-        if (column < p.n / 2)
-            reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldc + column] =
-                __float2bfloat16_rn(__fdividef(value, 1.0f + __expf(-value)) * exchange[row]);
+    float result[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const float up = __shfl_xor_sync(0xffffffffu, value[c], 16);
+        result[c] = __fdividef(value[c], 1.0f + __expf(-value[c])) * up;
     }
-    __syncthreads();
+    if (lane < 16) {
+        const int column = tile * kHalf + 4 * lane;
+        store4_bf16(reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldc + column, result, p.n / 2 - column, p.vector_out != 0);
+    }
 }
 
-// One finished element of a product that is added to the residual stream: token m, column tile * 128 + row; `before`
-// is the stream's value there (0 outside the matrix).  Called by whole warps with the same m.
-__device__ __forceinline__ void stream_finish(const GemmParams& p, int m, int row, int tile, float value, float before) {
+// Token m of a product that is added to the residual stream: columns n4 .. n4 + 3; `before`: the stream's values
+// there, `weight`: the next norm's weights of those columns.
+__device__ __forceinline__ void stream_finish(const GemmParams& p, int m, int lane, int tile, int n4, const float (&value)[4],
+                                              const float (&before)[4], const float (&weight)[4]) {
     const StreamEpilogue& e = p.stream;
-    const int n = tile * kBlockRows + row;
-    float updated = 0.0f;
-    if (n < p.n) {
-        updated = before + value;
-        e.residual[(size_t)m * p.n + n] = updated;
-        if (e.next_weight != nullptr) {
-            const float w = e.weight_is_f32 ? reinterpret_cast<const float*>(e.next_weight)[n]
-                                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(e.next_weight)[n]);
-            e.scaled[(size_t)m * p.n + n] = __float2bfloat16_rn(updated * w);
-        }
+    const int valid = p.n - n4;       // <= 0: this lane's columns lie outside the matrix
+    float updated[4], scaled[4], squares = 0.0f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        updated[c] = c < valid ? before[c] + value[c] : 0.0f;
+        scaled[c] = updated[c] * weight[c];
+        squares += updated[c] * updated[c];
+    }
+    if (valid > 0) {
+        store4_f32(e.residual + (size_t)m * p.n + n4, updated, valid, p.vector_stream != 0);
+        if (e.next_weight != nullptr) store4_bf16(e.scaled + (size_t)m * p.n + n4, scaled, valid, p.vector_stream != 0);
     }
     if (e.next_weight != nullptr) {
-        const float squares = warp_sum(updated * updated);
-        if ((row & 31) == 0) e.parts[(size_t)(tile * 4 + (row >> 5)) * e.stride + m] = squares;
+        squares = warp_sum(squares);
+        if (lane == 0) e.parts[(size_t)tile * e.stride + m] = squares;
     }
 }
 
@@ -264,7 +329,6 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
     __shared__ __align__(8) uint64_t accum_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed;
-    __shared__ float exchange[kBlockRows + 4];      // rope epilogue: a head's elements and its warps' sums
     __shared__ float row_scale[64];                 // RowScale: 1 / rms of each token's stream row
 
     // the dynamic region is aligned to 1024 bytes by hand (the swizzle atoms need it)
@@ -393,11 +457,13 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
         __syncthreads();
     }
 
+    // The tile of sums goes from tensor memory (lane = row of W, column = token) into shared memory as
+    // [token][128 rows], over the stages, which nobody reads any more; with K split, every rank's part lies in its own
+    // shared memory then.
     const int row = warp * 32 + lane;                 // row of the W tile
-    float* reduce = reinterpret_cast<float*>(aligned);   // [token_pad][128], reuses the stage memory
-    const int n = n0 + row;
-    const bool scaled = p.scale.parts != nullptr;
+    float* parts_tile = reinterpret_cast<float*>(aligned);
     for (int c0 = 0; c0 < p.token_pad; c0 += 16) {
+        if (c0 >= p.m) break;
         float values[16];
         if (n_kb > 0 && !bad) {
             tmem_load_16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, values);
@@ -405,83 +471,96 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
 #pragma unroll
             for (int i = 0; i < 16; ++i) values[i] = 0.0f;
         }
-        if (p.split > 1) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) reduce[(c0 + i) * kBlockRows + row] = values[i];
-            continue;
+        for (int i = 0; i < 16; ++i) parts_tile[(c0 + i) * kBlockRows + row] = values[i];
+    }
+    if (p.split > 1) cluster_sync();
+    else __syncthreads();
+
+    // Token rows are dealt round-robin to the ranks, and a rank's rows round-robin to its four warps; lane i finishes
+    // elements 4 i .. 4 i + 3 of the tile.  A warp asks for everything two of its tokens need at once (the ranks' parts,
+    // from the peers' shared memory; positions, pages, the stream's values) and adds the parts in the order of the ranks.
+    const int r4 = 4 * lane, n4 = n0 + r4;
+    const bool scaled = p.scale.parts != nullptr;
+    const uint32_t parts_address = smem_u32(parts_tile);
+    float weight[4] = {1.0f, 1.0f, 1.0f, 1.0f}, frequency[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (p.rope.on) {
+        const bool is_q = tile < p.rope.n_q_heads, is_k = !is_q && tile < p.rope.n_q_heads + p.rope.n_kv_heads;
+        if (is_q || is_k) {
+            load_weights4(is_q ? p.rope.q_weight : p.rope.k_weight, p.rope.weight_is_f32, r4, kBlockRows, weight);
+            if (p.rope.inv_freq != nullptr) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) frequency[c] = p.rope.inv_freq[(r4 + c) & (kBlockRows / 2 - 1)];
+            }
         }
-        if (scaled) {
+    } else if (p.stream.on) {
+        load_weights4(p.stream.next_weight, p.stream.weight_is_f32, n4, p.n, weight);
+    }
+    constexpr int kTokensAtOnce = 2;
+    const int token_step = 4 * p.split;               // between two tokens of one warp
+    for (int m0 = (int)rank + p.split * warp; m0 < p.m; m0 += kTokensAtOnce * token_step) {
+        float4 parts[kTokensAtOnce][kMaxSplit];
+        float before[kTokensAtOnce][4];
+        RopeRow info[kTokensAtOnce];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) values[i] *= c0 + i < p.m ? row_scale[c0 + i] : 0.0f;
-        }
-        if (p.stream.on) {
+        for (int j = 0; j < kTokensAtOnce; ++j) {
+            const int m = m0 + j * token_step;
+            info[j].position = info[j].page = 0;
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-                if (c0 + i < p.m)
-                    stream_finish(p, c0 + i, row, tile, values[i], n < p.n ? p.stream.residual[(size_t)(c0 + i) * p.n + n] : 0.0f);
-        } else if (p.rope.on) {
+            for (int c = 0; c < 4; ++c) before[j][c] = 0.0f;
+            if (m >= p.m) continue;       // the same for the whole warp
+            if (p.rope.on) info[j] = rope_row(p, m, tile);
+            if (p.stream.on) {
+                if (p.vector_stream && n4 + 3 < p.n) {
+                    const float4 v = *reinterpret_cast<const float4*>(p.stream.residual + (size_t)m * p.n + n4);
+                    before[j][0] = v.x, before[j][1] = v.y, before[j][2] = v.z, before[j][3] = v.w;
+                } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-                if (c0 + i < p.m) rope_finish(p, c0 + i, row, tile, values[i], exchange);
-        } else if (p.silu_gate) {
+                    for (int c = 0; c < 4; ++c)
+                        if (n4 + c < p.n) before[j][c] = p.stream.residual[(size_t)m * p.n + n4 + c];
+                }
+            }
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-                if (c0 + i < p.m) silu_finish(p, c0 + i, row, tile, values[i], exchange);
-        } else if (n < p.n) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const int m = c0 + i;
-                if (m < p.m) {
-                    if (p.out_is_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldc + n] = values[i];
-                    else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(values[i]);
+            for (int peer = 0; peer < kMaxSplit; ++peer) {
+                if (peer >= p.split) {
+                    parts[j][peer] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                } else if (p.split > 1) {
+                    parts[j][peer] = load_peer4(parts_address + (uint32_t)(m * kBlockRows + r4) * 4u, (uint32_t)peer);
+                } else {
+                    parts[j][peer] = *reinterpret_cast<const float4*>(parts_tile + m * kBlockRows + r4);
                 }
             }
         }
-    }
-    if (p.split > 1) {
-        cluster_sync();          // every CTA's partial tile is in its shared memory
-        const uint32_t reduce_address = smem_u32(reduce);
-        // Token rows are dealt round-robin to the ranks.  The peers' parts of up to four rows are all requested
-        // before the first is used (a load from a peer's shared memory takes some hundred cycles; one at a time
-        // they were most of the epilogue), then summed in the order of the ranks.
-        constexpr int kRowsAtOnce = 4;
-        for (int m0 = (int)rank; m0 < p.m; m0 += kRowsAtOnce * p.split) {
-            float parts[kRowsAtOnce][kMaxSplit];
-            float before[kRowsAtOnce];      // the stream's values, asked for together with the peers' parts
 #pragma unroll
-            for (int j = 0; j < kRowsAtOnce; ++j) {
-                const int m = m0 + j * p.split;
-                before[j] = (p.stream.on && m < p.m && n < p.n) ? p.stream.residual[(size_t)m * p.n + n] : 0.0f;
+        for (int j = 0; j < kTokensAtOnce; ++j) {
+            const int m = m0 + j * token_step;
+            if (m >= p.m) continue;
+            float total[4] = {parts[j][0].x, parts[j][0].y, parts[j][0].z, parts[j][0].w};
+#pragma unroll
+            for (int peer = 1; peer < kMaxSplit; ++peer) {      // absent peers add 0
+                total[0] += parts[j][peer].x;
+                total[1] += parts[j][peer].y;
+                total[2] += parts[j][peer].z;
+                total[3] += parts[j][peer].w;
             }
+            if (scaled) {
+                const float s = row_scale[m];
 #pragma unroll
-            for (int j = 0; j < kRowsAtOnce; ++j) {
-                const int m = m0 + j * p.split;
-#pragma unroll
-                for (int peer = 0; peer < kMaxSplit; ++peer)
-                    parts[j][peer] = (m < p.m && peer < p.split)
-                                         ? load_peer(reduce_address + (uint32_t)(m * kBlockRows + row) * 4u, (uint32_t)peer) : 0.0f;
+                for (int c = 0; c < 4; ++c) total[c] *= s;
             }
-#pragma unroll
-            for (int j = 0; j < kRowsAtOnce; ++j) {
-                const int m = m0 + j * p.split;
-                float total = parts[j][0];
-#pragma unroll
-                for (int peer = 1; peer < kMaxSplit; ++peer) total += parts[j][peer];      // absent peers add 0
-                if (scaled && m < p.m) total *= row_scale[m];
-                if (p.stream.on) {
-                    if (m < p.m) stream_finish(p, m, row, tile, total, before[j]);
-                } else if (p.rope.on) {
-                    if (m < p.m) rope_finish(p, m, row, tile, total, exchange);
-                } else if (p.silu_gate) {
-                    if (m < p.m) silu_finish(p, m, row, tile, total, exchange);
-                } else if (m < p.m && n < p.n) {
-                    if (p.out_is_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldc + n] = total;
-                    else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(total);
-                }
+            if (p.stream.on) {
+                stream_finish(p, m, lane, tile, n4, total, before[j], weight);
+            } else if (p.rope.on) {
+                rope_finish(p, m, lane, tile, total, weight, frequency, info[j]);
+            } else if (p.silu_gate) {
+                silu_finish(p, m, lane, tile, total);
+            } else if (n4 < p.n) {
+                if (p.out_is_f32) store4_f32(reinterpret_cast<float*>(p.out) + (size_t)m * p.ldc + n4, total, p.n - n4, p.vector_out != 0);
+                else store4_bf16(reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldc + n4, total, p.n - n4, p.vector_out != 0);
             }
         }
-        cluster_sync();          // nobody leaves while a peer may still read its shared memory
     }
+    if (p.split > 1) cluster_sync();          // nobody leaves while a peer may still read its shared memory
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(64));
@@ -543,6 +622,9 @@ static int small_m_launch(const void* x, const void* w, void* out, int m, int n,
         p.stream = StreamEpilogue{};
         p.stream.on = 0;
     }
+    p.vector_out = out != nullptr && aligned16(out) && ldc % 4 == 0 &&
+                   (rope == nullptr || (aligned16(rope->k_pages) && aligned16(rope->v_pages)));
+    p.vector_stream = p.stream.on && aligned16(p.stream.residual) && (p.stream.scaled == nullptr || aligned16(p.stream.scaled)) && n % 4 == 0;
     const int tiles = (n + kBlockRows - 1) / kBlockRows;
     const int total_kb = (k + kBlockK - 1) / kBlockK;
     // K is split across a cluster so that the tiles fill the machine; each rank keeps >= 4 K blocks.  The
@@ -618,7 +700,7 @@ LLM_EXPORT int llm_gemm_small_m(const void* x, const void* w, void* out, int m, 
 }
 
 // How many partial sums of squares per token llm_gemm_into_stream leaves for a stream of n columns.
-LLM_EXPORT int llm_gemm_into_stream_parts(int n) { return 4 * ((n + kBlockRows - 1) / kBlockRows); }
+LLM_EXPORT int llm_gemm_into_stream_parts(int n) { return (n + kBlockRows - 1) / kBlockRows; }
 
 // residual[m, n] += x[m, k] W^T (32-bit stream, contiguous).  With next_weight [n] (bfloat16, or float when
 // weight_is_f32): scaled[m, n] = bfloat16(residual * next_weight) and parts[i * parts_stride + token], i <
