@@ -12,7 +12,7 @@
 //
 // The epilogue moves the tile through shared memory as [token][128 rows] and hands whole token rows to warps: a
 // token's 128 elements are four per lane, so per-head and per-row reductions are warp reductions, rotation partners
-// and gate/up pairs a shuffle away, stores 8 or 16 bytes per lane, and the four warps work on different tokens
+// and gate/up pairs a shuffle away, stores 8 or 16 bytes per lane, and the warps work on different tokens
 // without a block barrier (per-token block barriers cost 9 to 14 us of a q/k/v product at 32 to 64 tokens).
 //
 // One elected thread issues the TMA copies, one issues the MMAs; mbarriers carry "stage full" (TMA
@@ -48,7 +48,8 @@ constexpr int kBlockRows = 128;     // rows of W per CTA (UMMA M)
 constexpr int kAtomK = 64;          // one 128-byte swizzle atom of bfloat16
 constexpr int kAtoms = 2;           // atoms per pipeline stage
 constexpr int kBlockK = kAtomK * kAtoms;
-constexpr int kThreads = 128;
+constexpr int kThreads = 256;       // at most: four warps up to 16 tokens, eight beyond (two have a role in the main
+                                    // loop, all work in the epilogue, whose time per token is instruction issue)
 constexpr int kMaxStages = 12;
 constexpr int kMaxSplit = 8;
 
@@ -173,7 +174,7 @@ __device__ __forceinline__ void cluster_sync() {
 // ---- The epilogues.  A finished token row of a tile is handled by ONE WARP: lane i holds the four elements
 // 4 i .. 4 i + 3 of the tile's 128, so a head's sum of squares or a stream row's is one warp reduction, the partner of
 // a rotation (64 elements further) and the up value of a gate sit in lane i ^ 16, and every store is 8 or 16 bytes per
-// lane and 256 or 512 contiguous bytes per warp.  The four warps of a block take different tokens at the same time
+// lane and 256 or 512 contiguous bytes per warp.  The warps of a block take different tokens at the same time
 // and never meet at a block barrier; what a token needs beside the sums (its position, its page, the stream's values)
 // is asked for together with the sums' parts.
 
@@ -342,7 +343,7 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
     const uint32_t stage_bytes = b_offset + kAtoms * b_pitch;
 
     pdl_trigger();   // let the next kernel start launching
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
     const uint32_t rank = p.split > 1 ? cluster_rank() : 0;
     const int tile = blockIdx.x / p.split;
     const int n0 = tile * kBlockRows;
@@ -433,7 +434,7 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
         // ---- the two warps without a role in the main loop add the sums of squares, in an order that depends on
         // the number of parts only, and leave 1 / rms per token for the epilogue
         pdl_wait();
-        for (int m = warp - 2; m < p.m; m += 2) {
+        for (int m = warp - 2; m < p.m; m += n_warps - 2) {
             float squares = 0.0f;
             for (int i = lane; i < p.scale.n_parts; i += 32) squares += p.scale.parts[(size_t)i * p.scale.stride + m];
             squares = warp_sum(squares);
@@ -441,7 +442,7 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
         }
     }
 
-    // ---- epilogue: all four warps; warp w reads tensor-memory lanes 32 w .. 32 w + 31 = rows of the tile
+    // ---- epilogue: all warps
     __syncwarp();
     pdl_wait();     // global memory is written below: the kernels before this one must be done with it
     bool ready = true;
@@ -460,13 +461,15 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
     // The tile of sums goes from tensor memory (lane = row of W, column = token) into shared memory as
     // [token][128 rows], over the stages, which nobody reads any more; with K split, every rank's part lies in its own
     // shared memory then.
-    const int row = warp * 32 + lane;                 // row of the W tile
+    // warp w reads tensor-memory lanes 32 (w mod 4) .. + 31 = rows of the tile; warps 0-3 and 4-7 take turns with the
+    // groups of 16 tokens
+    const int row = (warp & 3) * 32 + lane;
     float* parts_tile = reinterpret_cast<float*>(aligned);
-    for (int c0 = 0; c0 < p.token_pad; c0 += 16) {
+    for (int c0 = (warp >> 2) * 16; c0 < p.token_pad; c0 += 4 * n_warps) {
         if (c0 >= p.m) break;
         float values[16];
         if (n_kb > 0 && !bad) {
-            tmem_load_16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, values);
+            tmem_load_16(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)c0, values);
         } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) values[i] = 0.0f;
@@ -477,7 +480,7 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
     if (p.split > 1) cluster_sync();
     else __syncthreads();
 
-    // Token rows are dealt round-robin to the ranks, and a rank's rows round-robin to its four warps; lane i finishes
+    // Token rows are dealt round-robin to the ranks, and a rank's rows round-robin to its warps; lane i finishes
     // elements 4 i .. 4 i + 3 of the tile.  A warp asks for everything two of its tokens need at once (the ranks' parts,
     // from the peers' shared memory; positions, pages, the stream's values) and adds the parts in the order of the ranks.
     const int r4 = 4 * lane, n4 = n0 + r4;
@@ -496,8 +499,8 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
     } else if (p.stream.on) {
         load_weights4(p.stream.next_weight, p.stream.weight_is_f32, n4, p.n, weight);
     }
-    constexpr int kTokensAtOnce = 2;
-    const int token_step = 4 * p.split;               // between two tokens of one warp
+    constexpr int kTokensAtOnce = 1;
+    const int token_step = n_warps * p.split;         // between two tokens of one warp
     for (int m0 = (int)rank + p.split * warp; m0 < p.m; m0 += kTokensAtOnce * token_step) {
         float4 parts[kTokensAtOnce][kMaxSplit];
         float before[kTokensAtOnce][4];
@@ -664,7 +667,7 @@ static int small_m_launch(const void* x, const void* w, void* out, int m, int n,
     if (int limit_status = llm_raise_shared_limit(reinterpret_cast<const void*>(gemm_small_m_kernel), (size_t)226 * 1024, "gemm_small_m")) return limit_status;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3((unsigned)(tiles * split), 1, 1);
-    config.blockDim = dim3(kThreads, 1, 1);
+    config.blockDim = dim3(m > 16 ? kThreads : kThreads / 2, 1, 1);
     config.dynamicSmemBytes = shared;
     config.stream = stream;
     cudaLaunchAttribute attribute[2];

@@ -15,7 +15,7 @@ import torch
 
 # up to this many rows a step runs this way (the rows this package's product kernel is used for);
 # LLMSERVER_B200_STREAM_EPILOGUES=0 switches it off (the stand-alone add + norm kernel then runs at every row count)
-STREAM_ROWS = 16 if os.environ.get("LLMSERVER_B200_STREAM_EPILOGUES", "1") != "0" else 0
+STREAM_ROWS = int(os.environ.get("LLMSERVER_B200_STREAM_ROWS", "16")) if os.environ.get("LLMSERVER_B200_STREAM_EPILOGUES", "1") != "0" else 0
 NO_SCALE = (0, 0, 0, 0.0)
 
 
