@@ -239,6 +239,26 @@ __device__ __forceinline__ RopeRow rope_row(const GemmParams& p, int m, int tile
     return r;
 }
 
+// What finishing token m needs beside the product: its position and page (q/k/v epilogue) or the stream's values at
+// columns n4 .. n4 + 3 (stream epilogue).  Nothing for a token that does not exist.
+__device__ __forceinline__ void token_inputs(const GemmParams& p, int m, int tile, int n4, RopeRow& info, float (&before)[4]) {
+    info.position = info.page = 0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) before[c] = 0.0f;
+    if (m >= p.m) return;
+    if (p.rope.on) info = rope_row(p, m, tile);
+    if (p.stream.on) {
+        if (p.vector_stream && n4 + 3 < p.n) {
+            const float4 v = *reinterpret_cast<const float4*>(p.stream.residual + (size_t)m * p.n + n4);
+            before[0] = v.x, before[1] = v.y, before[2] = v.z, before[3] = v.w;
+        } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                if (n4 + c < p.n) before[c] = p.stream.residual[(size_t)m * p.n + n4 + c];
+        }
+    }
+}
+
 // Token m of head `tile` of the q/k/v projection: per-head norm, rotation, Q to the output, K and V into the cache.
 // `weight`: the head norm's weights of this lane's elements, `frequency`: the rotation's of elements 4 lane + c mod 64.
 __device__ __forceinline__ void rope_finish(const GemmParams& p, int m, int lane, int tile, float (&value)[4],
@@ -445,6 +465,28 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
     // ---- epilogue: all warps
     __syncwarp();
     pdl_wait();     // global memory is written below: the kernels before this one must be done with it
+    // What the epilogue needs beside the product is asked for now, while the product is still being made: the norm
+    // weights and frequencies of this lane's four elements, and for the first token this warp will finish its
+    // position and page (a chain of three dependent loads) or the stream's values.
+    const int r4 = 4 * lane, n4 = n0 + r4;
+    const int token_step = n_warps * p.split;         // between two tokens of one warp (rows are dealt round-robin to
+    const int first_token = (int)rank + p.split * warp;   // the ranks, a rank's rows round-robin to its warps)
+    float weight[4] = {1.0f, 1.0f, 1.0f, 1.0f}, frequency[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    RopeRow info;
+    float before[4];
+    if (p.rope.on) {
+        const bool is_q = tile < p.rope.n_q_heads, is_k = !is_q && tile < p.rope.n_q_heads + p.rope.n_kv_heads;
+        if (is_q || is_k) {
+            load_weights4(is_q ? p.rope.q_weight : p.rope.k_weight, p.rope.weight_is_f32, r4, kBlockRows, weight);
+            if (p.rope.inv_freq != nullptr) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) frequency[c] = p.rope.inv_freq[(r4 + c) & (kBlockRows / 2 - 1)];
+            }
+        }
+    } else if (p.stream.on) {
+        load_weights4(p.stream.next_weight, p.stream.weight_is_f32, n4, p.n, weight);
+    }
+    token_inputs(p, first_token, tile, n4, info, before);
     bool ready = true;
     if (n_kb > 0) ready = mbar_wait(smem_u32(&accum_bar), 0);
     if (!ready) failed = 1;
@@ -480,87 +522,45 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
     if (p.split > 1) cluster_sync();
     else __syncthreads();
 
-    // Token rows are dealt round-robin to the ranks, and a rank's rows round-robin to its warps; lane i finishes
-    // elements 4 i .. 4 i + 3 of the tile.  A warp asks for everything two of its tokens need at once (the ranks' parts,
-    // from the peers' shared memory; positions, pages, the stream's values) and adds the parts in the order of the ranks.
-    const int r4 = 4 * lane, n4 = n0 + r4;
+    // Lane i finishes elements 4 i .. 4 i + 3 of the tile for its warp's tokens, one token after the other.
     const bool scaled = p.scale.parts != nullptr;
     const uint32_t parts_address = smem_u32(parts_tile);
-    float weight[4] = {1.0f, 1.0f, 1.0f, 1.0f}, frequency[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    if (p.rope.on) {
-        const bool is_q = tile < p.rope.n_q_heads, is_k = !is_q && tile < p.rope.n_q_heads + p.rope.n_kv_heads;
-        if (is_q || is_k) {
-            load_weights4(is_q ? p.rope.q_weight : p.rope.k_weight, p.rope.weight_is_f32, r4, kBlockRows, weight);
-            if (p.rope.inv_freq != nullptr) {
+    for (int m = first_token; m < p.m; m += token_step) {
+        if (m != first_token) token_inputs(p, m, tile, n4, info, before);
+        // the ranks' parts of the token, all asked for before the first is used, added in the order of the ranks
+        float4 parts[kMaxSplit];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) frequency[c] = p.rope.inv_freq[(r4 + c) & (kBlockRows / 2 - 1)];
+        for (int peer = 0; peer < kMaxSplit; ++peer) {
+            if (peer >= p.split) {
+                parts[peer] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            } else if (p.split > 1) {
+                parts[peer] = load_peer4(parts_address + (uint32_t)(m * kBlockRows + r4) * 4u, (uint32_t)peer);
+            } else {
+                parts[peer] = *reinterpret_cast<const float4*>(parts_tile + m * kBlockRows + r4);
             }
         }
-    } else if (p.stream.on) {
-        load_weights4(p.stream.next_weight, p.stream.weight_is_f32, n4, p.n, weight);
-    }
-    constexpr int kTokensAtOnce = 1;
-    const int token_step = n_warps * p.split;         // between two tokens of one warp
-    for (int m0 = (int)rank + p.split * warp; m0 < p.m; m0 += kTokensAtOnce * token_step) {
-        float4 parts[kTokensAtOnce][kMaxSplit];
-        float before[kTokensAtOnce][4];
-        RopeRow info[kTokensAtOnce];
+        float total[4] = {parts[0].x, parts[0].y, parts[0].z, parts[0].w};
 #pragma unroll
-        for (int j = 0; j < kTokensAtOnce; ++j) {
-            const int m = m0 + j * token_step;
-            info[j].position = info[j].page = 0;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) before[j][c] = 0.0f;
-            if (m >= p.m) continue;       // the same for the whole warp
-            if (p.rope.on) info[j] = rope_row(p, m, tile);
-            if (p.stream.on) {
-                if (p.vector_stream && n4 + 3 < p.n) {
-                    const float4 v = *reinterpret_cast<const float4*>(p.stream.residual + (size_t)m * p.n + n4);
-                    before[j][0] = v.x, before[j][1] = v.y, before[j][2] = v.z, before[j][3] = v.w;
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        if (n4 + c < p.n) before[j][c] = p.stream.residual[(size_t)m * p.n + n4 + c];
-                }
-            }
-#pragma unroll
-            for (int peer = 0; peer < kMaxSplit; ++peer) {
-                if (peer >= p.split) {
-                    parts[j][peer] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                } else if (p.split > 1) {
-                    parts[j][peer] = load_peer4(parts_address + (uint32_t)(m * kBlockRows + r4) * 4u, (uint32_t)peer);
-                } else {
-                    parts[j][peer] = *reinterpret_cast<const float4*>(parts_tile + m * kBlockRows + r4);
-                }
-            }
+        for (int peer = 1; peer < kMaxSplit; ++peer) {      // absent peers add 0
+            total[0] += parts[peer].x;
+            total[1] += parts[peer].y;
+            total[2] += parts[peer].z;
+            total[3] += parts[peer].w;
         }
+        if (scaled) {
+            const float s = row_scale[m];
 #pragma unroll
-        for (int j = 0; j < kTokensAtOnce; ++j) {
-            const int m = m0 + j * token_step;
-            if (m >= p.m) continue;
-            float total[4] = {parts[j][0].x, parts[j][0].y, parts[j][0].z, parts[j][0].w};
-#pragma unroll
-            for (int peer = 1; peer < kMaxSplit; ++peer) {      // absent peers add 0
-                total[0] += parts[j][peer].x;
-                total[1] += parts[j][peer].y;
-                total[2] += parts[j][peer].z;
-                total[3] += parts[j][peer].w;
-            }
-            if (scaled) {
-                const float s = row_scale[m];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) total[c] *= s;
-            }
-            if (p.stream.on) {
-                stream_finish(p, m, lane, tile, n4, total, before[j], weight);
-            } else if (p.rope.on) {
-                rope_finish(p, m, lane, tile, total, weight, frequency, info[j]);
-            } else if (p.silu_gate) {
-                silu_finish(p, m, lane, tile, total);
-            } else if (n4 < p.n) {
-                if (p.out_is_f32) store4_f32(reinterpret_cast<float*>(p.out) + (size_t)m * p.ldc + n4, total, p.n - n4, p.vector_out != 0);
-                else store4_bf16(reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldc + n4, total, p.n - n4, p.vector_out != 0);
-            }
+            for (int c = 0; c < 4; ++c) total[c] *= s;
+        }
+        if (p.stream.on) {
+            stream_finish(p, m, lane, tile, n4, total, before, weight);
+        } else if (p.rope.on) {
+            rope_finish(p, m, lane, tile, total, weight, frequency, info);
+        } else if (p.silu_gate) {
+            silu_finish(p, m, lane, tile, total);
+        } else if (n4 < p.n) {
+            if (p.out_is_f32) store4_f32(reinterpret_cast<float*>(p.out) + (size_t)m * p.ldc + n4, total, p.n - n4, p.vector_out != 0);
+            else store4_bf16(reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldc + n4, total, p.n - n4, p.vector_out != 0);
         }
     }
     if (p.split > 1) cluster_sync();          // nobody leaves while a peer may still read its shared memory
