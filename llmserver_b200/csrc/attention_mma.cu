@@ -754,32 +754,42 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
     // four warps' rows, for the splits that merge inside a cluster
     float* mine = merge + (size_t)4 * 16 * (D + 2);
     const bool in_cluster = meets_cluster;
-    for (int index = threadIdx.x; index < group * D; index += kThreads) {
-        const int r = index / D, d = index % D;
-        float best = -INFINITY;
+    // a warp takes whole heads of the group (their maxima and weights are made once per head, not once per element),
+    // a lane two neighbouring elements at a time
+    for (int r = warp; r < group; r += 4) {
+        float weights[4], best = -INFINITY, denominator = 0.0f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) best = fmaxf(best, merge[((size_t)w * 16 + r) * (D + 2) + D]);
-        float numerator = 0.0f, denominator = 0.0f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float* row = merge + ((size_t)w * 16 + r) * (D + 2);
-            const float weight = row[D] == -INFINITY ? 0.0f : exp2f(row[D] - best);
-            numerator += row[d] * weight;
-            denominator += row[D + 1] * weight;
+            weights[w] = row[D] == -INFINITY ? 0.0f : exp2f(row[D] - best);
+            denominator += row[D + 1] * weights[w];
         }
         const int head = kv_head * group + r;
-        if (n_splits == 1) {
-            p.out[(size_t)token * p.n_q_heads * D + (size_t)head * D + d] = __float2bfloat16_rn(numerator / denominator);
-        } else if (in_cluster) {
-            mine[r * (D + 2) + d] = numerator / denominator;
-            if (d == 0) {
+        const size_t slot = ((size_t)(p.slot_by_seq ? seq : token) * p.n_q_heads + head) * p.max_splits + split;
+        for (int d = 2 * lane; d < D; d += 64) {
+            float numerator[2] = {0.0f, 0.0f};
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float2 pair = *reinterpret_cast<const float2*>(merge + ((size_t)w * 16 + r) * (D + 2) + d);
+                numerator[0] += pair.x * weights[w];
+                numerator[1] += pair.y * weights[w];
+            }
+            if (n_splits == 1) {
+                *reinterpret_cast<__nv_bfloat162*>(p.out + (size_t)token * p.n_q_heads * D + (size_t)head * D + d) =
+                    __floats2bfloat162_rn(numerator[0] / denominator, numerator[1] / denominator);
+            } else if (in_cluster) {
+                *reinterpret_cast<float2*>(mine + r * (D + 2) + d) = make_float2(numerator[0] / denominator, numerator[1] / denominator);
+            } else {
+                *reinterpret_cast<float2*>(p.partial_out + slot * D + d) = make_float2(numerator[0] / denominator, numerator[1] / denominator);
+            }
+        }
+        if (lane == 0 && n_splits > 1) {
+            if (in_cluster) {
                 mine[r * (D + 2) + D] = best;
                 mine[r * (D + 2) + D + 1] = denominator;
-            }
-        } else {
-            const size_t slot = ((size_t)(p.slot_by_seq ? seq : token) * p.n_q_heads + head) * p.max_splits + split;
-            p.partial_out[slot * D + d] = numerator / denominator;
-            if (d == 0) {
+            } else {
                 p.partial_ml[slot * 2] = best;
                 p.partial_ml[slot * 2 + 1] = denominator;
             }
