@@ -13,9 +13,12 @@ from typing import Optional
 
 import torch
 
-# up to this many rows a step runs this way (the rows this package's product kernel is used for);
-# LLMSERVER_B200_STREAM_EPILOGUES=0 switches it off (the stand-alone add + norm kernel then runs at every row count)
-STREAM_ROWS = int(os.environ.get("LLMSERVER_B200_STREAM_ROWS", "16")) if os.environ.get("LLMSERVER_B200_STREAM_EPILOGUES", "1") != "0" else 0
+# Up to this many rows a step runs this way: 16, the rows up to which this package's product kernel is always used
+# (LLMSERVER_B200_STREAM_ROWS changes it, up to the kernel's 64 rows; beyond 16 rows the library's products win most
+# measurements and the stand-alone kernels run beside them).  LLMSERVER_B200_STREAM_EPILOGUES=0 switches it off: the
+# stand-alone add + norm kernel then runs at every row count.
+STREAM_ROWS = (min(max(int(os.environ.get("LLMSERVER_B200_STREAM_ROWS", "16")), 0), 64)
+               if os.environ.get("LLMSERVER_B200_STREAM_EPILOGUES", "1") != "0" else 0)
 NO_SCALE = (0, 0, 0, 0.0)
 
 
