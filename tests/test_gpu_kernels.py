@@ -653,7 +653,8 @@ def test_the_microbenchmarks_run(capsys):
 
 @pytest.mark.parametrize("rows,cols,inner,split,weight_dtype,with_norm", [
     (1, 4096, 12288, 0, torch.bfloat16, True), (8, 4096, 4096, 4, torch.bfloat16, True), (16, 200, 136, 1, torch.float32, True),
-    (5, 1000, 512, 2, torch.bfloat16, True), (3, 328, 264, 0, torch.bfloat16, False)])
+    (5, 1000, 512, 2, torch.bfloat16, True), (3, 328, 264, 0, torch.bfloat16, False),
+    (7, 326, 264, 3, torch.bfloat16, True), (2, 130, 72, 1, torch.float32, True)])      # widths that are no multiple of four
 def test_product_added_to_the_stream_in_its_epilogue(rows, cols, inner, split, weight_dtype, with_norm):
     """residual += x W^T inside the product kernel, with the next norm's input prepared: the stream times the norm's
     weight and, in parts, the rows' sums of squares."""
