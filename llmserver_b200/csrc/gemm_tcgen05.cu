@@ -178,6 +178,11 @@ __device__ __forceinline__ void cluster_sync() {
 // and never meet at a block barrier; what a token needs beside the sums (its position, its page, the stream's values)
 // is asked for together with the sums' parts.
 
+// The two halves of a cluster barrier, for a block that says "I have read all I need of your shared memory" as soon
+// as that is so and waits for the others' word only before it leaves.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ float4 load_peer4(uint32_t local_address, uint32_t rank) {
     uint32_t remote;
     float4 value;
@@ -525,6 +530,7 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
     // Lane i finishes elements 4 i .. 4 i + 3 of the tile for its warp's tokens, one token after the other.
     const bool scaled = p.scale.parts != nullptr;
     const uint32_t parts_address = smem_u32(parts_tile);
+    bool arrived = false;
     for (int m = first_token; m < p.m; m += token_step) {
         if (m != first_token) token_inputs(p, m, tile, n4, info, before);
         // the ranks' parts of the token, all asked for before the first is used, added in the order of the ranks
@@ -547,6 +553,10 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
             total[2] += parts[peer].z;
             total[3] += parts[peer].w;
         }
+        if (p.split > 1 && m + token_step >= p.m) {      // this warp's last token: its parts are here (they were added)
+            cluster_arrive();
+            arrived = true;
+        }
         if (scaled) {
             const float s = row_scale[m];
 #pragma unroll
@@ -563,7 +573,10 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
             else store4_bf16(reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldc + n4, total, p.n - n4, p.vector_out != 0);
         }
     }
-    if (p.split > 1) cluster_sync();          // nobody leaves while a peer may still read its shared memory
+    if (p.split > 1) {          // nobody leaves while a peer may still read its shared memory
+        if (!arrived) cluster_arrive();
+        cluster_wait();
+    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(64));
