@@ -122,6 +122,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float low, float high) {
 __device__ __forceinline__ void cluster_arrive_wait() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The two halves on their own: a thread arrives as soon as it has read what it needs of the other blocks' shared
+// memory and waits for the others only before it leaves.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
 __device__ __forceinline__ float load_cluster(uint32_t local_address, uint32_t rank) {
     uint32_t remote;
     float value;
@@ -803,6 +807,7 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
         cluster_arrive_wait();
         const uint32_t mine_address = smem_address(mine);
         constexpr int kMaxRanks = 16;     // the largest cluster the launcher forms: it merges more splits by the merge kernel
+        bool arrived = false;
         for (int index = split * kThreads + threadIdx.x; index < group * D; index += n_splits * kThreads) {
             const int r = index / D, d = index % D;
             // all ranks' values are asked for before the first is used: a load from another block's shared memory
@@ -827,9 +832,14 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
                     denominator += weight;
                 }
             }
+            if (index + n_splits * kThreads >= group * D) {      // the last element of this thread: its values are here
+                cluster_arrive();
+                arrived = true;
+            }
             p.out[(size_t)token * p.n_q_heads * D + (size_t)(kv_head * group + r) * D + d] = __float2bfloat16_rn(numerator / denominator);
         }
-        cluster_arrive_wait();      // nobody leaves while another rank may still read its shared memory
+        if (!arrived) cluster_arrive();
+        cluster_wait();      // nobody leaves while another rank may still read its shared memory
     }
 }
 

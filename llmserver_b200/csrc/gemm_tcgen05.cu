@@ -524,8 +524,15 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
 #pragma unroll
         for (int i = 0; i < 16; ++i) parts_tile[(c0 + i) * kBlockRows + row] = values[i];
     }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     if (p.split > 1) cluster_sync();
     else __syncthreads();
+    // every warp has read its part of the tensor memory (each load waited for its data before the barrier): it is
+    // given back now, so that nothing but the rows' results stands between a warp and its exit
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(64));
+    }
 
     // Lane i finishes elements 4 i .. 4 i + 3 of the tile for its warp's tokens, one token after the other.
     const bool scaled = p.scale.parts != nullptr;
@@ -577,9 +584,6 @@ __global__ void __launch_bounds__(kThreads) gemm_small_m_kernel(const __grid_con
         if (!arrived) cluster_arrive();
         cluster_wait();
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(64));
 }
 
 // Tensor map of a row-major [rows, k] bfloat16 matrix, box = [box_rows, 64] with 128-byte swizzle.
