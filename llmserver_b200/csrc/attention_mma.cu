@@ -126,6 +126,13 @@ __device__ __forceinline__ void cluster_arrive_wait() {
 // memory and waits for the others only before it leaves.
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+__device__ __forceinline__ float2 load_cluster2(uint32_t local_address, uint32_t rank) {
+    uint32_t remote;
+    float2 value;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(rank));
+    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(value.x), "=f"(value.y) : "r"(remote) : "memory");
+    return value;
+}
 __device__ __forceinline__ float load_cluster(uint32_t local_address, uint32_t rank) {
     uint32_t remote;
     float value;
@@ -816,8 +823,11 @@ __global__ void __launch_bounds__(kDecodeThreads) attention_decode_tma_kernel(co
 #pragma unroll
             for (int s = 0; s < kMaxRanks; ++s) {
                 const bool present = s < n_splits;
-                maxima[s] = present ? load_cluster(mine_address + (uint32_t)(r * (D + 2) + D) * 4u, (uint32_t)s) : -INFINITY;
-                sums[s] = present ? load_cluster(mine_address + (uint32_t)(r * (D + 2) + D + 1) * 4u, (uint32_t)s) : 0.0f;
+                // a head's maximum and sum lie side by side (8-byte aligned: D + 2 is even)
+                const float2 statistics = present ? load_cluster2(mine_address + (uint32_t)(r * (D + 2) + D) * 4u, (uint32_t)s)
+                                                  : make_float2(-INFINITY, 0.0f);
+                maxima[s] = statistics.x;
+                sums[s] = statistics.y;
                 outputs[s] = present ? load_cluster(mine_address + (uint32_t)(r * (D + 2) + d) * 4u, (uint32_t)s) : 0.0f;
             }
             float best = -INFINITY;
